@@ -1,0 +1,106 @@
+/* C ABI of the B200 pi0.5 action-chunk engine.
+ *
+ * One handle = one engine on one GPU.  Every pointer is a plain device (or, where stated, host)
+ * pointer; no framework types cross this boundary.  Every function returns a PI05_* status code;
+ * argument errors are detected on the host and never touch the GPU.  Handles hold all state, so
+ * several handles (one per GPU) can live in one process.
+ *
+ * The entry points replace, one for one, the native interface of the reference's megakernel arm
+ * (mk/pi05_mk.cu:3658-3670: setup / workspace_bytes / launch / layout_offsets / build_config /
+ * fg_timeouts / att_timeouts) as it is driven by megakernel.py:117-186.
+ */
+#ifndef PI05_B200_H_
+#define PI05_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct pi05_engine* pi05_handle_t;
+
+enum {
+  PI05_OK = 0,
+  PI05_ERR_ARGUMENT = 1,      /* null pointer, bad size, misaligned buffer, bad handle */
+  PI05_ERR_UNSUPPORTED = 2,   /* geometry / batch / tensor-parallel setting not built */
+  PI05_ERR_CUDA = 3,          /* a CUDA runtime or driver call failed (see pi05_last_error) */
+  PI05_ERR_NOT_BOUND = 4,     /* launch before bind */
+  PI05_ERR_DEVICE_TIMEOUT = 5,/* a bounded device-side wait gave up; see pi05_status */
+  PI05_ERR_NO_DEVICE = 6      /* no usable sm_100 GPU */
+};
+
+/* Number of input tensors and their fixed order (reference megakernel.py:21-25):
+ *  0 action_in_weight [1024,32] f32     1 action_in_bias [1024] f32
+ *  2 time_in_weight [1024,1024] f32     3 time_in_bias [1024] f32
+ *  4 time_out_weight [1024,1024] f32    5 time_out_bias [1024] f32
+ *  6 action_out_weight [32,1024] f32    7 action_out_bias [32] f32
+ *  8 wq [18,2048,1024] bf16   9 wk [18,256,1024] bf16  10 wv [18,256,1024] bf16
+ * 11 wo [18,1024,2048] bf16  12 wg [18,4096,1024] bf16 13 wu [18,4096,1024] bf16
+ * 14 wd [18,1024,4096] bf16
+ * 15 attn_norm_weight [18,3072,1024] f32  16 attn_norm_bias [18,3072] f32
+ * 17 ffn_norm_weight  [18,3072,1024] f32  18 ffn_norm_bias  [18,3072] f32
+ * 19 final_norm_weight [3072,1024] f32    20 final_norm_bias [3072] f32
+ * 21 noise [50,32] f32   22 prefix_k [18,P,1,256] bf16   23 prefix_v [18,P,1,256] bf16
+ * 24 prefix_mask [P] bool (one byte per token, non-zero = valid)                              */
+#define PI05_NUM_INPUTS 25
+
+/* Replaces setup(device) (mk/pi05_mk.cu:3363-3380).  max_prefix bounds the prefix length accepted by
+ * pi05_bind; max_batch, tp_rank and tp_size select the batched / tensor-parallel builds (only
+ * max_batch = 1, tp_size = 1 exist today; anything else returns PI05_ERR_UNSUPPORTED). */
+int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_size, pi05_handle_t* out);
+
+/* Replaces workspace_bytes() (mk/pi05_mk.cu:3659-3660): size of the scratch buffer the caller allocates
+ * on the engine's GPU (256-byte aligned) and passes to pi05_bind. */
+int pi05_workspace_bytes(pi05_handle_t h, size_t* bytes);
+
+/* Replaces the tensor-list half of launch() (mk/pi05_mk.cu:3523-3557) and MegakernelArm.bind
+ * (megakernel.py:167-176): records the 25 device pointers (caller-owned, read-only, kept across launches and
+ * across in-place refills), the output buffer actions [50,32] f32 and the workspace, clears the workspace and
+ * encodes the TMA descriptors.  prefix_len is P (1..max_prefix).  Synchronises the device. */
+int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, int batch,
+              void* actions, void* workspace, size_t workspace_bytes);
+
+/* Counterpart of the harness's optional refresh_weights() (bench.py:209-216).  The engine reads the caller's
+ * tensors in place and keeps no repacked copies, so this only re-validates the binding. */
+int pi05_refresh(pi05_handle_t h);
+
+/* Replaces launch() (mk/pi05_mk.cu:3523-3620): one whole action chunk, asynchronous on `stream` (a cudaStream_t;
+ * NULL = default stream).  n_steps <= 10 Euler steps and n_layers <= 18 expert layers are run (dt stays -0.1);
+ * the graded chunk is (10, 18).  stamps, if non-NULL, is a device buffer of PI05_NUM_STAMPS uint64 that
+ * receives globaltimer values at stage boundaries of the first pass (the reference's tstamp tensor,
+ * mk/pi05_mk.cu:351). */
+int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsigned long long* stamps);
+#define PI05_NUM_STAMPS 64
+
+/* Replaces fg_timeouts()/att_timeouts() (mk/pi05_mk.cu:3505-3520): synchronises the device and reads the status
+ * word the kernel writes when a bounded wait gives up.  code = 0 when the last launches completed; otherwise
+ * code is a PI05_WAIT_* value and where = (cta << 16) | stage.  Clears the word. */
+int pi05_status(pi05_handle_t h, int* code, int* where);
+
+/* Replaces layout_offsets() (mk/pi05_mk.cu:3622-3627): byte offset and size of a named workspace buffer
+ * ("mod", "cond", "h", "an_attn", "an_ffn", "q", "k", "v", "attn", "o_acc", "act", "d_acc", "x", "rope", ...)
+ * for stage-by-stage checks. */
+int pi05_workspace_region(pi05_handle_t h, const char* name, size_t* offset, size_t* bytes);
+
+/* Debug control: run only the first max_stage stages after the prologue (a stage is one of the seven
+ * per-layer steps QKV, attention, O, residual+norm, gate/up, down, residual+norm); negative = run everything.
+ * wait_limit_cycles > 0 overrides the bound of every device-side wait. */
+int pi05_debug(pi05_handle_t h, int max_stage, long long wait_limit_cycles);
+
+/* Replaces build_config() (mk/pi05_mk.cu:3632-3656): a JSON object describing the build and the schedule. */
+const char* pi05_config_json(pi05_handle_t h);
+
+/* Number of kernel launches issued by this handle since creation (one per pi05_launch). */
+int pi05_launch_count(pi05_handle_t h, unsigned long long* count);
+
+const char* pi05_error_string(int code);
+const char* pi05_last_error(pi05_handle_t h);
+
+int pi05_destroy(pi05_handle_t h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PI05_B200_H_ */

@@ -1,0 +1,15 @@
+"""B200-native pi0.5 action-chunk engine: one persistent sm_100a kernel behind a C ABI.
+
+``Pi05Arm`` is the drop-in arm for the reference's benchmark harness; ``fixture``
+holds the geometry and the seeded synthetic inputs.  The native library is loaded
+when an arm is created and its absence is an error (no CPU path exists).
+"""
+
+from .fixture import ORDER, SEEDS, Geometry, make_inputs, sol  # noqa: F401
+
+
+def __getattr__(name):
+    if name == "Pi05Arm":
+        from .arm import Pi05Arm
+        return Pi05Arm
+    raise AttributeError(name)

@@ -1,0 +1,66 @@
+"""ctypes binding of the C ABI declared in ``include/pi05_b200.h``.
+
+There is no fallback: if the shared library is missing or a symbol is absent,
+loading raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libpi05_b200.so")
+NUM_INPUTS = 25
+NUM_STAMPS = 64
+
+OK, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_NOT_BOUND, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE = range(7)
+
+_c = ctypes
+SIGNATURES = {
+    "pi05_create": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_void_p)]),
+    "pi05_workspace_bytes": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_size_t)]),
+    "pi05_bind": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_void_p), _c.c_int, _c.c_int, _c.c_void_p,
+                             _c.c_void_p, _c.c_size_t]),
+    "pi05_refresh": (_c.c_int, [_c.c_void_p]),
+    "pi05_launch": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
+    "pi05_status": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
+    "pi05_workspace_region": (_c.c_int, [_c.c_void_p, _c.c_char_p, _c.POINTER(_c.c_size_t),
+                                         _c.POINTER(_c.c_size_t)]),
+    "pi05_debug": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_longlong]),
+    "pi05_config_json": (_c.c_char_p, [_c.c_void_p]),
+    "pi05_launch_count": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_ulonglong)]),
+    "pi05_error_string": (_c.c_char_p, [_c.c_int]),
+    "pi05_last_error": (_c.c_char_p, [_c.c_void_p]),
+    "pi05_destroy": (_c.c_int, [_c.c_void_p]),
+}
+
+_lib = None
+
+
+class EngineError(RuntimeError):
+    def __init__(self, code: int, message: str) -> None:
+        super().__init__(f"pi05 engine error {code}: {message}")
+        self.code = code
+
+
+def load() -> ctypes.CDLL:
+    """Load the native library (once) and declare every entry point."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m pi05_megakernel_b200.build` "
+                          "(there is no fallback path)")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)       # AttributeError if the library does not export it
+        fn.restype, fn.argtypes = restype, argtypes
+    _lib = lib
+    return lib
+
+
+def check(lib, handle, rc: int) -> None:
+    if rc != OK:
+        detail = lib.pi05_last_error(handle).decode() if handle else ""
+        raise EngineError(rc, lib.pi05_error_string(rc).decode() + (f" ({detail})" if detail else ""))

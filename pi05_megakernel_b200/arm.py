@@ -1,0 +1,142 @@
+"""The engine as a benchmark arm: the reference harness's arm protocol over the C ABI.
+
+Same surface as the reference's ``MegakernelArm`` (megakernel.py:117-186) as the
+harness uses it (bench.py:123-135, 209-216, 234-252): ``Arm(geo, variant,
+device)``, ``bind(inputs)``, ``launch()`` (asynchronous on the current stream,
+one whole chunk), ``outputs()["actions"]`` (a persistent [50, 32] FP32 buffer
+the arm owns), optional ``refresh_weights()``, ``config`` and ``close()``.
+torch only supplies device memory and the current stream; the work is done by
+``libpi05_b200.so``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import json
+
+import torch
+
+from . import _lib
+from .fixture import ORDER, Geometry, shapes
+
+
+def parse_variant(variant: str) -> dict:
+    """``b200`` or ``b200-s<steps>-l<layers>``: the optional suffixes truncate the
+    Euler steps / expert layers (debug runs; the graded chunk is the plain name)."""
+    name, *suffixes = variant.split("-")
+    if name != "b200":
+        raise ValueError(f"bad variant {variant!r}: expected b200[-s<steps>][-l<layers>]")
+    out = {"steps": None, "layers": None}
+    for suffix in suffixes:
+        if len(suffix) > 1 and suffix[0] == "s" and suffix[1:].isdigit() and out["steps"] is None:
+            out["steps"] = int(suffix[1:])
+        elif len(suffix) > 1 and suffix[0] == "l" and suffix[1:].isdigit() and out["layers"] is None:
+            out["layers"] = int(suffix[1:])
+        else:
+            raise ValueError(f"bad variant suffix {suffix!r} in {variant!r}")
+    return out
+
+
+class Pi05Arm:
+    name = "b200-megakernel"
+
+    def __init__(self, geo: Geometry, variant: str = "b200", device: str = "cuda") -> None:
+        if (geo.horizon, geo.action_dim, geo.layers, geo.steps, geo.hidden, geo.intermediate,
+                geo.q_heads, geo.kv_heads, geo.head_dim) != (50, 32, 18, 10, 1024, 4096, 8, 1, 256):
+            raise ValueError("the engine is specialised for horizon 50, action 32, 18 layers, 10 steps, "
+                             "width 1024/4096, 8 query heads over 1 KV head of 256")
+        pv = parse_variant(variant)
+        self.geo, self.variant = geo, variant
+        self.steps = geo.steps if pv["steps"] is None else pv["steps"]
+        self.layers = geo.layers if pv["layers"] is None else pv["layers"]
+        if not (1 <= self.steps <= geo.steps and 1 <= self.layers <= geo.layers):
+            raise ValueError(f"variant {variant!r} asks for more steps or layers than the geometry has")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: the engine has no CPU path")
+        self.lib = _lib.load()
+        self.device = torch.device(device)
+        index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.device = torch.device("cuda", index)
+        handle = ctypes.c_void_p()
+        _lib.check(self.lib, None, self.lib.pi05_create(index, geo.prefix, 1, 0, 1, ctypes.byref(handle)))
+        self.handle = handle
+        nbytes = ctypes.c_size_t()
+        _lib.check(self.lib, handle, self.lib.pi05_workspace_bytes(handle, ctypes.byref(nbytes)))
+        self.ws = torch.empty(nbytes.value, dtype=torch.uint8, device=self.device)
+        self.actions = torch.zeros((geo.horizon, geo.action_dim), dtype=torch.float32, device=self.device)
+        self.tensors: list[torch.Tensor] | None = None
+        self.stamps: torch.Tensor | None = None
+        self.config = json.loads(self.lib.pi05_config_json(handle).decode())
+        self.config.update(prefix=geo.prefix, steps=self.steps, layers=self.layers)
+
+    # ------------------------------------------------------------------ arm protocol
+    def bind(self, inputs: dict) -> None:
+        want = shapes(self.geo)
+        tensors = []
+        for name in ORDER:
+            value = inputs[name]
+            shape, dtype = want[name]
+            if tuple(value.shape) != tuple(shape) or value.dtype != dtype:
+                raise ValueError(f"{name}: expected {shape} {dtype}, got {tuple(value.shape)} {value.dtype}")
+            if not value.is_contiguous():
+                raise ValueError(f"{name} must be contiguous")
+            if value.device != self.device:
+                raise ValueError(f"{name} must live on {self.device}")
+            tensors.append(value)
+        ptrs = (ctypes.c_void_p * _lib.NUM_INPUTS)(*[t.data_ptr() for t in tensors])
+        _lib.check(self.lib, self.handle, self.lib.pi05_bind(
+            self.handle, ptrs, self.geo.prefix, 1, self.actions.data_ptr(), self.ws.data_ptr(),
+            self.ws.numel()))
+        self.tensors = tensors
+
+    def refresh_weights(self) -> None:
+        _lib.check(self.lib, self.handle, self.lib.pi05_refresh(self.handle))
+
+    def launch(self) -> None:
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        stamps = self.stamps.data_ptr() if self.stamps is not None else None
+        _lib.check(self.lib, self.handle, self.lib.pi05_launch(self.handle, self.steps, self.layers, stream, stamps))
+
+    def outputs(self) -> dict:
+        return {"actions": self.actions}
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.pi05_destroy(self.handle)
+            self.handle = None
+        self.tensors = None
+
+    def __del__(self) -> None:  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ diagnostics
+    def status(self) -> tuple[int, int]:
+        """Synchronise and return (code, where) of the device status word; raises on a device timeout."""
+        code, where = ctypes.c_int(), ctypes.c_int()
+        rc = self.lib.pi05_status(self.handle, ctypes.byref(code), ctypes.byref(where))
+        if rc == _lib.ERR_DEVICE_TIMEOUT:
+            raise _lib.EngineError(rc, f"device wait kind {code.value} gave up at cta {where.value >> 16}, "
+                                       f"stage {where.value & 0xffff}")
+        _lib.check(self.lib, self.handle, rc)
+        return code.value, where.value
+
+    def debug(self, max_stage: int = -1, wait_limit_cycles: int = 0) -> None:
+        _lib.check(self.lib, self.handle, self.lib.pi05_debug(self.handle, max_stage, wait_limit_cycles))
+
+    def enable_stamps(self, on: bool = True) -> None:
+        self.stamps = torch.zeros(_lib.NUM_STAMPS, dtype=torch.int64, device=self.device) if on else None
+
+    def region(self, name: str, dtype: torch.dtype, shape: tuple) -> torch.Tensor:
+        """A view of a named workspace buffer (stage-by-stage checks)."""
+        off, nbytes = ctypes.c_size_t(), ctypes.c_size_t()
+        _lib.check(self.lib, self.handle, self.lib.pi05_workspace_region(
+            self.handle, name.encode(), ctypes.byref(off), ctypes.byref(nbytes)))
+        return self.ws[off.value:off.value + nbytes.value].view(dtype).view(shape)
+
+    def launch_count(self) -> int:
+        n = ctypes.c_ulonglong()
+        _lib.check(self.lib, self.handle, self.lib.pi05_launch_count(self.handle, ctypes.byref(n)))
+        return n.value

@@ -1,0 +1,1388 @@
+// B200 (sm_100a) pi0.5 action-chunk engine: the whole chunk (time MLP + adaRMS modulations, then
+// n_steps Euler steps x n_layers Gemma-300M expert layers) as ONE persistent kernel, plus the C ABI.
+//
+// Semantics follow the reference's eager definition of the chunk (reference/pi05.py:218-309) and the rounding
+// schedule its own megakernel uses (mk/pi05_mk.cu:2609-2643 RoPE, 2797-2836 attention, 1301-1327 residual,
+// 1453-1475 step tail).  The structure is new:
+//
+//   * CTAs have fixed roles.  "GEMM CTAs" stream BF16 weights with TMA into a deep shared-memory ring and run
+//     tcgen05 MMAs (weights on the M=128 side, the 50 tokens padded to N=64, FP32 accumulators in TMEM).  Their
+//     weight producer never waits for activations, so HBM keeps streaming across stage, layer and step
+//     boundaries.  "Row CTAs" run attention (warp MMA, online softmax over 64-key chunks) and the per-token
+//     row operations (gated residual, adaRMS, Euler step, action projections).
+//   * Stages are ordered by device-scope counters (release add / acquire poll) that only the producers of a
+//     stage bump and only its consumers poll; there is no grid-wide barrier inside the layer loop.
+//   * Every wait is bounded.  A wait that gives up writes a status word, every other wait sees it and the
+//     kernel drains and exits; the host reads the word through pi05_status().
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/pi05_b200.h"
+#include "ptx_sm100.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------------------------------- geometry
+constexpr int T = 50;          // action tokens
+constexpr int ADIM = 32;       // action width
+constexpr int W = 1024;        // expert width
+constexpr int NL = 18;         // expert layers
+constexpr int NS = 10;         // Euler steps
+constexpr int HD = 256;        // head dim
+constexpr int NQH = 8;         // query heads (one KV head)
+constexpr int QD = NQH * HD;   // 2048
+constexpr int FF = 4096;       // MLP width
+constexpr int NNORM = 2 * NL + 1;  // adaRMS norms (attn, ffn per layer + final)
+constexpr int MODW = 3 * W;        // scale | shift | gate
+constexpr float EPS = 1e-6f;
+
+constexpr int THREADS = 256;
+constexpr int NROW_CTAS = 25;      // attention / row-op CTAs: two tokens each
+constexpr int KATOM = 64;          // K elements per TMA box (128 B of BF16 = one swizzle row)
+constexpr int W_ATOM_BYTES = 128 * 128;  // 128 weight rows x 64 k
+constexpr int A_ATOM_BYTES = 64 * 128;   // 64 token rows x 64 k
+constexpr int NW = 10;             // weight ring depth (160 KB)
+constexpr int NA = 4;              // activation ring depth (32 KB)
+constexpr int STAGE_STRIDE = 72;   // BF16 elements per row of the epilogue exchange buffer (144 B)
+constexpr int STAGE_BYTES = 128 * STAGE_STRIDE * 2;
+constexpr int TMEM_COLS = 128;     // two 64-column accumulators
+
+constexpr int OFF_WRING = 0;
+constexpr int OFF_ARING = OFF_WRING + NW * W_ATOM_BYTES;
+constexpr int OFF_STAGE = OFF_ARING + NA * A_ATOM_BYTES;   // also the prologue's scratch
+constexpr int OFF_BARS = OFF_STAGE + STAGE_BYTES;
+constexpr int SMEM_BYTES = OFF_BARS + 512 + 1024;          // + barriers + alignment slack
+
+// attention shared-memory layout (row CTAs), all below OFF_STAGE
+constexpr int KV_STRIDE = HD + 8;                   // BF16 elements per K/V/Q row (528 B: conflict-free ldmatrix)
+constexpr int KV_STAGE_BYTES = 64 * KV_STRIDE * 2;  // one 64-key chunk of K or of V
+constexpr int P_STRIDE = 64 + 8;
+constexpr int OFF_KS = 0;
+constexpr int OFF_VS = OFF_KS + 2 * KV_STAGE_BYTES;
+constexpr int OFF_QS = OFF_VS + 2 * KV_STAGE_BYTES;
+constexpr int OFF_PS = OFF_QS + 16 * KV_STRIDE * 2;
+constexpr int OFF_RED = OFF_PS + 16 * P_STRIDE * 2;          // float [8][16]
+constexpr int OFF_KVALID = OFF_RED + 8 * 16 * 4;             // uint8 [2][64]
+constexpr int OFF_ROWBUF = OFF_KVALID + 128;                 // row-op scratch: float [2][1024 + 64]
+constexpr int ATT_SMEM_END = OFF_ROWBUF + 2 * (1024 + 64) * 4;
+static_assert(ATT_SMEM_END <= OFF_STAGE, "attention smem must not reach the prologue scratch");
+static_assert(SMEM_BYTES <= 232448, "over the 227 KB per-CTA limit");
+
+// stages of one layer pass, in dependency order
+enum { ST_QKV = 0, ST_ATT = 1, ST_O = 2, ST_RATT = 3, ST_GU = 4, ST_DOWN = 5, ST_RFFN = 6, NSTAGE = 7 };
+enum { G_QKV = 0, G_O = 1, G_GU = 2, G_DOWN = 3 };
+__device__ __constant__ int kGemmStage[4] = {ST_QKV, ST_O, ST_GU, ST_DOWN};
+
+// event counters (uint32 each) in the control block
+enum { EV_P0 = 0, EV_P1, EV_P2, EV_P3, EV_ANA, EV_QKV, EV_ATT, EV_O, EV_ANF, EV_GU, EV_DOWN, EV_EXIT, NEVENTS };
+
+// wait kinds reported in the status word
+enum { WAIT_W_EMPTY = 1, WAIT_W_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_T_EMPTY, WAIT_T_FULL, WAIT_EVENT,
+       WAIT_DRAIN };
+
+struct Unit { int gemm, tile, k0, nk; };
+constexpr int MAX_UNITS = 8;
+
+struct alignas(64) TMaps {
+  CUtensorMap wq, wk, wv, wo, wg, wu, wd;   // weights: {K, L*rows} BF16, box {64, 64}, 128-B swizzle
+  CUtensorMap an_attn, an_ffn, attn, act;   // activations: {K, 50} BF16, box {64, 64}, rows >= 50 read as zero
+};
+
+struct Params {
+  TMaps maps;
+  // inputs
+  const float *ain_w, *ain_b, *tin_w, *tin_b, *tout_w, *tout_b, *aout_w, *aout_b;
+  const float *attn_nw, *attn_nb, *ffn_nw, *ffn_nb, *fin_nw, *fin_nb;
+  const float* noise;
+  const __nv_bfloat16 *prefix_k, *prefix_v;
+  const uint8_t* prefix_mask;
+  float* actions;
+  // workspace
+  unsigned int* ctrl;      // [0..3] status, [16 + e] event counters
+  float *temb, *hid, *cond, *mod, *x, *o_acc, *d_acc;
+  uint32_t* rope;          // [T][128] (cos bf16 | sin bf16 << 16)
+  __nv_bfloat16 *h, *an_attn, *an_ffn, *q, *k, *v, *attn, *act;
+  const Unit* sched;       // [grid][MAX_UNITS]
+  const int* sched_n;      // [grid]
+  unsigned long long* stamps;
+  long long wait_limit;
+  int prefix, n_steps, n_layers, max_stage, n_gemm_ctas;
+  int n_units[4];          // units per GEMM kind (event targets)
+  float t_steps[NS];
+  float dt;
+};
+
+// ------------------------------------------------------------------------------------------- bounded waits
+struct Ctx {
+  unsigned int* status;
+  long long limit;
+  int cta;
+};
+
+__device__ __noinline__ void report_timeout(const Ctx& c, int kind, int stage) {
+  if (atomicCAS(c.status, 0u, (unsigned)kind) == 0u) {
+    c.status[1] = ((unsigned)c.cta << 16) | ((unsigned)stage & 0xffffu);
+    __threadfence();
+  }
+}
+
+// Returns false when the wait gave up (limit reached, or another wait already reported an error).
+__device__ __forceinline__ bool wait_mbar(const Ctx& c, uint32_t bar, uint32_t parity, int kind, int stage) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (unsigned i = 0;; ++i) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((i & 31u) == 31u) {
+      if (ptx::ld_relaxed(c.status) != 0u) return false;
+      if (clock64() - t0 > c.limit) { report_timeout(c, kind, stage); return false; }
+    }
+  }
+}
+
+__device__ __forceinline__ bool wait_event(const Ctx& c, const unsigned int* ev, unsigned int target, int stage) {
+  if ((int)(ptx::ld_acquire(ev) - target) >= 0) return true;
+  const long long t0 = clock64();
+  for (unsigned i = 0;; ++i) {
+    if ((int)(ptx::ld_acquire(ev) - target) >= 0) return true;
+    if ((i & 31u) == 31u) {
+      if (ptx::ld_relaxed(c.status) != 0u) return false;
+      if (clock64() - t0 > c.limit) { report_timeout(c, WAIT_EVENT, stage); return false; }
+    }
+    __nanosleep(20);
+  }
+}
+
+// Called by one thread after the CTA-level barrier that follows the CTA's writes.
+__device__ __forceinline__ void signal_event(unsigned int* ev) {
+  ptx::fence_acq_rel_gpu();
+  ptx::red_release_add(ev, 1u);
+}
+
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// ------------------------------------------------------------------------------------------- small math
+__device__ __forceinline__ float rb(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float z = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(z));
+}
+
+// ------------------------------------------------------------------------------------------- prologue
+// Sum ten per-lane partials over the 32 lanes with 12 shuffles; lanes with an even index end up holding
+// the total of value `idx` (idx < 0: nothing).  The order of additions is fixed.
+__device__ __forceinline__ float reduce10(float (&v)[10], int lane, int& idx) {
+  const unsigned full = 0xffffffffu;
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4, b1 = lane & 2;
+#pragma unroll
+  for (int i = 0; i < 5; ++i) {
+    const float send = b4 ? v[i] : v[i + 5];
+    const float keep = b4 ? v[i + 5] : v[i];
+    v[i] = keep + __shfl_xor_sync(full, send, 16);
+  }
+  {
+    const float s0 = b3 ? v[0] : v[3], k0 = b3 ? v[3] : v[0];
+    const float s1 = b3 ? v[1] : v[4], k1 = b3 ? v[4] : v[1];
+    const float s2 = b3 ? v[2] : 0.f, k2 = b3 ? 0.f : v[2];
+    v[0] = k0 + __shfl_xor_sync(full, s0, 8);
+    v[1] = k1 + __shfl_xor_sync(full, s1, 8);
+    v[2] = k2 + __shfl_xor_sync(full, s2, 8);
+  }
+  {
+    const float s0 = b2 ? v[0] : v[2], k0 = b2 ? v[2] : v[0];
+    const float s1 = b2 ? v[1] : 0.f, k1 = b2 ? 0.f : v[1];
+    v[0] = k0 + __shfl_xor_sync(full, s0, 4);
+    v[1] = k1 + __shfl_xor_sync(full, s1, 4);
+  }
+  {
+    const float s0 = b1 ? v[0] : v[1], k0 = b1 ? v[1] : v[0];
+    v[0] = k0 + __shfl_xor_sync(full, s0, 2);
+  }
+  v[0] += __shfl_xor_sync(full, v[0], 1);
+  int in5 = b3 ? (b2 ? -1 : 3 + (b1 ? 1 : 0)) : (b2 ? (b1 ? -1 : 2) : (b1 ? 1 : 0));
+  idx = in5 < 0 ? -1 : in5 + (b4 ? 5 : 0);
+  return v[0];
+}
+
+// out[s][row] = f(W[row][:] . in[s][:] + bias[row]) for the ten time steps at once; FP32 weights streamed from
+// HBM exactly once.  Four warps share a row (a quarter of K each, the ten input vectors of that quarter live in
+// registers), eight rows per batch.  MODE 0/1: time MLP layers (SiLU).  MODE 2: the 37 modulation layers.
+template <int MODE>
+__device__ void matvec10(const Params& p, const float* __restrict__ in, uint8_t* smem, int cta, int ncta) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = warp >> 2, quarter = warp & 3;
+  const int koff = quarter * 256 + lane * 4;
+  float c[NS][8];
+#pragma unroll
+  for (int s = 0; s < NS; ++s) {
+    const float4 a = *reinterpret_cast<const float4*>(in + s * W + koff);
+    const float4 b = *reinterpret_cast<const float4*>(in + s * W + koff + 128);
+    c[s][0] = a.x; c[s][1] = a.y; c[s][2] = a.z; c[s][3] = a.w;
+    c[s][4] = b.x; c[s][5] = b.y; c[s][6] = b.z; c[s][7] = b.w;
+  }
+  float* part = reinterpret_cast<float*>(smem + OFF_STAGE);  // [2 buf][2 group][4 quarter][8 row][10]
+  const int nrows = (MODE == 2) ? NNORM * MODW : W;
+  const int nbatch = nrows / 8;
+  int it = 0;
+  for (int b = cta * 2 + group; b < nbatch; b += ncta * 2, ++it) {
+    const int row0 = b * 8;
+    const float* wbase;
+    const float* bias;
+    float* out;      // out[s * ostride + r]
+    int ostride;
+    if (MODE == 0) { wbase = p.tin_w + (size_t)row0 * W; bias = p.tin_b + row0; out = p.hid + row0; ostride = W; }
+    else if (MODE == 1) { wbase = p.tout_w + (size_t)row0 * W; bias = p.tout_b + row0; out = p.cond + row0; ostride = W; }
+    else {
+      const int n = row0 / MODW, j = row0 % MODW;
+      if (n == NNORM - 1) { wbase = p.fin_nw + (size_t)j * W; bias = p.fin_nb + j; }
+      else if (n & 1) { wbase = p.ffn_nw + ((size_t)(n >> 1) * MODW + j) * W; bias = p.ffn_nb + (size_t)(n >> 1) * MODW + j; }
+      else { wbase = p.attn_nw + ((size_t)(n >> 1) * MODW + j) * W; bias = p.attn_nb + (size_t)(n >> 1) * MODW + j; }
+      out = p.mod + (size_t)n * MODW + j;
+      ostride = NNORM * MODW;
+    }
+    float4 w[8][2];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      w[r][0] = ptx::ldg_stream_f4(wbase + (size_t)r * W + koff);
+      w[r][1] = ptx::ldg_stream_f4(wbase + (size_t)r * W + koff + 128);
+    }
+    float* pb = part + (((it & 1) * 2 + group) * 4 + quarter) * 80;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      float acc[10];
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        float a = w[r][0].x * c[s][0];
+        a = fmaf(w[r][0].y, c[s][1], a);
+        a = fmaf(w[r][0].z, c[s][2], a);
+        a = fmaf(w[r][0].w, c[s][3], a);
+        a = fmaf(w[r][1].x, c[s][4], a);
+        a = fmaf(w[r][1].y, c[s][5], a);
+        a = fmaf(w[r][1].z, c[s][6], a);
+        a = fmaf(w[r][1].w, c[s][7], a);
+        acc[s] = a;
+      }
+      int idx;
+      const float tot = reduce10(acc, lane, idx);
+      if (!(lane & 1) && idx >= 0) pb[r * 10 + idx] = tot;
+    }
+    ptx::named_bar_sync(2 + group, 128);
+    const int i = tid & 127;
+    if (i < 80) {
+      const int r = i / 10, s = i % 10;
+      const float* q0 = part + (((it & 1) * 2 + group) * 4) * 80 + r * 10 + s;
+      float v = ((q0[0] + q0[80]) + (q0[160] + q0[240])) + bias[r];
+      if (MODE != 2) v = silu(v);
+      out[(size_t)s * ostride + r] = v;
+    }
+  }
+}
+
+// Grid-wide rendezvous of the prologue: every CTA arrives, every CTA waits.
+__device__ bool grid_event(const Params& p, const Ctx& c, int ev, int ncta) {
+  __syncthreads();
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) {
+    signal_event(p.ctrl + 16 + ev);
+    ok_flag = wait_event(c, p.ctrl + 16 + ev, (unsigned)ncta, -1 - ev) ? 1 : 0;
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+__device__ int count_valid(const Params& p) {
+  __shared__ int s_cnt;
+  if (threadIdx.x == 0) s_cnt = 0;
+  __syncthreads();
+  int n = 0;
+  for (int i = threadIdx.x; i < p.prefix; i += THREADS) n += p.prefix_mask[i] ? 1 : 0;
+  for (int o = 16; o; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+  if ((threadIdx.x & 31) == 0 && n) atomicAdd(&s_cnt, n);
+  __syncthreads();
+  return s_cnt;
+}
+
+// Time embedding (FP64, reference/pi05.py:232-237), RoPE table (reference/pi05.py:218-229) and clearing of the
+// split-K accumulators.
+__device__ void prologue_tables(const Params& p, int cta, int ncta) {
+  const int nvalid = count_valid(p);
+  const int gtid = cta * THREADS + threadIdx.x, gn = ncta * THREADS;
+  for (int i = gtid; i < NS * W; i += gn) {
+    const int s = i / W, j = i % W, f = j % (W / 2);
+    const double step = 1.0 / (W / 2 - 1);
+    const double frac = f < (W / 4) ? step * f : 1.0 - step * (W / 2 - 1 - f);
+    const double period = 4e-3 * pow(4.0 / 4e-3, frac);
+    const double phase = (double)p.t_steps[s] * (1.0 / period * 2 * 3.141592653589793);
+    p.temb[i] = (float)(j < W / 2 ? sin(phase) : cos(phase));
+  }
+  for (int i = gtid; i < T * (HD / 2); i += gn) {
+    const int t = i / (HD / 2), j = i % (HD / 2);
+    const float e = (float)(2 * j) / (float)HD;
+    const float inv = 1.0f / (float)pow(10000.0, (double)e);
+    const float phase = (float)(nvalid + t) * inv;
+    p.rope[i] = pack_bf16((float)cos((double)phase), (float)sin((double)phase));
+  }
+  for (int i = gtid; i < T * W; i += gn) { p.o_acc[i] = 0.f; p.d_acc[i] = 0.f; }
+}
+
+// ------------------------------------------------------------------------------------------- row operations
+enum { ROW_INIT = 0, ROW_ATT = 1, ROW_FFN = 2 };
+
+// Per-token work between GEMMs, two tokens per CTA, 128 threads per token, 8 columns per thread:
+//   ROW_ATT: h += bf16(bf16(o_acc) * gate_attn); an_ffn = adaRMS_ffn(h)
+//   ROW_FFN: h += bf16(bf16(d_acc) * gate_ffn); then either an_attn = adaRMS_attn[l+1](h), or at the last layer
+//            the step tail: final adaRMS, v = Wout n + b, x += dt v, and (unless it was the last step)
+//            h = bf16(Win x + b), an_attn = adaRMS_attn[0](h) with the next step's modulation.
+//   ROW_INIT: x = noise, h = bf16(Win x + b), an_attn = adaRMS_attn[0](h).
+__device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int step, int layer) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int half = tid >> 7, i = tid & 127, wq = (tid >> 5) & 3;
+  const int t = unit * 2 + half;
+  const int c0 = i * 8;
+  float* rowbuf = reinterpret_cast<float*>(smem + OFF_ROWBUF) + half * (1024 + 64);
+  float* red = rowbuf + 1024;      // [0..3] warp sums, [8..39] x row
+  const int bar = 4 + half;
+  const float* mod_s = p.mod + (size_t)step * NNORM * MODW;
+
+  float hn[8];
+  auto sumsq = [&](const float (&v)[8]) -> float {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    ptx::named_bar_sync(bar, 128);          // previous use of red[] is over
+    if (lane == 0) red[wq] = ss;
+    ptx::named_bar_sync(bar, 128);
+    return (red[0] + red[1]) + (red[2] + red[3]);
+  };
+  auto ada_norm = [&](const float (&v)[8], const float* mod, __nv_bfloat16* dst) {
+    const float ss = sumsq(v);
+    const float rs = 1.0f / sqrtf(ss * (1.0f / W) + EPS);
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+      const float a = __fadd_rn(__fmul_rn(__fmul_rn(v[e], rs), __fadd_rn(1.0f, mod[c0 + e])), mod[W + c0 + e]);
+      const float b = __fadd_rn(__fmul_rn(__fmul_rn(v[e + 1], rs), __fadd_rn(1.0f, mod[c0 + e + 1])), mod[W + c0 + e + 1]);
+      o[e >> 1] = pack_bf16(a, b);
+    }
+    *reinterpret_cast<uint4*>(dst + (size_t)t * W + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+  };
+  auto store_h = [&](const float (&v)[8]) {
+    uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+    *reinterpret_cast<uint4*>(p.h + (size_t)t * W + c0) = o;
+  };
+  // h = bf16(Win x + b) for this thread's 8 columns; x row in red[8..39]
+  auto action_in = [&]() {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float* wr = p.ain_w + (size_t)(c0 + e) * ADIM;
+      float a = 0.f;
+#pragma unroll
+      for (int k = 0; k < ADIM; k += 4) {
+        const float4 w4 = *reinterpret_cast<const float4*>(wr + k);
+        a = fmaf(w4.x, red[8 + k], a); a = fmaf(w4.y, red[9 + k], a);
+        a = fmaf(w4.z, red[10 + k], a); a = fmaf(w4.w, red[11 + k], a);
+      }
+      hn[e] = rb(a + p.ain_b[c0 + e]);
+    }
+  };
+
+  if (mode == ROW_INIT) {
+    if (i < ADIM) { const float xv = p.noise[t * ADIM + i]; p.x[t * ADIM + i] = xv; red[8 + i] = xv; }
+    ptx::named_bar_sync(bar, 128);
+    action_in();
+    store_h(hn);
+    ada_norm(hn, mod_s, p.an_attn);
+    return;
+  }
+
+  // gated residual
+  float* acc = (mode == ROW_ATT ? p.o_acc : p.d_acc) + (size_t)t * W + c0;
+  const float* gate = mod_s + (size_t)(2 * layer + (mode == ROW_ATT ? 0 : 1)) * MODW + 2 * W + c0;
+  {
+    const float4 a0 = *reinterpret_cast<const float4*>(acc), a1 = *reinterpret_cast<const float4*>(acc + 4);
+    *reinterpret_cast<float4*>(acc) = make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(acc + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    const uint4 hv = *reinterpret_cast<const uint4*>(p.h + (size_t)t * W + c0);
+    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float hold = (e & 1) ? bf16_hi(hw[e >> 1]) : bf16_lo(hw[e >> 1]);
+      hn[e] = rb(hold + rb(rb(av[e]) * rb(gate[e])));
+    }
+  }
+  if (mode == ROW_ATT) {
+    store_h(hn);
+    ada_norm(hn, mod_s + (size_t)(2 * layer + 1) * MODW, p.an_ffn);
+    return;
+  }
+  if (layer + 1 < p.n_layers) {
+    store_h(hn);
+    ada_norm(hn, mod_s + (size_t)(2 * layer + 2) * MODW, p.an_attn);
+    return;
+  }
+  // ---- step tail: final norm, action_out, Euler update
+  {
+    const float* mod = mod_s + (size_t)(NNORM - 1) * MODW;
+    const float ss = sumsq(hn);
+    const float rs = 1.0f / sqrtf(ss * (1.0f / W) + EPS);
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      rowbuf[c0 + e] = rb(__fadd_rn(__fmul_rn(__fmul_rn(hn[e], rs), __fadd_rn(1.0f, mod[c0 + e])), mod[W + c0 + e]));
+    ptx::named_bar_sync(bar, 128);
+    // warp wq: outputs wq*8 .. wq*8+7
+    for (int a = wq * 8; a < wq * 8 + 8; ++a) {
+      const float* wr = p.aout_w + (size_t)a * W;
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = lane * 4 + j * 128;
+        const float4 w4 = *reinterpret_cast<const float4*>(wr + k);
+        s = fmaf(w4.x, rowbuf[k], s); s = fmaf(w4.y, rowbuf[k + 1], s);
+        s = fmaf(w4.z, rowbuf[k + 2], s); s = fmaf(w4.w, rowbuf[k + 3], s);
+      }
+      for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0) {
+        const float vel = s + p.aout_b[a];
+        const float xn = p.x[t * ADIM + a] + p.dt * vel;
+        p.x[t * ADIM + a] = xn;
+        red[8 + a] = xn;
+        if (step + 1 == p.n_steps) p.actions[t * ADIM + a] = xn;
+      }
+    }
+    ptx::named_bar_sync(bar, 128);
+    if (step + 1 < p.n_steps) {
+      action_in();
+      store_h(hn);
+      ada_norm(hn, p.mod + (size_t)(step + 1) * NNORM * MODW, p.an_attn);
+    } else {
+      store_h(hn);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- attention
+// 16 query rows (2 tokens x 8 heads, all sharing the one KV head) against [prefix ; suffix] keys in 64-key chunks.
+// Scores: bf16(q.k) / 16, masked; running max; p = bf16(exp(s - m)); o += p V (FP32); out = bf16(o / sum exp).
+struct AttChunkIssue {
+  const Params& p;
+  uint8_t* smem;
+  int layer, npc;
+  __device__ void operator()(int chunk, int stage) const {
+    const int tid = threadIdx.x;
+    uint8_t* ks = smem + OFF_KS + stage * KV_STAGE_BYTES;
+    uint8_t* vs = smem + OFF_VS + stage * KV_STAGE_BYTES;
+    uint8_t* kvalid = smem + OFF_KVALID + stage * 64;
+    const bool is_prefix = chunk < npc;
+    const __nv_bfloat16* ksrc = is_prefix ? p.prefix_k + ((size_t)layer * p.prefix + (size_t)chunk * 64) * HD : p.k;
+    const __nv_bfloat16* vsrc = is_prefix ? p.prefix_v + ((size_t)layer * p.prefix + (size_t)chunk * 64) * HD : p.v;
+    const int nrows = is_prefix ? min(64, p.prefix - chunk * 64) : T;
+    if (tid < 64) {
+      uint8_t ok = 0;
+      if (tid < nrows) ok = is_prefix ? (p.prefix_mask[chunk * 64 + tid] ? 1 : 0) : 1;
+      kvalid[tid] = ok;
+    }
+    // 64 rows x 32 16-byte pieces for K, then the same for V
+    for (int idx = tid; idx < 2 * 64 * 32; idx += THREADS) {
+      const int isv = idx >= 64 * 32;
+      const int r = (idx >> 5) & 63, cidx = idx & 31;
+      uint8_t* dst = (isv ? vs : ks) + r * (KV_STRIDE * 2) + cidx * 16;
+      if (r < nrows) ptx::cp_async_16(ptx::smem_u32(dst), (isv ? vsrc : ksrc) + (size_t)r * HD + cidx * 8);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    ptx::cp_async_commit();
+  }
+};
+
+__device__ void attention_unit(const Params& p, uint8_t* smem, int unit, const AttChunkIssue& issue) {
+  const int npc = issue.npc;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, qd = lane & 3;
+  const int nchunks = npc + 1;
+  const uint32_t qs = ptx::smem_u32(smem + OFF_QS), ps = ptx::smem_u32(smem + OFF_PS);
+  float* red = reinterpret_cast<float*>(smem + OFF_RED);
+
+  float m_lo = -1e30f, m_hi = -1e30f, l_lo = 0.f, l_hi = 0.f;
+  float o[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) o[a][b] = 0.f;
+
+  for (int c = 0; c < nchunks; ++c) {
+    const int stage = c & 1;
+    const uint32_t ks = ptx::smem_u32(smem + OFF_KS + stage * KV_STAGE_BYTES);
+    const uint32_t vs = ptx::smem_u32(smem + OFF_VS + stage * KV_STAGE_BYTES);
+    const uint8_t* kvalid = smem + OFF_KVALID + stage * 64;
+    // ---- S = Q K^T for this warp's 8 keys
+    float s4[4] = {0.f, 0.f, 0.f, 0.f};
+    const int kb = warp * 8;
+#pragma unroll 4
+    for (int kk = 0; kk < HD / 16; kk += 2) {
+      uint32_t a0, a1, a2, a3, a4, a5, a6, a7, b0, b1, b2, b3;
+      const uint32_t qaddr = qs + ((lane & 15) * KV_STRIDE + kk * 16 + (lane >> 4) * 8) * 2;
+      ptx::ldmatrix_x4(qaddr, a0, a1, a2, a3);
+      ptx::ldmatrix_x4(qaddr + 32, a4, a5, a6, a7);
+      const uint32_t kaddr = ks + ((kb + (lane & 7)) * KV_STRIDE + kk * 16 + (lane >> 3) * 8) * 2;
+      ptx::ldmatrix_x4(kaddr, b0, b1, b2, b3);
+      ptx::mma_16816(s4, a0, a1, a2, a3, b0, b1);
+      ptx::mma_16816(s4, a4, a5, a6, a7, b2, b3);
+    }
+    const bool v0 = kvalid[kb + 2 * qd] != 0, v1 = kvalid[kb + 2 * qd + 1] != 0;
+    const float NEG = -INFINITY;
+    float s_lo0 = v0 ? rb(s4[0]) * 0.0625f : NEG, s_lo1 = v1 ? rb(s4[1]) * 0.0625f : NEG;
+    float s_hi0 = v0 ? rb(s4[2]) * 0.0625f : NEG, s_hi1 = v1 ? rb(s4[3]) * 0.0625f : NEG;
+    float cm_lo = fmaxf(s_lo0, s_lo1), cm_hi = fmaxf(s_hi0, s_hi1);
+    cm_lo = fmaxf(cm_lo, __shfl_xor_sync(0xffffffffu, cm_lo, 1));
+    cm_lo = fmaxf(cm_lo, __shfl_xor_sync(0xffffffffu, cm_lo, 2));
+    cm_hi = fmaxf(cm_hi, __shfl_xor_sync(0xffffffffu, cm_hi, 1));
+    cm_hi = fmaxf(cm_hi, __shfl_xor_sync(0xffffffffu, cm_hi, 2));
+    if (qd == 0) { red[warp * 16 + g] = cm_lo; red[warp * 16 + g + 8] = cm_hi; }
+    __syncthreads();
+    float mn_lo = m_lo, mn_hi = m_hi;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) {
+      mn_lo = fmaxf(mn_lo, red[w8 * 16 + g]);
+      mn_hi = fmaxf(mn_hi, red[w8 * 16 + g + 8]);
+    }
+    const float al_lo = expf(m_lo - mn_lo), al_hi = expf(m_hi - mn_hi);
+    m_lo = mn_lo; m_hi = mn_hi;
+    const float p00 = expf(s_lo0 - mn_lo), p01 = expf(s_lo1 - mn_lo);
+    const float p10 = expf(s_hi0 - mn_hi), p11 = expf(s_hi1 - mn_hi);
+    l_lo = l_lo * al_lo + (p00 + p01);
+    l_hi = l_hi * al_hi + (p10 + p11);
+    {
+      uint8_t* pbase = smem + OFF_PS;
+      *reinterpret_cast<uint32_t*>(pbase + (g * P_STRIDE + kb + 2 * qd) * 2) = pack_bf16(p00, p01);
+      *reinterpret_cast<uint32_t*>(pbase + ((g + 8) * P_STRIDE + kb + 2 * qd) * 2) = pack_bf16(p10, p11);
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) { o[nt][0] *= al_lo; o[nt][1] *= al_lo; o[nt][2] *= al_hi; o[nt][3] *= al_hi; }
+    __syncthreads();
+    // ---- O += P V for this warp's 32 output dims
+    const int db = warp * 32;
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t a0, a1, a2, a3, r0, r1, r2, r3, r4, r5, r6, r7;
+      ptx::ldmatrix_x4(ps + ((lane & 15) * P_STRIDE + kk * 16 + (lane >> 4) * 8) * 2, a0, a1, a2, a3);
+      const uint32_t vaddr = vs + ((kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KV_STRIDE + db + (lane >> 4) * 8) * 2;
+      ptx::ldmatrix_x4_trans(vaddr, r0, r1, r2, r3);
+      ptx::ldmatrix_x4_trans(vaddr + 32, r4, r5, r6, r7);
+      ptx::mma_16816(o[0], a0, a1, a2, a3, r0, r1);
+      ptx::mma_16816(o[1], a0, a1, a2, a3, r2, r3);
+      ptx::mma_16816(o[2], a0, a1, a2, a3, r4, r5);
+      ptx::mma_16816(o[3], a0, a1, a2, a3, r6, r7);
+    }
+    __syncthreads();   // P, red and this K/V stage may be overwritten from here on
+    if (c + 2 < nchunks) {
+      // refill this stage with chunk c + 2, then make sure chunk c + 1 has landed
+      issue(c + 2, stage);
+      ptx::cp_async_wait<1>();
+    } else {
+      ptx::cp_async_wait<0>();
+    }
+    __syncthreads();
+  }
+  // ---- normalise and store
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  if (qd == 0) { red[warp * 16 + g] = l_lo; red[warp * 16 + g + 8] = l_hi; }
+  __syncthreads();
+  float tl_lo = 0.f, tl_hi = 0.f;
+#pragma unroll
+  for (int w8 = 0; w8 < 8; ++w8) { tl_lo += red[w8 * 16 + g]; tl_hi += red[w8 * 16 + g + 8]; }
+  const float il_lo = 1.0f / tl_lo, il_hi = 1.0f / tl_hi;
+  __nv_bfloat16* out = p.attn + (size_t)unit * 2 * QD;   // rows m = token_local * 8 + head are contiguous
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int col = warp * 32 + nt * 8 + 2 * qd;
+    *reinterpret_cast<uint32_t*>(out + (size_t)g * HD + col) = pack_bf16(o[nt][0] * il_lo, o[nt][1] * il_lo);
+    *reinterpret_cast<uint32_t*>(out + (size_t)(g + 8) * HD + col) = pack_bf16(o[nt][2] * il_hi, o[nt][3] * il_hi);
+  }
+  ptx::fence_proxy_async_global();   // attn is read by the O projection's TMA
+}
+
+// ------------------------------------------------------------------------------------------- GEMM CTA roles
+struct Bars {
+  uint32_t wfull, wempty, afull, aempty, tfull, tempty;   // shared-memory addresses of barrier arrays
+};
+
+__device__ __forceinline__ int stage_of(int pass, int gemm) { return pass * NSTAGE + kGemmStage[gemm]; }
+
+struct Producer { int pass, u, a; uint32_t it; bool done; };
+
+// Issue weight loads in schedule order until `until` loads have been issued in total (or the schedule ends).
+__device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t wring,
+                                const Bars& b, Producer& st, uint32_t until, uint64_t policy) {
+  const int npass = p.n_steps * p.n_layers;
+  while (!st.done && st.it < until) {
+    if (st.pass >= npass) { st.done = true; break; }
+    if (st.u >= nunits) { st.u = 0; ++st.pass; continue; }
+    const Unit un = units[st.u];
+    if (stage_of(st.pass, un.gemm) >= p.max_stage) { st.done = true; break; }
+    if (st.a >= un.nk) { st.a = 0; ++st.u; continue; }
+    const int slot = st.it % NW;
+    const uint32_t par = (st.it / NW) & 1;
+    if (!wait_mbar(c, b.wempty + 8 * slot, par ^ 1, WAIT_W_EMPTY, stage_of(st.pass, un.gemm))) { st.done = true; break; }
+    const int layer = st.pass % p.n_layers;
+    const CUtensorMap *ma, *mb;
+    int ra, rbw;
+    if (un.gemm == G_QKV) {
+      if (un.tile < 16) { ma = mb = &p.maps.wq; ra = layer * QD + (un.tile >> 1) * HD + (un.tile & 1) * 64; rbw = ra + 128; }
+      else if (un.tile < 18) { ma = mb = &p.maps.wk; ra = layer * HD + (un.tile - 16) * 64; rbw = ra + 128; }
+      else { ma = mb = &p.maps.wv; ra = layer * HD + (un.tile - 18) * 128; rbw = ra + 64; }
+    } else if (un.gemm == G_O) { ma = mb = &p.maps.wo; ra = layer * W + un.tile * 128; rbw = ra + 64; }
+    else if (un.gemm == G_GU) { ma = &p.maps.wg; mb = &p.maps.wu; ra = rbw = layer * FF + un.tile * 64; }
+    else { ma = mb = &p.maps.wd; ra = layer * W + un.tile * 128; rbw = ra + 64; }
+    const uint32_t full = b.wfull + 8 * slot;
+    const uint32_t dst = wring + slot * W_ATOM_BYTES;
+    const int kc = (un.k0 + st.a) * KATOM;
+    ptx::mbar_expect_tx(full, W_ATOM_BYTES);
+    ptx::tma_load_2d_hint(dst, ma, full, kc, ra, policy);
+    ptx::tma_load_2d_hint(dst + W_ATOM_BYTES / 2, mb, full, kc, rbw, policy);
+    ++st.a;
+    ++st.it;
+  }
+}
+
+__device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t aring, const Bars& b) {
+  const int npass = p.n_steps * p.n_layers;
+  uint32_t ait = 0;
+  for (int pass = 0; pass < npass; ++pass) {
+    for (int u = 0; u < nunits; ++u) {
+      const Unit un = units[u];
+      const int stage = stage_of(pass, un.gemm);
+      if (stage >= p.max_stage) return;
+      const CUtensorMap* m;
+      int ev;
+      unsigned target;
+      if (un.gemm == G_QKV) { m = &p.maps.an_attn; ev = EV_ANA; target = NROW_CTAS * (pass + 1); }
+      else if (un.gemm == G_O) { m = &p.maps.attn; ev = EV_ATT; target = NROW_CTAS * (pass + 1); }
+      else if (un.gemm == G_GU) { m = &p.maps.an_ffn; ev = EV_ANF; target = NROW_CTAS * (pass + 1); }
+      else { m = &p.maps.act; ev = EV_GU; target = p.n_units[G_GU] * (pass + 1); }
+      if (!wait_event(c, p.ctrl + 16 + ev, target, stage)) return;
+      ptx::fence_proxy_async_global();
+      for (int a = 0; a < un.nk; ++a, ++ait) {
+        const int slot = ait % NA;
+        if (!wait_mbar(c, b.aempty + 8 * slot, ((ait / NA) & 1) ^ 1, WAIT_A_EMPTY, stage)) return;
+        ptx::mbar_expect_tx(b.afull + 8 * slot, A_ATOM_BYTES);
+        ptx::tma_load_2d(aring + slot * A_ATOM_BYTES, m, b.afull + 8 * slot, (un.k0 + a) * KATOM, 0);
+      }
+    }
+  }
+}
+
+// Returns the number of weight atoms consumed (for the drain at exit).
+__device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t wring,
+                               uint32_t aring, const Bars& b, uint32_t tmem) {
+  const int npass = p.n_steps * p.n_layers;
+  const uint32_t idesc = ptx::umma_idesc_bf16(128, 64);
+  uint32_t it = 0, ait = 0, uit = 0;
+  for (int pass = 0; pass < npass; ++pass) {
+    for (int u = 0; u < nunits; ++u, ++uit) {
+      const Unit un = units[u];
+      const int stage = stage_of(pass, un.gemm);
+      if (stage >= p.max_stage) return it;
+      const uint32_t buf = uit & 1;
+      if (!wait_mbar(c, b.tempty + 8 * buf, ((uit >> 1) & 1) ^ 1, WAIT_T_EMPTY, stage)) return it;
+      ptx::tc_fence_after();
+      const uint32_t d = tmem + buf * 64;
+      for (int a = 0; a < un.nk; ++a, ++it, ++ait) {
+        const int ws = it % NW, as = ait % NA;
+        if (!wait_mbar(c, b.wfull + 8 * ws, (it / NW) & 1, WAIT_W_FULL, stage)) return it;
+        if (!wait_mbar(c, b.afull + 8 * as, (ait / NA) & 1, WAIT_A_FULL, stage)) return it;
+        ptx::tc_fence_after();
+        const uint64_t ad = ptx::umma_smem_desc(wring + ws * W_ATOM_BYTES);
+        const uint64_t bd = ptx::umma_smem_desc(aring + as * A_ATOM_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < KATOM / 16; ++kk)
+          ptx::umma_bf16(d, ad + 2 * kk, bd + 2 * kk, idesc, (a | kk) ? 1u : 0u);
+        ptx::umma_commit(b.wempty + 8 * ws);
+        ptx::umma_commit(b.aempty + 8 * as);
+      }
+      ptx::umma_commit(b.tfull + 8 * buf);
+    }
+  }
+  return it;
+}
+
+// Four warps (128 threads); thread r owns accumulator row r (one weight row) for all 64 token columns.
+__device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int nunits, uint8_t* smem, const Bars& b,
+                         uint32_t tmem) {
+  const int npass = p.n_steps * p.n_layers;
+  const int et = threadIdx.x - 128;          // 0..127 = accumulator row
+  const int ew = et >> 5;                    // TMEM lane quadrant of this warp (warp index % 4)
+  __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + OFF_STAGE);
+  uint32_t uit = 0;
+  for (int pass = 0; pass < npass; ++pass) {
+    for (int u = 0; u < nunits; ++u, ++uit) {
+      const Unit un = units[u];
+      const int stage = stage_of(pass, un.gemm);
+      if (stage >= p.max_stage) return;
+      const uint32_t buf = uit & 1;
+      const bool ok = wait_mbar(c, b.tfull + 8 * buf, (uit >> 1) & 1, WAIT_T_FULL, stage);
+      {  // all 128 threads agree on whether to go on
+        int any_fail;
+        asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 p, %1, 0;\nbarrier.cta.red.or.pred q, 1, 128, p;\nselp.u32 %0, 1, 0, q;\n}"
+                     : "=r"(any_fail) : "r"(ok ? 0 : 1) : "memory");
+        if (any_fail) return;
+      }
+      ptx::tc_fence_after();
+      uint32_t r[64];
+      {
+        uint32_t lo[32], hi[32];
+        const uint32_t taddr = tmem + buf * 64 + ((uint32_t)(ew * 32) << 16);
+        ptx::tmem_ld_32x32(taddr, lo);
+        ptx::tmem_ld_32x32(taddr + 32, hi);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { r[i] = lo[i]; r[32 + i] = hi[i]; }
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(b.tempty + 8 * buf);
+
+      if (un.gemm == G_O || un.gemm == G_DOWN) {
+        // split-K partial: FP32 reduction into the L2-resident accumulator [T][W]
+        float* acc = (un.gemm == G_O ? p.o_acc : p.d_acc) + un.tile * 128 + et;
+#pragma unroll
+        for (int t = 0; t < T; ++t) ptx::red_add_f32(acc + (size_t)t * W, __uint_as_float(r[t]));
+      } else {
+        // exchange BF16-rounded rows through shared memory: row et <-> row et ^ 64
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) pk[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        uint4* mine = reinterpret_cast<uint4*>(stg + et * STAGE_STRIDE);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mine[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+        ptx::named_bar_sync(1, 128);
+        const uint4* other = reinterpret_cast<const uint4*>(stg + (et ^ 64) * STAGE_STRIDE);
+        uint32_t po[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const uint4 v = other[i]; po[4 * i] = v.x; po[4 * i + 1] = v.y; po[4 * i + 2] = v.z; po[4 * i + 3] = v.w; }
+        if (un.gemm == G_GU) {
+          // rows 0..63 gate, 64..127 up of features tile*64 + (et & 63); each thread finishes half of the tokens
+          const bool is_up = et >= 64;
+          __nv_bfloat16* dst = p.act + un.tile * 64 + (et & 63);
+#pragma unroll
+          for (int t = 0; t < T; ++t) {
+            if ((t >= 25) == is_up) {
+              const float a = (t & 1) ? bf16_hi(pk[t >> 1]) : bf16_lo(pk[t >> 1]);
+              const float o2 = (t & 1) ? bf16_hi(po[t >> 1]) : bf16_lo(po[t >> 1]);
+              const float gv = is_up ? o2 : a, uv = is_up ? a : o2;
+              dst[(size_t)t * FF] = __float2bfloat16_rn(rb(gelu_tanh(gv)) * uv);
+            }
+          }
+          ptx::fence_proxy_async_global();   // act is read by the down projection's TMA
+        } else {
+          // QKV: q / k tiles pair dim d (row < 64) with dim d + 128 (row >= 64) for RoPE; v tiles are plain
+          const bool hi = et >= 64;
+          if (un.tile < 18) {
+            const bool isq = un.tile < 16;
+            const int cblk = isq ? (un.tile & 1) : (un.tile - 16);
+            const int j = cblk * 64 + (et & 63);                    // rotary index 0..127
+            const int d = j + (hi ? 128 : 0);
+            __nv_bfloat16* dst = isq ? p.q + (un.tile >> 1) * HD + d : p.k + d;
+            const int ld = isq ? QD : HD;
+            const uint32_t* rope = p.rope + j;
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+              const uint32_t cs = rope[t * (HD / 2)];
+              const float x = (t & 1) ? bf16_hi(pk[t >> 1]) : bf16_lo(pk[t >> 1]);
+              const float y = (t & 1) ? bf16_hi(po[t >> 1]) : bf16_lo(po[t >> 1]);
+              const float rot = hi ? y : -y;                       // rotate_half: (-x2, x1)
+              dst[(size_t)t * ld] = __float2bfloat16_rn(rb(x * bf16_lo(cs)) + rb(rot * bf16_hi(cs)));
+            }
+          } else {
+            __nv_bfloat16* dst = p.v + (un.tile - 18) * 128 + et;
+#pragma unroll
+            for (int t = 0; t < T; ++t)
+              dst[(size_t)t * HD] = __float2bfloat16_rn((t & 1) ? bf16_hi(pk[t >> 1]) : bf16_lo(pk[t >> 1]));
+          }
+        }
+      }
+      ptx::named_bar_sync(1, 128);
+      if (et == 0) {
+        const int ev = un.gemm == G_QKV ? EV_QKV : un.gemm == G_O ? EV_O : un.gemm == G_GU ? EV_GU : EV_DOWN;
+        signal_event(p.ctrl + 16 + ev);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- row CTA main loop
+__device__ bool cta_wait_event(const Params& p, const Ctx& c, int ev, unsigned target, int stage) {
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = wait_event(c, p.ctrl + 16 + ev, target, stage) ? 1 : 0;
+  __syncthreads();
+  const int ok = ok_flag;
+  __syncthreads();
+  return ok != 0;
+}
+
+__device__ void cta_signal(const Params& p, int ev) {
+  __syncthreads();
+  if (threadIdx.x == 0) signal_event(p.ctrl + 16 + ev);
+}
+
+__device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit) {
+  const int npass = p.n_steps * p.n_layers;
+  const int npc = (p.prefix + 63) / 64;
+  const bool stamp = p.stamps != nullptr && unit == 0 && threadIdx.x == 0;
+  for (int pass = 0; pass < npass; ++pass) {
+    const int layer = pass % p.n_layers, step = pass / p.n_layers;
+    const int sbase = 6 + pass * NSTAGE;
+    // ---- attention
+    if (pass * NSTAGE + ST_ATT >= p.max_stage) return;
+    AttChunkIssue issue{p, smem, layer, npc};
+    issue(0, 0);                       // prefix chunks do not depend on this layer's QKV: fetch before waiting
+    if (npc >= 2) issue(1, 1);
+    if (!cta_wait_event(p, c, EV_QKV, p.n_units[G_QKV] * (pass + 1), pass * NSTAGE + ST_ATT)) return;
+    if (stamp && sbase + ST_QKV < PI05_NUM_STAMPS) p.stamps[sbase + ST_QKV] = globaltimer();
+    if (npc < 2) issue(1, 1);          // chunk 1 is the suffix chunk
+    {
+      const __nv_bfloat16* qsrc = p.q + (size_t)unit * 2 * QD;
+      for (int idx = threadIdx.x; idx < 16 * 32; idx += THREADS) {
+        const int r = idx >> 5, cidx = idx & 31;
+        ptx::cp_async_16(ptx::smem_u32(smem + OFF_QS + r * (KV_STRIDE * 2) + cidx * 16), qsrc + (size_t)r * HD + cidx * 8);
+      }
+      ptx::cp_async_commit();
+      ptx::cp_async_wait<0>();
+      __syncthreads();
+    }
+    attention_unit(p, smem, unit, issue);
+    cta_signal(p, EV_ATT);
+    if (stamp && sbase + ST_ATT < PI05_NUM_STAMPS) p.stamps[sbase + ST_ATT] = globaltimer();
+    // ---- residual + norm after the O projection
+    if (pass * NSTAGE + ST_RATT >= p.max_stage) return;
+    if (!cta_wait_event(p, c, EV_O, p.n_units[G_O] * (pass + 1), pass * NSTAGE + ST_RATT)) return;
+    if (stamp && sbase + ST_O < PI05_NUM_STAMPS) p.stamps[sbase + ST_O] = globaltimer();
+    row_op(p, smem, unit, ROW_ATT, step, layer);
+    ptx::fence_proxy_async_global();
+    cta_signal(p, EV_ANF);
+    if (stamp && sbase + ST_RATT < PI05_NUM_STAMPS) p.stamps[sbase + ST_RATT] = globaltimer();
+    // ---- residual + norm (or step tail) after the down projection
+    if (pass * NSTAGE + ST_RFFN >= p.max_stage) return;
+    if (!cta_wait_event(p, c, EV_DOWN, p.n_units[G_DOWN] * (pass + 1), pass * NSTAGE + ST_RFFN)) return;
+    if (stamp && sbase + ST_DOWN < PI05_NUM_STAMPS) p.stamps[sbase + ST_DOWN] = globaltimer();
+    row_op(p, smem, unit, ROW_FFN, step, layer);
+    ptx::fence_proxy_async_global();
+    cta_signal(p, EV_ANA);
+    if (stamp && sbase + ST_RFFN < PI05_NUM_STAMPS) p.stamps[sbase + ST_RFFN] = globaltimer();
+  }
+}
+
+// ------------------------------------------------------------------------------------------- the kernel
+__global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_constant__ Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int cta = blockIdx.x, ncta = gridDim.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool is_gemm = cta < p.n_gemm_ctas;
+  const Ctx c{p.ctrl, p.wait_limit, cta};
+  const bool stamp = p.stamps != nullptr && cta == p.n_gemm_ctas && tid == 0;
+  if (stamp) p.stamps[0] = globaltimer();
+
+  __shared__ uint32_t s_tmem;
+  __shared__ uint32_t s_issued, s_consumed;
+  Bars b;
+  {
+    const uint32_t base = ptx::smem_u32(smem + OFF_BARS);
+    b.wfull = base; b.wempty = base + 8 * NW; b.afull = base + 16 * NW; b.aempty = b.afull + 8 * NA;
+    b.tfull = b.aempty + 8 * NA; b.tempty = b.tfull + 16;
+  }
+  const uint32_t wring = ptx::smem_u32(smem + OFF_WRING), aring = ptx::smem_u32(smem + OFF_ARING);
+  const Unit* units = p.sched + (size_t)cta * MAX_UNITS;
+  const int nunits = is_gemm ? p.sched_n[cta] : 0;
+
+  if (tid == 0) {
+    s_issued = 0; s_consumed = 0;
+    for (int i = 0; i < NW; ++i) { ptx::mbar_init(b.wfull + 8 * i, 1); ptx::mbar_init(b.wempty + 8 * i, 1); }
+    for (int i = 0; i < NA; ++i) { ptx::mbar_init(b.afull + 8 * i, 1); ptx::mbar_init(b.aempty + 8 * i, 1); }
+    for (int i = 0; i < 2; ++i) { ptx::mbar_init(b.tfull + 8 * i, 1); ptx::mbar_init(b.tempty + 8 * i, 128); }
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_shared();
+  }
+  if (is_gemm && warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&s_tmem), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = s_tmem;
+
+  // The first ring of weights does not depend on anything: start streaming before the prologue.
+  Producer prod{0, 0, 0, 0u, false};
+  uint64_t policy = 0;
+  if (is_gemm && warp == 0 && lane == 0) {
+    policy = ptx::policy_evict_first();
+    weight_producer(p, c, units, nunits, wring, b, prod, NW, policy);
+  }
+
+  // ---------------- prologue: tables, time MLP, all modulation rows (FP32 weights streamed once)
+  bool ok = true;
+  prologue_tables(p, cta, ncta);
+  ok = grid_event(p, c, EV_P0, ncta);
+  if (stamp) p.stamps[1] = globaltimer();
+  if (ok) { matvec10<0>(p, p.temb, smem, cta, ncta); ok = grid_event(p, c, EV_P1, ncta); }
+  if (stamp) p.stamps[2] = globaltimer();
+  if (ok) { matvec10<1>(p, p.hid, smem, cta, ncta); ok = grid_event(p, c, EV_P2, ncta); }
+  if (stamp) p.stamps[3] = globaltimer();
+  if (ok) { matvec10<2>(p, p.cond, smem, cta, ncta); ok = grid_event(p, c, EV_P3, ncta); }
+  if (stamp) p.stamps[4] = globaltimer();
+
+  if (ok) {
+    if (is_gemm) {
+      if (warp == 0) {
+        if (lane == 0) {
+          weight_producer(p, c, units, nunits, wring, b, prod, 0xffffffffu, policy);
+          s_issued = prod.it;
+        }
+      } else if (warp == 1) {
+        if (lane == 0) s_consumed = mma_issuer(p, c, units, nunits, wring, aring, b, tmem);
+      } else if (warp == 2) {
+        if (lane == 0) act_producer(p, c, units, nunits, aring, b);
+      } else if (warp >= 4) {
+        epilogue(p, c, units, nunits, smem, b, tmem);
+      }
+    } else {
+      const int unit = cta - p.n_gemm_ctas;
+      row_op(p, smem, unit, ROW_INIT, 0, 0);
+      ptx::fence_proxy_async_global();
+      cta_signal(p, EV_ANA);
+      if (stamp) p.stamps[5] = globaltimer();
+      row_cta(p, c, smem, unit);
+    }
+  } else if (is_gemm && warp == 0 && lane == 0) {
+    s_issued = prod.it;
+  }
+
+  // ---------------- teardown: drain loads still in flight, free TMEM, last CTA out clears the counters
+  __syncthreads();
+  if (is_gemm && warp == 0 && lane == 0) {
+    const uint32_t issued = s_issued, consumed = s_consumed;
+    for (uint32_t it = consumed; it < issued; ++it) {
+      const long long t0 = clock64();
+      while (!ptx::mbar_try_wait(b.wfull + 8 * (it % NW), (it / NW) & 1)) {
+        if (clock64() - t0 > c.limit) { report_timeout(c, WAIT_DRAIN, 0); break; }
+      }
+    }
+  }
+  __syncthreads();
+  if (is_gemm && warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, TMEM_COLS);
+  }
+  if (tid == 0) {
+    __threadfence();
+    const unsigned prev = atomicAdd(p.ctrl + 16 + EV_EXIT, 1u);
+    if (prev == (unsigned)ncta - 1) {
+      __threadfence();
+      for (int e = 0; e < NEVENTS; ++e) p.ctrl[16 + e] = 0u;
+      __threadfence();
+    }
+  }
+}
+
+// =========================================================================================== host side
+struct Region { const char* name; size_t off, bytes; };
+
+}  // namespace
+
+struct pi05_engine {
+  int device = 0;
+  int sms = 0;
+  int grid = 0;
+  int n_gemm = 0;
+  int max_prefix = 0;
+  int prefix = 0;
+  bool bound = false;
+  const void* inputs[PI05_NUM_INPUTS] = {};
+  void* actions = nullptr;
+  uint8_t* ws = nullptr;
+  size_t ws_bytes = 0;
+  std::vector<Region> regions;
+  std::vector<Unit> sched;       // [grid][MAX_UNITS]
+  std::vector<int> sched_n;
+  int n_units[4] = {0, 0, 0, 0};
+  TMaps maps;
+  int max_stage = 0x7fffffff;
+  long long wait_limit = 4000000000ll;    // ~2 s of SM clocks
+  unsigned long long launches = 0;
+  std::string config;
+  std::string last_error;
+};
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    ok = cudaSetDevice(dev) == cudaSuccess;
+  }
+  ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+int fail_cuda(pi05_engine* h, const char* what, cudaError_t e) {
+  h->last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return PI05_ERR_CUDA;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+void build_layout(pi05_engine* h) {
+  size_t off = 0;
+  auto add = [&](const char* name, size_t bytes) {
+    h->regions.push_back({name, off, bytes});
+    off = align_up(off + bytes, 256);
+  };
+  add("ctrl", 1024);
+  add("temb", (size_t)NS * W * 4);
+  add("hid", (size_t)NS * W * 4);
+  add("cond", (size_t)NS * W * 4);
+  add("mod", (size_t)NS * NNORM * MODW * 4);
+  add("rope", (size_t)T * (HD / 2) * 4);
+  add("x", (size_t)T * ADIM * 4);
+  add("h", (size_t)T * W * 2);
+  add("an_attn", (size_t)T * W * 2);
+  add("an_ffn", (size_t)T * W * 2);
+  add("q", (size_t)T * QD * 2);
+  add("k", (size_t)T * HD * 2);
+  add("v", (size_t)T * HD * 2);
+  add("attn", (size_t)T * QD * 2);
+  add("o_acc", (size_t)T * W * 4);
+  add("d_acc", (size_t)T * W * 4);
+  add("act", (size_t)T * FF * 2);
+  add("sched", (size_t)h->grid * MAX_UNITS * sizeof(Unit));
+  add("sched_n", (size_t)h->grid * sizeof(int));
+  h->ws_bytes = off;
+}
+
+const Region* find_region(const pi05_engine* h, const char* name) {
+  for (const Region& r : h->regions)
+    if (strcmp(r.name, name) == 0) return &r;
+  return nullptr;
+}
+
+template <typename Tp>
+Tp* region_ptr(const pi05_engine* h, const char* name) {
+  return reinterpret_cast<Tp*>(h->ws + find_region(h, name)->off);
+}
+
+// Static work schedule: which CTA runs which 128-row weight tile over which range of 64-wide K atoms.
+//   gate/up: 64 tiles (64 gate rows + the matching 64 up rows), full K, one per CTA 0..63
+//   QKV:     20 tiles (16 q, 2 k, 2 v), full K, one per CTA 64..83
+//   O, down: 8 row tiles each, K split in contiguous runs over the remaining GEMM CTAs
+bool build_schedule(pi05_engine* h) {
+  const int ng = h->n_gemm;
+  if (ng < 64 + 20 + 8) return false;
+  h->sched.assign((size_t)h->grid * MAX_UNITS, Unit{0, 0, 0, 0});
+  h->sched_n.assign(h->grid, 0);
+  std::vector<std::vector<Unit>> per(h->grid);
+  for (int u = 0; u < 20; ++u) per[64 + u].push_back(Unit{G_QKV, u, 0, W / KATOM});
+  const int od0 = 84, nod = ng - od0;
+  auto split = [&](int gemm, int tiles, int atoms_per_tile) {
+    const int total = tiles * atoms_per_tile;
+    for (int j = 0; j < nod; ++j) {
+      int a0 = (int)((long long)total * j / nod), a1 = (int)((long long)total * (j + 1) / nod);
+      while (a0 < a1) {
+        const int tile = a0 / atoms_per_tile, k0 = a0 % atoms_per_tile;
+        const int n = std::min(a1 - a0, atoms_per_tile - k0);
+        per[od0 + j].push_back(Unit{gemm, tile, k0, n});
+        a0 += n;
+      }
+    }
+  };
+  split(G_O, W / 128, QD / KATOM);
+  for (int u = 0; u < 64; ++u) per[u].push_back(Unit{G_GU, u, 0, W / KATOM});
+  split(G_DOWN, W / 128, FF / KATOM);
+  for (int g = 0; g < 4; ++g) h->n_units[g] = 0;
+  for (int ctaid = 0; ctaid < h->grid; ++ctaid) {
+    if ((int)per[ctaid].size() > MAX_UNITS) return false;
+    h->sched_n[ctaid] = (int)per[ctaid].size();
+    for (size_t i = 0; i < per[ctaid].size(); ++i) {
+      h->sched[(size_t)ctaid * MAX_UNITS + i] = per[ctaid][i];
+      h->n_units[per[ctaid][i].gemm]++;
+    }
+  }
+  return true;
+}
+
+int encode_2d(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) { h->last_error = "cuTensorMapEncodeTiled is not available from this driver"; return PI05_ERR_CUDA; }
+  cuuint64_t dims[2] = {inner, rows};
+  cuuint64_t strides[1] = {inner * 2};
+  cuuint32_t box[2] = {KATOM, 64};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    h->last_error = "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r);
+    return PI05_ERR_CUDA;
+  }
+  return PI05_OK;
+}
+
+bool valid_handle(pi05_handle_t h) { return h != nullptr; }
+
+}  // namespace
+
+// =========================================================================================== C ABI
+extern "C" {
+
+const char* pi05_error_string(int code) {
+  switch (code) {
+    case PI05_OK: return "ok";
+    case PI05_ERR_ARGUMENT: return "invalid argument";
+    case PI05_ERR_UNSUPPORTED: return "unsupported configuration";
+    case PI05_ERR_CUDA: return "CUDA call failed";
+    case PI05_ERR_NOT_BOUND: return "engine has no bound inputs";
+    case PI05_ERR_DEVICE_TIMEOUT: return "a device-side wait timed out";
+    case PI05_ERR_NO_DEVICE: return "no usable sm_100 device";
+    default: return "unknown error";
+  }
+}
+
+const char* pi05_last_error(pi05_handle_t h) { return valid_handle(h) ? h->last_error.c_str() : "bad handle"; }
+
+int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_size, pi05_handle_t* out) {
+  if (!out) return PI05_ERR_ARGUMENT;
+  *out = nullptr;
+  if (device < 0 || max_prefix < 1 || max_prefix > 4096 || max_batch < 1 || tp_size < 1 || tp_rank < 0 ||
+      tp_rank >= tp_size)
+    return PI05_ERR_ARGUMENT;
+  if (max_batch != 1 || tp_size != 1) return PI05_ERR_UNSUPPORTED;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) { cudaGetLastError(); return PI05_ERR_NO_DEVICE; }
+  if (device >= ndev) return PI05_ERR_ARGUMENT;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { cudaGetLastError(); return PI05_ERR_NO_DEVICE; }
+  if (prop.major != 10) return PI05_ERR_NO_DEVICE;
+  pi05_engine* h = new (std::nothrow) pi05_engine();
+  if (!h) return PI05_ERR_ARGUMENT;
+  h->device = device;
+  h->sms = prop.multiProcessorCount;
+  h->grid = h->sms;
+  h->n_gemm = h->grid - NROW_CTAS;
+  h->max_prefix = max_prefix;
+  if (!build_schedule(h)) { delete h; return PI05_ERR_UNSUPPORTED; }
+  build_layout(h);
+  DeviceGuard guard(device);
+  if (!guard.ok) { delete h; return PI05_ERR_CUDA; }
+  cudaError_t e = cudaFuncSetAttribute(pi05_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) { cudaGetLastError(); delete h; return PI05_ERR_CUDA; }
+  int coop = 0, blocks = 0;
+  cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device);
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, pi05_chunk_kernel, THREADS, SMEM_BYTES);
+  if (e != cudaSuccess || blocks < 1 || !coop) { cudaGetLastError(); delete h; return PI05_ERR_UNSUPPORTED; }
+  char buf[1024];
+  snprintf(buf, sizeof buf,
+           "{\"kernel\": \"pi05_chunk_kernel\", \"arch\": \"sm_100a\", \"launches_per_chunk\": 1, \"grid\": %d, "
+           "\"threads\": %d, \"smem_bytes\": %d, \"gemm_ctas\": %d, \"row_ctas\": %d, \"weight_ring\": %d, "
+           "\"act_ring\": %d, \"units\": {\"qkv\": %d, \"o\": %d, \"gate_up\": %d, \"down\": %d}, "
+           "\"mma\": \"tcgen05 cta_group::1 M128 N64 K16 bf16\", \"sync\": \"device-scope counters, bounded waits\"}",
+           h->grid, THREADS, SMEM_BYTES, h->n_gemm, NROW_CTAS, NW, NA, h->n_units[0], h->n_units[1], h->n_units[2],
+           h->n_units[3]);
+  h->config = buf;
+  *out = h;
+  return PI05_OK;
+}
+
+int pi05_workspace_bytes(pi05_handle_t h, size_t* bytes) {
+  if (!valid_handle(h) || !bytes) return PI05_ERR_ARGUMENT;
+  *bytes = h->ws_bytes;
+  return PI05_OK;
+}
+
+int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, int batch, void* actions,
+              void* workspace, size_t workspace_bytes) {
+  if (!valid_handle(h) || !inputs || !actions || !workspace) return PI05_ERR_ARGUMENT;
+  if (batch != 1) return PI05_ERR_UNSUPPORTED;
+  if (prefix_len < 1 || prefix_len > h->max_prefix) return PI05_ERR_ARGUMENT;
+  if (workspace_bytes < h->ws_bytes) { h->last_error = "workspace too small"; return PI05_ERR_ARGUMENT; }
+  for (int i = 0; i < PI05_NUM_INPUTS; ++i) {
+    if (!inputs[i]) { h->last_error = "null input pointer"; return PI05_ERR_ARGUMENT; }
+    if (i != 24 && (reinterpret_cast<uintptr_t>(inputs[i]) & 15)) {
+      h->last_error = "input " + std::to_string(i) + " is not 16-byte aligned";
+      return PI05_ERR_ARGUMENT;
+    }
+  }
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(actions) & 15)) {
+    h->last_error = "workspace must be 256-byte and actions 16-byte aligned";
+    return PI05_ERR_ARGUMENT;
+  }
+  DeviceGuard guard(h->device);
+  if (!guard.ok) return PI05_ERR_CUDA;
+  h->bound = false;
+  for (int i = 0; i < PI05_NUM_INPUTS; ++i) h->inputs[i] = inputs[i];
+  h->actions = actions;
+  h->ws = static_cast<uint8_t*>(workspace);
+  h->prefix = prefix_len;
+  cudaError_t e = cudaMemset(workspace, 0, h->ws_bytes);
+  if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(workspace)", e);
+  e = cudaMemcpy(region_ptr<void>(h, "sched"), h->sched.data(), h->sched.size() * sizeof(Unit), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return fail_cuda(h, "cudaMemcpy(schedule)", e);
+  e = cudaMemcpy(region_ptr<void>(h, "sched_n"), h->sched_n.data(), h->sched_n.size() * sizeof(int), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return fail_cuda(h, "cudaMemcpy(schedule)", e);
+  int rc;
+  if ((rc = encode_2d(h, &h->maps.wq, inputs[8], W, (uint64_t)NL * QD))) return rc;
+  if ((rc = encode_2d(h, &h->maps.wk, inputs[9], W, (uint64_t)NL * HD))) return rc;
+  if ((rc = encode_2d(h, &h->maps.wv, inputs[10], W, (uint64_t)NL * HD))) return rc;
+  if ((rc = encode_2d(h, &h->maps.wo, inputs[11], QD, (uint64_t)NL * W))) return rc;
+  if ((rc = encode_2d(h, &h->maps.wg, inputs[12], W, (uint64_t)NL * FF))) return rc;
+  if ((rc = encode_2d(h, &h->maps.wu, inputs[13], W, (uint64_t)NL * FF))) return rc;
+  if ((rc = encode_2d(h, &h->maps.wd, inputs[14], FF, (uint64_t)NL * W))) return rc;
+  if ((rc = encode_2d(h, &h->maps.an_attn, region_ptr<void>(h, "an_attn"), W, T))) return rc;
+  if ((rc = encode_2d(h, &h->maps.an_ffn, region_ptr<void>(h, "an_ffn"), W, T))) return rc;
+  if ((rc = encode_2d(h, &h->maps.attn, region_ptr<void>(h, "attn"), QD, T))) return rc;
+  if ((rc = encode_2d(h, &h->maps.act, region_ptr<void>(h, "act"), FF, T))) return rc;
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceSynchronize", e);
+  h->bound = true;
+  return PI05_OK;
+}
+
+int pi05_refresh(pi05_handle_t h) {
+  if (!valid_handle(h)) return PI05_ERR_ARGUMENT;
+  return h->bound ? PI05_OK : PI05_ERR_NOT_BOUND;
+}
+
+int pi05_debug(pi05_handle_t h, int max_stage, long long wait_limit_cycles) {
+  if (!valid_handle(h)) return PI05_ERR_ARGUMENT;
+  h->max_stage = max_stage < 0 ? 0x7fffffff : max_stage;
+  if (wait_limit_cycles > 0) h->wait_limit = wait_limit_cycles;
+  return PI05_OK;
+}
+
+int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsigned long long* stamps) {
+  if (!valid_handle(h)) return PI05_ERR_ARGUMENT;
+  if (!h->bound) return PI05_ERR_NOT_BOUND;
+  if (n_steps < 1 || n_steps > NS || n_layers < 1 || n_layers > NL) return PI05_ERR_ARGUMENT;
+  DeviceGuard guard(h->device);
+  if (!guard.ok) return PI05_ERR_CUDA;
+  Params p;
+  memset(&p, 0, sizeof p);
+  p.maps = h->maps;
+  const void* const* in = h->inputs;
+  p.ain_w = (const float*)in[0]; p.ain_b = (const float*)in[1];
+  p.tin_w = (const float*)in[2]; p.tin_b = (const float*)in[3];
+  p.tout_w = (const float*)in[4]; p.tout_b = (const float*)in[5];
+  p.aout_w = (const float*)in[6]; p.aout_b = (const float*)in[7];
+  p.attn_nw = (const float*)in[15]; p.attn_nb = (const float*)in[16];
+  p.ffn_nw = (const float*)in[17]; p.ffn_nb = (const float*)in[18];
+  p.fin_nw = (const float*)in[19]; p.fin_nb = (const float*)in[20];
+  p.noise = (const float*)in[21];
+  p.prefix_k = (const __nv_bfloat16*)in[22]; p.prefix_v = (const __nv_bfloat16*)in[23];
+  p.prefix_mask = (const uint8_t*)in[24];
+  p.actions = (float*)h->actions;
+  p.ctrl = region_ptr<unsigned int>(h, "ctrl");
+  p.temb = region_ptr<float>(h, "temb"); p.hid = region_ptr<float>(h, "hid"); p.cond = region_ptr<float>(h, "cond");
+  p.mod = region_ptr<float>(h, "mod"); p.x = region_ptr<float>(h, "x");
+  p.o_acc = region_ptr<float>(h, "o_acc"); p.d_acc = region_ptr<float>(h, "d_acc");
+  p.rope = region_ptr<uint32_t>(h, "rope");
+  p.h = region_ptr<__nv_bfloat16>(h, "h"); p.an_attn = region_ptr<__nv_bfloat16>(h, "an_attn");
+  p.an_ffn = region_ptr<__nv_bfloat16>(h, "an_ffn"); p.q = region_ptr<__nv_bfloat16>(h, "q");
+  p.k = region_ptr<__nv_bfloat16>(h, "k"); p.v = region_ptr<__nv_bfloat16>(h, "v");
+  p.attn = region_ptr<__nv_bfloat16>(h, "attn"); p.act = region_ptr<__nv_bfloat16>(h, "act");
+  p.sched = region_ptr<Unit>(h, "sched"); p.sched_n = region_ptr<int>(h, "sched_n");
+  p.stamps = stamps;
+  p.wait_limit = h->wait_limit;
+  p.prefix = h->prefix; p.n_steps = n_steps; p.n_layers = n_layers; p.max_stage = h->max_stage;
+  p.n_gemm_ctas = h->n_gemm;
+  for (int g = 0; g < 4; ++g) p.n_units[g] = h->n_units[g];
+  const double dt = -1.0 / NS;
+  for (int s = 0; s < NS; ++s) p.t_steps[s] = (float)(1.0 + s * dt);
+  p.dt = (float)dt;
+  void* args[] = {&p};
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)pi05_chunk_kernel, dim3(h->grid), dim3(THREADS), args,
+                                              SMEM_BYTES, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail_cuda(h, "cudaLaunchCooperativeKernel", e);
+  h->launches++;
+  return PI05_OK;
+}
+
+int pi05_status(pi05_handle_t h, int* code, int* where) {
+  if (!valid_handle(h) || !code || !where) return PI05_ERR_ARGUMENT;
+  if (!h->ws) return PI05_ERR_NOT_BOUND;
+  DeviceGuard guard(h->device);
+  if (!guard.ok) return PI05_ERR_CUDA;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceSynchronize", e);
+  unsigned int st[2] = {0, 0};
+  e = cudaMemcpy(st, h->ws, sizeof st, cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail_cuda(h, "cudaMemcpy(status)", e);
+  *code = (int)st[0];
+  *where = (int)st[1];
+  if (st[0]) {
+    e = cudaMemset(h->ws, 0, 1024);   // status and every counter: the next launch starts clean
+    if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(status)", e);
+    return PI05_ERR_DEVICE_TIMEOUT;
+  }
+  return PI05_OK;
+}
+
+int pi05_workspace_region(pi05_handle_t h, const char* name, size_t* offset, size_t* bytes) {
+  if (!valid_handle(h) || !name || !offset || !bytes) return PI05_ERR_ARGUMENT;
+  const Region* r = find_region(h, name);
+  if (!r) return PI05_ERR_ARGUMENT;
+  *offset = r->off;
+  *bytes = r->bytes;
+  return PI05_OK;
+}
+
+const char* pi05_config_json(pi05_handle_t h) { return valid_handle(h) ? h->config.c_str() : "{}"; }
+
+int pi05_launch_count(pi05_handle_t h, unsigned long long* count) {
+  if (!valid_handle(h) || !count) return PI05_ERR_ARGUMENT;
+  *count = h->launches;
+  return PI05_OK;
+}
+
+int pi05_destroy(pi05_handle_t h) {
+  if (!valid_handle(h)) return PI05_ERR_ARGUMENT;
+  delete h;
+  return PI05_OK;
+}
+
+}  // extern "C"
