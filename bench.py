@@ -1,0 +1,281 @@
+"""Benchmark of the pi0.5 action-chunk engine on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 50 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the eager CPU path on the box's host cores
+
+One "step" is one whole action chunk (10 Euler steps x 18 layers, B=1, prefix 128) = one kernel launch.
+The L2 is flushed (a 2x-L2 zero fill) before every timed chunk and each chunk is timed with CUDA events on
+the launching stream, as the reference harness does for its "isolated" number (bench.py:259-293 there).
+With N > 1 every rank runs its own observation on its own GPU with replicated weights and no collective in
+the data path; the reported time is the maximum over ranks.  Rank 0 prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from pi05_megakernel_b200 import fixture as FX  # noqa: E402
+
+METRIC = "action chunks/sec, whole box (B=1 per GPU, prefix 128, L2 flushed before every chunk)"
+UNIT = "chunks/s"
+SOTA_GRAPH_MS = 6.73      # the reference's best published arm on one B200 (README.md:24 there)
+HBM_NOMINAL = 8.0e12
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def ncu_traffic() -> float | None:
+    """DRAM bytes per launch from the committed ncu summary (None until one exists)."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get("dram_bytes_per_launch")
+    return None
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle sampling during the timed region."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_chunks_per_sec(geo, inputs_cpu, runs: int) -> tuple[float, int]:
+    """The eager BF16 chunk of the CPU oracle (the restatement of reference/pi05.py::reference)."""
+    from oracle import pi05_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ogeo = O.Geo(prefix=geo.prefix)
+    O.chunk(inputs_cpu, ogeo, False, 1, 2)      # warm the thread pool
+    t0 = time.perf_counter()
+    for _ in range(runs):
+        O.chunk(inputs_cpu, ogeo, False)
+    return runs / (time.perf_counter() - t0), torch.get_num_threads()
+
+
+def run_reference(args, rank: int) -> None:
+    if rank != 0:
+        return
+    geo = FX.Geometry(prefix=args.prefix)
+    cpu = FX.make_inputs(geo, FX.SEEDS[0], "cpu")
+    from oracle import pi05_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ogeo = O.Geo(prefix=geo.prefix)
+    steps, warm = max(1, min(args.steps, 20)), max(1, min(args.warmup, 2))
+    for _ in range(warm):
+        O.chunk(cpu, ogeo, False)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.chunk(cpu, ogeo, False)
+    dt = (time.perf_counter() - t0) / steps
+    value = 1.0 / dt
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"pi0.5 action chunk, B=1, prefix {geo.prefix}, 10 steps x 18 layers "
+                               "(eager CPU path, BF16 rounding schedule of the reference)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{steps} whole chunks (each step is one full chunk)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--prefix", type=int, default=128)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return 0
+    warmup = max(3, args.warmup)
+
+    import torch.distributed as dist
+    from pi05_megakernel_b200.arm import Pi05Arm
+    dist_on = world > 1
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if dist_on:
+        dist.init_process_group("nccl", device_id=device)
+
+    geo = FX.Geometry(prefix=args.prefix)
+    weights = FX.make_weights(geo, FX.SEEDS[0])
+    obs = FX.make_observation(geo, FX.SEEDS[0] + 1000 * rank)        # every GPU: its own observation
+    cpu = {k: {**weights, **obs}[k] for k in FX.ORDER}
+    dev = {k: v.to(device) for k, v in cpu.items()}
+    arm = Pi05Arm(geo, "b200", str(device))
+    arm.bind(dev)
+    l2 = torch.cuda.get_device_properties(device).L2_cache_size
+    flush = torch.empty(2 * l2, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream(device)
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if dist_on:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def timed(k: int) -> list[float]:
+        out = []
+        for _ in range(k):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            arm.launch()
+            b.record(stream)
+            out.append((a, b))
+        torch.cuda.synchronize(device)
+        return [a.elapsed_time(b) for a, b in out]
+
+    # ---- device-resident inputs: `value`
+    timed(warmup)
+    arm.status()
+    launches0 = arm.launch_count()
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    samples = timed(args.steps)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    launches = arm.launch_count() - launches0
+    arm.status()
+    ms_step = sum(samples) / len(samples)
+
+    # ---- end to end through the arm with host buffers: pinned observation -> device, chunk, actions -> host
+    obs_names = ("noise", "prefix_k", "prefix_v", "prefix_mask")
+    pinned = {k: cpu[k].pin_memory() for k in obs_names}
+    host_out = torch.empty((geo.horizon, geo.action_dim), dtype=torch.float32).pin_memory()
+    h2d = sum(pinned[k].numel() * pinned[k].element_size() for k in obs_names)
+    d2h = host_out.numel() * 4
+
+    def e2e_step():
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for k in obs_names:
+            dev[k].copy_(pinned[k], non_blocking=True)
+        arm.launch()
+        host_out.copy_(arm.outputs()["actions"], non_blocking=True)
+        b.record(stream)
+        b.synchronize()
+        return a.elapsed_time(b)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_ms = [e2e_step() for _ in range(args.steps)]
+    barrier()
+    e2e_step_ms = sum(e2e_ms) / len(e2e_ms)
+
+    if dist_on:
+        t = torch.tensor([ms_step, e2e_step_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, e2e_step_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peak_gbs, peak_kind = measured_peaks()
+        floor = FX.sol(geo)
+        alg_bytes = floor["bytes_restream"]
+        achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": world * 1e3 / ms_step, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": (1e3 / ms_step) / (1e3 / SOTA_GRAPH_MS) if world == 1 else None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"pi0.5 action chunk, B=1 per GPU, prefix {geo.prefix}, 10 Euler steps x 18 "
+                                   "Gemma-300M expert layers, BF16 weights and prefix K/V, FP32 time MLP / "
+                                   "modulation; one persistent kernel launch per chunk",
+                       "l2": "flushed before every timed chunk (2x L2 zero fill)",
+                       "parallelism": f"dp{world} (independent observations, replicated weights, no collective)",
+                       "engine": arm.config},
+            "ms_per_chunk": ms_step, "ms_per_chunk_median": statistics.median(samples),
+            "x_hbm_floor_nominal": ms_step / (alg_bytes / HBM_NOMINAL * 1e3),
+            "x_hbm_floor_measured": ms_step / (alg_bytes / (peak_gbs * 1e9) * 1e3),
+            "vs_baseline_note": f"value / (1000 / {SOTA_GRAPH_MS} ms), the reference's published sota-graph arm on one B200",
+            "clocks": clocks,
+            "e2e": {"value": world * 1e3 / e2e_step_ms, "unit": UNIT, "ms_per_chunk": e2e_step_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                         "frac": achieved / peak_gbs, "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_launch": alg_bytes, "traffic": ncu_traffic()},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cps, cores = cpu_chunks_per_sec(geo, cpu, 5)
+            line["cpu_baseline"] = {"value": cps, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": "5 whole chunks of the same workload (eager BF16 schedule)"}
+        print(json.dumps(line), flush=True)
+    arm.close()
+    if dist_on:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

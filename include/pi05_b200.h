@@ -69,10 +69,11 @@ int pi05_refresh(pi05_handle_t h);
 /* Replaces launch() (mk/pi05_mk.cu:3523-3620): one whole action chunk, asynchronous on `stream` (a cudaStream_t;
  * NULL = default stream).  n_steps <= 10 Euler steps and n_layers <= 18 expert layers are run (dt stays -0.1);
  * the graded chunk is (10, 18).  stamps, if non-NULL, is a device buffer of PI05_NUM_STAMPS uint64 that
- * receives globaltimer values at stage boundaries of the first pass (the reference's tstamp tensor,
- * mk/pi05_mk.cu:351). */
+ * receives globaltimer values at stage boundaries of the first layer passes and, from three GEMM CTAs, at the
+ * points of their pipeline in the second pass (the reference's tstamp tensor, mk/pi05_mk.cu:351).  The caller
+ * zeroes it. */
 int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsigned long long* stamps);
-#define PI05_NUM_STAMPS 64
+#define PI05_NUM_STAMPS 256
 
 /* Replaces fg_timeouts()/att_timeouts() (mk/pi05_mk.cu:3505-3520): synchronises the device and reads the status
  * word the kernel writes when a bounded wait gives up.  code = 0 when the last launches completed; otherwise
@@ -86,8 +87,21 @@ int pi05_workspace_region(pi05_handle_t h, const char* name, size_t* offset, siz
 
 /* Debug control: run only the first max_stage stages after the prologue (a stage is one of the seven
  * per-layer steps QKV, attention, O, residual+norm, gate/up, down, residual+norm); negative = run everything.
- * wait_limit_cycles > 0 overrides the bound of every device-side wait. */
-int pi05_debug(pi05_handle_t h, int max_stage, long long wait_limit_cycles);
+ * wait_limit_cycles > 0 overrides the bound (in SM clock cycles) of every device-side wait.  drop_event >= 0
+ * makes the row CTAs skip that stage-completion signal (PI05_EVENT_*), so that the waits on it run out: the
+ * way to exercise the time-out path without stalling a GPU; negative = signal everything. */
+int pi05_debug(pi05_handle_t h, int max_stage, long long wait_limit_cycles, int drop_event);
+#define PI05_EVENT_ATTENTION_DONE 6
+#define PI05_EVENT_FFN_NORM_READY 8
+/* pi05_status codes: which kind of wait gave up */
+#define PI05_WAIT_WEIGHT_SLOT 1
+#define PI05_WAIT_WEIGHT_DATA 2
+#define PI05_WAIT_ACT_SLOT 3
+#define PI05_WAIT_ACT_DATA 4
+#define PI05_WAIT_TMEM_SLOT 5
+#define PI05_WAIT_TMEM_DATA 6
+#define PI05_WAIT_EVENT 7
+#define PI05_WAIT_DRAIN 8
 
 /* Replaces build_config() (mk/pi05_mk.cu:3632-3656): a JSON object describing the build and the schedule. */
 const char* pi05_config_json(pi05_handle_t h);

@@ -12,8 +12,10 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libpi05_b200.so")
 NUM_INPUTS = 25
-NUM_STAMPS = 64
+NUM_STAMPS = 256
 
+EVENT_ATTENTION_DONE, EVENT_FFN_NORM_READY = 6, 8
+WAIT_EVENT = 7
 OK, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_NOT_BOUND, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE = range(7)
 
 _c = ctypes
@@ -27,7 +29,7 @@ SIGNATURES = {
     "pi05_status": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
     "pi05_workspace_region": (_c.c_int, [_c.c_void_p, _c.c_char_p, _c.POINTER(_c.c_size_t),
                                          _c.POINTER(_c.c_size_t)]),
-    "pi05_debug": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_longlong]),
+    "pi05_debug": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_longlong, _c.c_int]),
     "pi05_config_json": (_c.c_char_p, [_c.c_void_p]),
     "pi05_launch_count": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_ulonglong)]),
     "pi05_error_string": (_c.c_char_p, [_c.c_int]),

@@ -123,8 +123,9 @@ class Pi05Arm:
         _lib.check(self.lib, self.handle, rc)
         return code.value, where.value
 
-    def debug(self, max_stage: int = -1, wait_limit_cycles: int = 0) -> None:
-        _lib.check(self.lib, self.handle, self.lib.pi05_debug(self.handle, max_stage, wait_limit_cycles))
+    def debug(self, max_stage: int = -1, wait_limit_cycles: int = 0, drop_event: int = -1) -> None:
+        _lib.check(self.lib, self.handle,
+                   self.lib.pi05_debug(self.handle, max_stage, wait_limit_cycles, drop_event))
 
     def enable_stamps(self, on: bool = True) -> None:
         self.stamps = torch.zeros(_lib.NUM_STAMPS, dtype=torch.int64, device=self.device) if on else None

@@ -49,17 +49,19 @@ constexpr float EPS = 1e-6f;
 constexpr int THREADS = 256;
 constexpr int NROW_CTAS = 25;      // attention / row-op CTAs: two tokens each
 constexpr int KATOM = 64;          // K elements per TMA box (128 B of BF16 = one swizzle row)
+constexpr int KSTAGE = 128;        // K elements per pipeline stage (two boxes)
 constexpr int W_ATOM_BYTES = 128 * 128;  // 128 weight rows x 64 k
 constexpr int A_ATOM_BYTES = 64 * 128;   // 64 token rows x 64 k
-constexpr int NW = 10;             // weight ring depth (160 KB)
-constexpr int NA = 4;              // activation ring depth (32 KB)
+constexpr int W_STAGE_BYTES = 2 * W_ATOM_BYTES;
+constexpr int A_STAGE_BYTES = 2 * A_ATOM_BYTES;
+constexpr int STAGE_BYTES_ALL = W_STAGE_BYTES + A_STAGE_BYTES;   // 48 KB: weights, then activations
+constexpr int NSTG = 4;            // pipeline depth (192 KB)
 constexpr int STAGE_STRIDE = 72;   // BF16 elements per row of the epilogue exchange buffer (144 B)
 constexpr int STAGE_BYTES = 128 * STAGE_STRIDE * 2;
 constexpr int TMEM_COLS = 128;     // two 64-column accumulators
 
-constexpr int OFF_WRING = 0;
-constexpr int OFF_ARING = OFF_WRING + NW * W_ATOM_BYTES;
-constexpr int OFF_STAGE = OFF_ARING + NA * A_ATOM_BYTES;   // also the prologue's scratch
+constexpr int OFF_RING = 0;
+constexpr int OFF_STAGE = OFF_RING + NSTG * STAGE_BYTES_ALL;   // epilogue exchange buffer; also the prologue's scratch
 constexpr int OFF_BARS = OFF_STAGE + STAGE_BYTES;
 constexpr int SMEM_BYTES = OFF_BARS + 512 + 1024;          // + barriers + alignment slack
 
@@ -92,6 +94,7 @@ enum { WAIT_W_EMPTY = 1, WAIT_W_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_T_EMPTY, W
 
 struct Unit { int gemm, tile, k0, nk; };
 constexpr int MAX_UNITS = 8;
+constexpr long long DRAIN_CYCLES = 400000;          // exit-time grace period for TMA loads still in flight after an abort
 
 struct alignas(64) TMaps {
   CUtensorMap wq, wk, wv, wo, wg, wu, wd;   // weights: {K, L*rows} BF16, box {64, 64}, 128-B swizzle
@@ -104,6 +107,7 @@ struct Params {
   const float *ain_w, *ain_b, *tin_w, *tin_b, *tout_w, *tout_b, *aout_w, *aout_b;
   const float *attn_nw, *attn_nb, *ffn_nw, *ffn_nb, *fin_nw, *fin_nb;
   const float* noise;
+  const __nv_bfloat16 *wq, *wk, *wv, *wo, *wg, *wu, *wd;
   const __nv_bfloat16 *prefix_k, *prefix_v;
   const uint8_t* prefix_mask;
   float* actions;
@@ -117,6 +121,7 @@ struct Params {
   unsigned long long* stamps;
   long long wait_limit;
   int prefix, n_steps, n_layers, max_stage, n_gemm_ctas;
+  int drop_event;          // debug: this event is never signalled (exercises the bounded waits); -1 = none
   int n_units[4];          // units per GEMM kind (event targets)
   float t_steps[NS];
   float dt;
@@ -164,14 +169,24 @@ __device__ __forceinline__ bool wait_event(const Ctx& c, const unsigned int* ev,
 
 // Called by one thread after the CTA-level barrier that follows the CTA's writes.
 __device__ __forceinline__ void signal_event(unsigned int* ev) {
-  ptx::fence_acq_rel_gpu();
-  ptx::red_release_add(ev, 1u);
+  ptx::red_release_add(ev, 1u);   // release at device scope: cumulative over the writes ordered by the CTA barrier
 }
 
 __device__ __forceinline__ unsigned long long globaltimer() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
+}
+
+// Optional in-kernel trace: GEMM CTAs 0 (gate/up), 64 (QKV) and 84 (O, down) stamp the second layer pass.
+// slot = 64 + 64 * which + gemm * 8 + point; points: 0 inputs seen, 1 last act load issued, 2 first operands
+// in smem, 3 all MMAs issued, 4 accumulator ready, 5 accumulator in registers, 6 stores issued, 7 signalled.
+__device__ __forceinline__ void trace(const Params& p, int cta, int pass, int gemm, int point) {
+  if (p.stamps == nullptr || pass != 1) return;
+  const int which = cta == 0 ? 0 : cta == 64 ? 1 : cta == 84 ? 2 : -1;
+  if (which < 0) return;
+  unsigned long long* slot = p.stamps + 64 + 64 * which + gemm * 8 + point;
+  if (*slot == 0) *slot = globaltimer();
 }
 
 // ------------------------------------------------------------------------------------------- small math
@@ -625,50 +640,68 @@ __device__ void attention_unit(const Params& p, uint8_t* smem, int unit, const A
 
 // ------------------------------------------------------------------------------------------- GEMM CTA roles
 struct Bars {
-  uint32_t wfull, wempty, afull, aempty, tfull, tempty;   // shared-memory addresses of barrier arrays
+  uint32_t full, empty, tfull, tempty;   // shared-memory addresses of barrier arrays
 };
 
 __device__ __forceinline__ int stage_of(int pass, int gemm) { return pass * NSTAGE + kGemmStage[gemm]; }
 
-struct Producer { int pass, u, a; uint32_t it; bool done; };
+struct Producer { int pass, u, a; uint32_t it, slot, par; bool done; };
 
-// Issue weight loads in schedule order until `until` loads have been issued in total (or the schedule ends).
-__device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t wring,
+// Tensor maps and first rows of the two 64-row halves of a unit's 128-row weight tile.
+__device__ __forceinline__ void weight_rows(const Params& p, const Unit& un, int layer, const CUtensorMap*& ma,
+                                            const CUtensorMap*& mb, int& ra, int& rbw) {
+  if (un.gemm == G_QKV) {
+    if (un.tile < 16) { ma = mb = &p.maps.wq; ra = layer * QD + (un.tile >> 1) * HD + (un.tile & 1) * 64; rbw = ra + 128; }
+    else if (un.tile < 18) { ma = mb = &p.maps.wk; ra = layer * HD + (un.tile - 16) * 64; rbw = ra + 128; }
+    else { ma = mb = &p.maps.wv; ra = layer * HD + (un.tile - 18) * 128; rbw = ra + 64; }
+  } else if (un.gemm == G_O) { ma = mb = &p.maps.wo; ra = layer * W + un.tile * 128; rbw = ra + 64; }
+  else if (un.gemm == G_GU) { ma = &p.maps.wg; mb = &p.maps.wu; ra = rbw = layer * FF + un.tile * 64; }
+  else { ma = mb = &p.maps.wd; ra = layer * W + un.tile * 128; rbw = ra + 64; }
+}
+
+// Issue weight loads in schedule order until `until` stages have been issued in total (or the schedule ends).
+// A stage holds 128 weight rows x 128 k as two 64-k halves, each made of two 64-row boxes.  The thread is alone
+// in its warp, so every instruction costs its full latency: everything that does not change within a unit is
+// computed once per unit.
+__device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t ring,
                                 const Bars& b, Producer& st, uint32_t until, uint64_t policy) {
   const int npass = p.n_steps * p.n_layers;
+  if (nunits == 0) { st.done = true; return; }
   while (!st.done && st.it < until) {
     if (st.pass >= npass) { st.done = true; break; }
-    if (st.u >= nunits) { st.u = 0; ++st.pass; continue; }
     const Unit un = units[st.u];
-    if (stage_of(st.pass, un.gemm) >= p.max_stage) { st.done = true; break; }
-    if (st.a >= un.nk) { st.a = 0; ++st.u; continue; }
-    const int slot = st.it % NW;
-    const uint32_t par = (st.it / NW) & 1;
-    if (!wait_mbar(c, b.wempty + 8 * slot, par ^ 1, WAIT_W_EMPTY, stage_of(st.pass, un.gemm))) { st.done = true; break; }
-    const int layer = st.pass % p.n_layers;
+    const int stage = stage_of(st.pass, un.gemm);
+    if (stage >= p.max_stage) { st.done = true; break; }
     const CUtensorMap *ma, *mb;
     int ra, rbw;
-    if (un.gemm == G_QKV) {
-      if (un.tile < 16) { ma = mb = &p.maps.wq; ra = layer * QD + (un.tile >> 1) * HD + (un.tile & 1) * 64; rbw = ra + 128; }
-      else if (un.tile < 18) { ma = mb = &p.maps.wk; ra = layer * HD + (un.tile - 16) * 64; rbw = ra + 128; }
-      else { ma = mb = &p.maps.wv; ra = layer * HD + (un.tile - 18) * 128; rbw = ra + 64; }
-    } else if (un.gemm == G_O) { ma = mb = &p.maps.wo; ra = layer * W + un.tile * 128; rbw = ra + 64; }
-    else if (un.gemm == G_GU) { ma = &p.maps.wg; mb = &p.maps.wu; ra = rbw = layer * FF + un.tile * 64; }
-    else { ma = mb = &p.maps.wd; ra = layer * W + un.tile * 128; rbw = ra + 64; }
-    const uint32_t full = b.wfull + 8 * slot;
-    const uint32_t dst = wring + slot * W_ATOM_BYTES;
-    const int kc = (un.k0 + st.a) * KATOM;
-    ptx::mbar_expect_tx(full, W_ATOM_BYTES);
-    ptx::tma_load_2d_hint(dst, ma, full, kc, ra, policy);
-    ptx::tma_load_2d_hint(dst + W_ATOM_BYTES / 2, mb, full, kc, rbw, policy);
-    ++st.a;
-    ++st.it;
+    weight_rows(p, un, st.pass % p.n_layers, ma, mb, ra, rbw);
+    int kc = (un.k0 + st.a) * KSTAGE;
+    uint32_t slot = st.slot, par = st.par, it = st.it;
+    int a = st.a;
+    for (; a < un.nk && it < until; ++a, ++it, kc += KSTAGE) {
+      if (!wait_mbar(c, b.empty + 8 * slot, par ^ 1, WAIT_W_EMPTY, stage)) { st.done = true; break; }
+      const uint32_t full = b.full + 8 * slot;
+      const uint32_t dst = ring + slot * STAGE_BYTES_ALL;
+      ptx::mbar_expect_tx(full, W_STAGE_BYTES);
+      ptx::tma_load_2d_hint(dst, ma, full, kc, ra, policy);
+      ptx::tma_load_2d_hint(dst + W_ATOM_BYTES / 2, mb, full, kc, rbw, policy);
+      ptx::tma_load_2d_hint(dst + W_ATOM_BYTES, ma, full, kc + KATOM, ra, policy);
+      ptx::tma_load_2d_hint(dst + W_ATOM_BYTES + W_ATOM_BYTES / 2, mb, full, kc + KATOM, rbw, policy);
+      if (++slot == NSTG) { slot = 0; par ^= 1; }
+    }
+    st.slot = slot; st.par = par; st.it = it; st.a = a;
+    if (a >= un.nk) {
+      st.a = 0;
+      if (++st.u >= nunits) { st.u = 0; ++st.pass; }
+    }
   }
 }
 
-__device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t aring, const Bars& b) {
+// Activation half of every stage: waits for the stage that produces the operand, then follows the same stage
+// order as the weight producer.
+__device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t ring, const Bars& b) {
   const int npass = p.n_steps * p.n_layers;
-  uint32_t ait = 0;
+  uint32_t slot = 0, par = 0;
   for (int pass = 0; pass < npass; ++pass) {
     for (int u = 0; u < nunits; ++u) {
       const Unit un = units[u];
@@ -682,23 +715,32 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
       else if (un.gemm == G_GU) { m = &p.maps.an_ffn; ev = EV_ANF; target = NROW_CTAS * (pass + 1); }
       else { m = &p.maps.act; ev = EV_GU; target = p.n_units[G_GU] * (pass + 1); }
       if (!wait_event(c, p.ctrl + 16 + ev, target, stage)) return;
+      trace(p, c.cta, pass, un.gemm, 0);
       ptx::fence_proxy_async_global();
-      for (int a = 0; a < un.nk; ++a, ++ait) {
-        const int slot = ait % NA;
-        if (!wait_mbar(c, b.aempty + 8 * slot, ((ait / NA) & 1) ^ 1, WAIT_A_EMPTY, stage)) return;
-        ptx::mbar_expect_tx(b.afull + 8 * slot, A_ATOM_BYTES);
-        ptx::tma_load_2d(aring + slot * A_ATOM_BYTES, m, b.afull + 8 * slot, (un.k0 + a) * KATOM, 0);
+      int kc = un.k0 * KSTAGE;
+      for (int a = 0; a < un.nk; ++a, kc += KSTAGE) {
+        if (!wait_mbar(c, b.empty + 8 * slot, par ^ 1, WAIT_A_EMPTY, stage)) return;
+        const uint32_t full = b.full + 8 * slot;
+        const uint32_t dst = ring + slot * STAGE_BYTES_ALL + W_STAGE_BYTES;
+        ptx::mbar_expect_tx(full, A_STAGE_BYTES);
+        ptx::tma_load_2d(dst, m, full, kc, 0);
+        ptx::tma_load_2d(dst + A_ATOM_BYTES, m, full, kc + KATOM, 0);
+        if (++slot == NSTG) { slot = 0; par ^= 1; }
       }
+      trace(p, c.cta, pass, un.gemm, 1);
     }
   }
 }
 
-// Returns the number of weight atoms consumed (for the drain at exit).
-__device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t wring,
-                               uint32_t aring, const Bars& b, uint32_t tmem) {
+// Returns the number of stages consumed (for the drain at exit).  One thread issues every MMA of the CTA, and a
+// tcgen05 instruction costs it about 50 cycles, so the loop does one wait and one commit per eight MMAs and
+// advances the shared-memory descriptors by adding constants to their low words.
+__device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t ring,
+                               const Bars& b, uint32_t tmem) {
   const int npass = p.n_steps * p.n_layers;
   const uint32_t idesc = ptx::umma_idesc_bf16(128, 64);
-  uint32_t it = 0, ait = 0, uit = 0;
+  const uint64_t adesc0 = ptx::umma_smem_desc(ring), bdesc0 = ptx::umma_smem_desc(ring + W_STAGE_BYTES);
+  uint32_t it = 0, uit = 0, slot = 0, par = 0;
   for (int pass = 0; pass < npass; ++pass) {
     for (int u = 0; u < nunits; ++u, ++uit) {
       const Unit un = units[u];
@@ -708,20 +750,27 @@ __device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units,
       if (!wait_mbar(c, b.tempty + 8 * buf, ((uit >> 1) & 1) ^ 1, WAIT_T_EMPTY, stage)) return it;
       ptx::tc_fence_after();
       const uint32_t d = tmem + buf * 64;
-      for (int a = 0; a < un.nk; ++a, ++it, ++ait) {
-        const int ws = it % NW, as = ait % NA;
-        if (!wait_mbar(c, b.wfull + 8 * ws, (it / NW) & 1, WAIT_W_FULL, stage)) return it;
-        if (!wait_mbar(c, b.afull + 8 * as, (ait / NA) & 1, WAIT_A_FULL, stage)) return it;
+      uint32_t accumulate = 0;
+      for (int a = 0; a < un.nk; ++a, ++it) {
+        if (!wait_mbar(c, b.full + 8 * slot, par, WAIT_W_FULL, stage)) return it;
+        if (a == 0) trace(p, c.cta, pass, un.gemm, 2);
         ptx::tc_fence_after();
-        const uint64_t ad = ptx::umma_smem_desc(wring + ws * W_ATOM_BYTES);
-        const uint64_t bd = ptx::umma_smem_desc(aring + as * A_ATOM_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < KATOM / 16; ++kk)
-          ptx::umma_bf16(d, ad + 2 * kk, bd + 2 * kk, idesc, (a | kk) ? 1u : 0u);
-        ptx::umma_commit(b.wempty + 8 * ws);
-        ptx::umma_commit(b.aempty + 8 * as);
+        const uint64_t ad = adesc0 + (uint64_t)(slot * (STAGE_BYTES_ALL >> 4));
+        const uint64_t bd = bdesc0 + (uint64_t)(slot * (STAGE_BYTES_ALL >> 4));
+        ptx::umma_bf16(d, ad, bd, idesc, accumulate);
+        ptx::umma_bf16(d, ad + 2, bd + 2, idesc, 1u);
+        ptx::umma_bf16(d, ad + 4, bd + 4, idesc, 1u);
+        ptx::umma_bf16(d, ad + 6, bd + 6, idesc, 1u);
+        ptx::umma_bf16(d, ad + (W_ATOM_BYTES >> 4), bd + (A_ATOM_BYTES >> 4), idesc, 1u);
+        ptx::umma_bf16(d, ad + (W_ATOM_BYTES >> 4) + 2, bd + (A_ATOM_BYTES >> 4) + 2, idesc, 1u);
+        ptx::umma_bf16(d, ad + (W_ATOM_BYTES >> 4) + 4, bd + (A_ATOM_BYTES >> 4) + 4, idesc, 1u);
+        ptx::umma_bf16(d, ad + (W_ATOM_BYTES >> 4) + 6, bd + (A_ATOM_BYTES >> 4) + 6, idesc, 1u);
+        accumulate = 1u;
+        ptx::umma_commit(b.empty + 8 * slot);
+        if (++slot == NSTG) { slot = 0; par ^= 1; }
       }
       ptx::umma_commit(b.tfull + 8 * buf);
+      trace(p, c.cta, pass, un.gemm, 3);
     }
   }
   return it;
@@ -748,6 +797,7 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
                      : "=r"(any_fail) : "r"(ok ? 0 : 1) : "memory");
         if (any_fail) return;
       }
+      if (et == 0) trace(p, c.cta, pass, un.gemm, 4);
       ptx::tc_fence_after();
       uint32_t r[64];
       {
@@ -761,6 +811,7 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
       }
       ptx::tc_fence_before();
       ptx::mbar_arrive(b.tempty + 8 * buf);
+      if (et == 0) trace(p, c.cta, pass, un.gemm, 5);
 
       if (un.gemm == G_O || un.gemm == G_DOWN) {
         // split-K partial: FP32 reduction into the L2-resident accumulator [T][W]
@@ -804,14 +855,16 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
             const int d = j + (hi ? 128 : 0);
             __nv_bfloat16* dst = isq ? p.q + (un.tile >> 1) * HD + d : p.k + d;
             const int ld = isq ? QD : HD;
-            const uint32_t* rope = p.rope + j;
+            const uint32_t* __restrict__ rope = p.rope + j;
+            uint32_t cs[T];
+#pragma unroll
+            for (int t = 0; t < T; ++t) cs[t] = __ldcg(rope + t * (HD / 2));   // all loads in flight before the stores
 #pragma unroll
             for (int t = 0; t < T; ++t) {
-              const uint32_t cs = rope[t * (HD / 2)];
               const float x = (t & 1) ? bf16_hi(pk[t >> 1]) : bf16_lo(pk[t >> 1]);
               const float y = (t & 1) ? bf16_hi(po[t >> 1]) : bf16_lo(po[t >> 1]);
               const float rot = hi ? y : -y;                       // rotate_half: (-x2, x1)
-              dst[(size_t)t * ld] = __float2bfloat16_rn(rb(x * bf16_lo(cs)) + rb(rot * bf16_hi(cs)));
+              dst[(size_t)t * ld] = __float2bfloat16_rn(rb(x * bf16_lo(cs[t])) + rb(rot * bf16_hi(cs[t])));
             }
           } else {
             __nv_bfloat16* dst = p.v + (un.tile - 18) * 128 + et;
@@ -821,10 +874,12 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
           }
         }
       }
+      if (et == 0) trace(p, c.cta, pass, un.gemm, 6);
       ptx::named_bar_sync(1, 128);
       if (et == 0) {
         const int ev = un.gemm == G_QKV ? EV_QKV : un.gemm == G_O ? EV_O : un.gemm == G_GU ? EV_GU : EV_DOWN;
         signal_event(p.ctrl + 16 + ev);
+        trace(p, c.cta, pass, un.gemm, 7);
       }
     }
   }
@@ -842,7 +897,7 @@ __device__ bool cta_wait_event(const Params& p, const Ctx& c, int ev, unsigned t
 
 __device__ void cta_signal(const Params& p, int ev) {
   __syncthreads();
-  if (threadIdx.x == 0) signal_event(p.ctrl + 16 + ev);
+  if (threadIdx.x == 0 && ev != p.drop_event) signal_event(p.ctrl + 16 + ev);
 }
 
 __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit) {
@@ -858,7 +913,7 @@ __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit) 
     issue(0, 0);                       // prefix chunks do not depend on this layer's QKV: fetch before waiting
     if (npc >= 2) issue(1, 1);
     if (!cta_wait_event(p, c, EV_QKV, p.n_units[G_QKV] * (pass + 1), pass * NSTAGE + ST_ATT)) return;
-    if (stamp && sbase + ST_QKV < PI05_NUM_STAMPS) p.stamps[sbase + ST_QKV] = globaltimer();
+    if (stamp && sbase + ST_QKV < 64) p.stamps[sbase + ST_QKV] = globaltimer();
     if (npc < 2) issue(1, 1);          // chunk 1 is the suffix chunk
     {
       const __nv_bfloat16* qsrc = p.q + (size_t)unit * 2 * QD;
@@ -872,23 +927,23 @@ __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit) 
     }
     attention_unit(p, smem, unit, issue);
     cta_signal(p, EV_ATT);
-    if (stamp && sbase + ST_ATT < PI05_NUM_STAMPS) p.stamps[sbase + ST_ATT] = globaltimer();
+    if (stamp && sbase + ST_ATT < 64) p.stamps[sbase + ST_ATT] = globaltimer();
     // ---- residual + norm after the O projection
     if (pass * NSTAGE + ST_RATT >= p.max_stage) return;
     if (!cta_wait_event(p, c, EV_O, p.n_units[G_O] * (pass + 1), pass * NSTAGE + ST_RATT)) return;
-    if (stamp && sbase + ST_O < PI05_NUM_STAMPS) p.stamps[sbase + ST_O] = globaltimer();
+    if (stamp && sbase + ST_O < 64) p.stamps[sbase + ST_O] = globaltimer();
     row_op(p, smem, unit, ROW_ATT, step, layer);
     ptx::fence_proxy_async_global();
     cta_signal(p, EV_ANF);
-    if (stamp && sbase + ST_RATT < PI05_NUM_STAMPS) p.stamps[sbase + ST_RATT] = globaltimer();
+    if (stamp && sbase + ST_RATT < 64) p.stamps[sbase + ST_RATT] = globaltimer();
     // ---- residual + norm (or step tail) after the down projection
     if (pass * NSTAGE + ST_RFFN >= p.max_stage) return;
     if (!cta_wait_event(p, c, EV_DOWN, p.n_units[G_DOWN] * (pass + 1), pass * NSTAGE + ST_RFFN)) return;
-    if (stamp && sbase + ST_DOWN < PI05_NUM_STAMPS) p.stamps[sbase + ST_DOWN] = globaltimer();
+    if (stamp && sbase + ST_DOWN < 64) p.stamps[sbase + ST_DOWN] = globaltimer();
     row_op(p, smem, unit, ROW_FFN, step, layer);
     ptx::fence_proxy_async_global();
     cta_signal(p, EV_ANA);
-    if (stamp && sbase + ST_RFFN < PI05_NUM_STAMPS) p.stamps[sbase + ST_RFFN] = globaltimer();
+    if (stamp && sbase + ST_RFFN < 64) p.stamps[sbase + ST_RFFN] = globaltimer();
   }
 }
 
@@ -908,17 +963,15 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
   Bars b;
   {
     const uint32_t base = ptx::smem_u32(smem + OFF_BARS);
-    b.wfull = base; b.wempty = base + 8 * NW; b.afull = base + 16 * NW; b.aempty = b.afull + 8 * NA;
-    b.tfull = b.aempty + 8 * NA; b.tempty = b.tfull + 16;
+    b.full = base; b.empty = base + 8 * NSTG; b.tfull = base + 16 * NSTG; b.tempty = b.tfull + 16;
   }
-  const uint32_t wring = ptx::smem_u32(smem + OFF_WRING), aring = ptx::smem_u32(smem + OFF_ARING);
+  const uint32_t ring = ptx::smem_u32(smem + OFF_RING);
   const Unit* units = p.sched + (size_t)cta * MAX_UNITS;
   const int nunits = is_gemm ? p.sched_n[cta] : 0;
 
   if (tid == 0) {
     s_issued = 0; s_consumed = 0;
-    for (int i = 0; i < NW; ++i) { ptx::mbar_init(b.wfull + 8 * i, 1); ptx::mbar_init(b.wempty + 8 * i, 1); }
-    for (int i = 0; i < NA; ++i) { ptx::mbar_init(b.afull + 8 * i, 1); ptx::mbar_init(b.aempty + 8 * i, 1); }
+    for (int i = 0; i < NSTG; ++i) { ptx::mbar_init(b.full + 8 * i, 2); ptx::mbar_init(b.empty + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) { ptx::mbar_init(b.tfull + 8 * i, 1); ptx::mbar_init(b.tempty + 8 * i, 128); }
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_shared();
@@ -933,11 +986,11 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
   const uint32_t tmem = s_tmem;
 
   // The first ring of weights does not depend on anything: start streaming before the prologue.
-  Producer prod{0, 0, 0, 0u, false};
+  Producer prod{0, 0, 0, 0u, 0u, 0u, false};
   uint64_t policy = 0;
   if (is_gemm && warp == 0 && lane == 0) {
     policy = ptx::policy_evict_first();
-    weight_producer(p, c, units, nunits, wring, b, prod, NW, policy);
+    weight_producer(p, c, units, nunits, ring, b, prod, NSTG, policy);
   }
 
   // ---------------- prologue: tables, time MLP, all modulation rows (FP32 weights streamed once)
@@ -956,13 +1009,13 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
     if (is_gemm) {
       if (warp == 0) {
         if (lane == 0) {
-          weight_producer(p, c, units, nunits, wring, b, prod, 0xffffffffu, policy);
+          weight_producer(p, c, units, nunits, ring, b, prod, 0xffffffffu, policy);
           s_issued = prod.it;
         }
       } else if (warp == 1) {
-        if (lane == 0) s_consumed = mma_issuer(p, c, units, nunits, wring, aring, b, tmem);
+        if (lane == 0) s_consumed = mma_issuer(p, c, units, nunits, ring, b, tmem);
       } else if (warp == 2) {
-        if (lane == 0) act_producer(p, c, units, nunits, aring, b);
+        if (lane == 0) act_producer(p, c, units, nunits, ring, b);
       } else if (warp >= 4) {
         epilogue(p, c, units, nunits, smem, b, tmem);
       }
@@ -980,14 +1033,11 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
 
   // ---------------- teardown: drain loads still in flight, free TMEM, last CTA out clears the counters
   __syncthreads();
-  if (is_gemm && warp == 0 && lane == 0) {
-    const uint32_t issued = s_issued, consumed = s_consumed;
-    for (uint32_t it = consumed; it < issued; ++it) {
-      const long long t0 = clock64();
-      while (!ptx::mbar_try_wait(b.wfull + 8 * (it % NW), (it / NW) & 1)) {
-        if (clock64() - t0 > c.limit) { report_timeout(c, WAIT_DRAIN, 0); break; }
-      }
-    }
+  if (is_gemm && warp == 0 && lane == 0 && s_issued != s_consumed) {
+    // Only after an aborted run: weight loads were issued whose stage was never consumed.  Their stage barrier
+    // also expects the activation half, which may never come, so give the copies in flight a fixed time to land.
+    const long long t0 = clock64();
+    while (clock64() - t0 < DRAIN_CYCLES) { }
   }
   __syncthreads();
   if (is_gemm && warp == 1) {
@@ -1028,6 +1078,7 @@ struct pi05_engine {
   int n_units[4] = {0, 0, 0, 0};
   TMaps maps;
   int max_stage = 0x7fffffff;
+  int drop_event = -1;
   long long wait_limit = 4000000000ll;    // ~2 s of SM clocks
   unsigned long long launches = 0;
   std::string config;
@@ -1108,7 +1159,7 @@ Tp* region_ptr(const pi05_engine* h, const char* name) {
   return reinterpret_cast<Tp*>(h->ws + find_region(h, name)->off);
 }
 
-// Static work schedule: which CTA runs which 128-row weight tile over which range of 64-wide K atoms.
+// Static work schedule: which CTA runs which 128-row weight tile over which range of 128-wide K stages.
 //   gate/up: 64 tiles (64 gate rows + the matching 64 up rows), full K, one per CTA 0..63
 //   QKV:     20 tiles (16 q, 2 k, 2 v), full K, one per CTA 64..83
 //   O, down: 8 row tiles each, K split in contiguous runs over the remaining GEMM CTAs
@@ -1118,7 +1169,7 @@ bool build_schedule(pi05_engine* h) {
   h->sched.assign((size_t)h->grid * MAX_UNITS, Unit{0, 0, 0, 0});
   h->sched_n.assign(h->grid, 0);
   std::vector<std::vector<Unit>> per(h->grid);
-  for (int u = 0; u < 20; ++u) per[64 + u].push_back(Unit{G_QKV, u, 0, W / KATOM});
+  for (int u = 0; u < 20; ++u) per[64 + u].push_back(Unit{G_QKV, u, 0, W / KSTAGE});
   const int od0 = 84, nod = ng - od0;
   auto split = [&](int gemm, int tiles, int atoms_per_tile) {
     const int total = tiles * atoms_per_tile;
@@ -1132,9 +1183,9 @@ bool build_schedule(pi05_engine* h) {
       }
     }
   };
-  split(G_O, W / 128, QD / KATOM);
-  for (int u = 0; u < 64; ++u) per[u].push_back(Unit{G_GU, u, 0, W / KATOM});
-  split(G_DOWN, W / 128, FF / KATOM);
+  split(G_O, W / 128, QD / KSTAGE);
+  for (int u = 0; u < 64; ++u) per[u].push_back(Unit{G_GU, u, 0, W / KSTAGE});
+  split(G_DOWN, W / 128, FF / KSTAGE);
   for (int g = 0; g < 4; ++g) h->n_units[g] = 0;
   for (int ctaid = 0; ctaid < h->grid; ++ctaid) {
     if ((int)per[ctaid].size() > MAX_UNITS) return false;
@@ -1219,10 +1270,10 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   char buf[1024];
   snprintf(buf, sizeof buf,
            "{\"kernel\": \"pi05_chunk_kernel\", \"arch\": \"sm_100a\", \"launches_per_chunk\": 1, \"grid\": %d, "
-           "\"threads\": %d, \"smem_bytes\": %d, \"gemm_ctas\": %d, \"row_ctas\": %d, \"weight_ring\": %d, "
-           "\"act_ring\": %d, \"units\": {\"qkv\": %d, \"o\": %d, \"gate_up\": %d, \"down\": %d}, "
+           "\"threads\": %d, \"smem_bytes\": %d, \"gemm_ctas\": %d, \"row_ctas\": %d, \"stages\": %d, "
+           "\"stage_bytes\": %d, \"units\": {\"qkv\": %d, \"o\": %d, \"gate_up\": %d, \"down\": %d}, "
            "\"mma\": \"tcgen05 cta_group::1 M128 N64 K16 bf16\", \"sync\": \"device-scope counters, bounded waits\"}",
-           h->grid, THREADS, SMEM_BYTES, h->n_gemm, NROW_CTAS, NW, NA, h->n_units[0], h->n_units[1], h->n_units[2],
+           h->grid, THREADS, SMEM_BYTES, h->n_gemm, NROW_CTAS, NSTG, STAGE_BYTES_ALL, h->n_units[0], h->n_units[1], h->n_units[2],
            h->n_units[3]);
   h->config = buf;
   *out = h;
@@ -1288,8 +1339,9 @@ int pi05_refresh(pi05_handle_t h) {
   return h->bound ? PI05_OK : PI05_ERR_NOT_BOUND;
 }
 
-int pi05_debug(pi05_handle_t h, int max_stage, long long wait_limit_cycles) {
-  if (!valid_handle(h)) return PI05_ERR_ARGUMENT;
+int pi05_debug(pi05_handle_t h, int max_stage, long long wait_limit_cycles, int drop_event) {
+  if (!valid_handle(h) || drop_event >= NEVENTS) return PI05_ERR_ARGUMENT;
+  h->drop_event = drop_event < 0 ? -1 : drop_event;
   h->max_stage = max_stage < 0 ? 0x7fffffff : max_stage;
   if (wait_limit_cycles > 0) h->wait_limit = wait_limit_cycles;
   return PI05_OK;
@@ -1313,6 +1365,9 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.ffn_nw = (const float*)in[17]; p.ffn_nb = (const float*)in[18];
   p.fin_nw = (const float*)in[19]; p.fin_nb = (const float*)in[20];
   p.noise = (const float*)in[21];
+  p.wq = (const __nv_bfloat16*)in[8]; p.wk = (const __nv_bfloat16*)in[9]; p.wv = (const __nv_bfloat16*)in[10];
+  p.wo = (const __nv_bfloat16*)in[11]; p.wg = (const __nv_bfloat16*)in[12]; p.wu = (const __nv_bfloat16*)in[13];
+  p.wd = (const __nv_bfloat16*)in[14];
   p.prefix_k = (const __nv_bfloat16*)in[22]; p.prefix_v = (const __nv_bfloat16*)in[23];
   p.prefix_mask = (const uint8_t*)in[24];
   p.actions = (float*)h->actions;
@@ -1330,6 +1385,7 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.wait_limit = h->wait_limit;
   p.prefix = h->prefix; p.n_steps = n_steps; p.n_layers = n_layers; p.max_stage = h->max_stage;
   p.n_gemm_ctas = h->n_gemm;
+  p.drop_event = h->drop_event;
   for (int g = 0; g < 4; ++g) p.n_units[g] = h->n_units[g];
   const double dt = -1.0 / NS;
   for (int s = 0; s < NS; ++s) p.t_steps[s] = (float)(1.0 + s * dt);

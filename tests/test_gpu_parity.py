@@ -1,0 +1,284 @@
+"""Parity of the CUDA engine with the oracle, through the arm / C ABI.  Every test needs a B200.
+
+Tolerances: the engine's result must sit inside the reference harness's band (fixture.py:105-120): error
+against the FP32 oracle <= 2x the BF16 reference's own error + rtol 0.003 (relative L2), and max-abs <=
+2x reference max-abs + atol 0.003 + 0.003 * max|exact|.  Stage checks compare single stages computed from
+the engine's own inputs to that stage, where only summation order differs: BF16 buffers within 2 BF16 ulps
+(relative 2^-7 of the value scale), FP32 accumulators within 1e-4 relative L2.
+"""
+import ctypes
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import pi05_oracle as O
+from pi05_megakernel_b200 import _lib
+from pi05_megakernel_b200 import fixture as FX
+from tests.helpers import fingerprints_match, load_full
+
+pytestmark = pytest.mark.gpu
+
+WAIT_DEFAULT = 4_000_000_000
+
+
+def _arm(geo, variant="b200"):
+    from pi05_megakernel_b200.arm import Pi05Arm
+    return Pi05Arm(geo, variant, "cuda")
+
+
+@pytest.fixture(scope="module")
+def case128():
+    geo = FX.Geometry(prefix=128)
+    cpu = FX.make_inputs(geo, FX.SEEDS[0], "cpu", "full")
+    dev = {k: v.cuda() for k, v in cpu.items()}
+    return geo, O.Geo(prefix=128), cpu, dev
+
+
+def _run(arm):
+    arm.launch()
+    arm.status()
+    return arm.outputs()["actions"].cpu()
+
+
+def _rel(got, want):
+    got, want = got.float(), want.float()
+    return float((got - want).norm() / want.norm().clamp_min(1e-30))
+
+
+def test_prologue_tables(case128):
+    """Time embedding, time MLP, all 370 modulation vectors, RoPE table, first action_in and norm."""
+    geo, ogeo, cpu, dev = case128
+    arm = _arm(geo)
+    arm.bind(dev)
+    arm.debug(0, 0, -1)
+    _run(arm)
+    dt = -1.0 / 10
+    times = [torch.full((1,), 1.0 + s * dt, dtype=torch.float32) for s in range(10)]
+    temb = torch.stack([O.time_embedding(t, 1024)[0] for t in times])
+    cond = torch.stack([O.time_condition(cpu, t, 1024)[0] for t in times])
+    assert torch.equal(arm.region("temb", torch.float32, (10, 1024)).cpu(), temb)
+    assert _rel(arm.region("cond", torch.float32, (10, 1024)).cpu(), cond) < 2e-6
+    nw = torch.cat([torch.stack([dev["attn_norm_weight"], dev["ffn_norm_weight"]], 1).reshape(36, 3072, 1024),
+                    dev["final_norm_weight"][None]])
+    nb = torch.cat([torch.stack([dev["attn_norm_bias"], dev["ffn_norm_bias"]], 1).reshape(36, 3072),
+                    dev["final_norm_bias"][None]])
+    torch.backends.cuda.matmul.allow_tf32 = False
+    mod_want = torch.einsum("sk,njk->snj", cond.cuda(), nw) + nb[None]
+    mod = arm.region("mod", torch.float32, (10, 37, 3072))
+    assert _rel(mod, mod_want) < 5e-6
+    pos, _ = O.suffix_layout(cpu["prefix_mask"], 50)
+    inv = 1.0 / (O.ROPE_THETA ** (torch.arange(0, 256, 2, dtype=torch.int64).float() / 256))
+    ph = pos.float()[:, None] * inv[None]
+    rope = arm.region("rope", torch.int32, (50, 128)).cpu()
+    rcos = (rope & 0xffff).to(torch.int16).view(torch.bfloat16)
+    rsin = ((rope >> 16) & 0xffff).to(torch.int16).view(torch.bfloat16)
+    # cos/sin of phases up to ~180 rad: allow a last-bit difference of the FP32 phase on a few entries
+    assert float((rcos.float() - ph.cos().to(torch.bfloat16).float()).abs().max()) <= 2 ** -7
+    assert float((rsin.float() - ph.sin().to(torch.bfloat16).float()).abs().max()) <= 2 ** -7
+    h0 = F.linear(cpu["noise"], cpu["action_in_weight"], cpu["action_in_bias"]).to(torch.bfloat16)
+    got_h0 = arm.region("h", torch.bfloat16, (50, 1024)).cpu()
+    assert float((got_h0.float() - h0.float()).abs().max()) <= 2 ** -8 * float(h0.abs().max())
+    an, _ = O.ada_rms(got_h0, mod[0, 0].cpu(), O._cast(False))
+    assert _rel(arm.region("an_attn", torch.bfloat16, (50, 1024)).cpu(), an) < 1e-3
+    arm.close()
+
+
+def test_one_layer_stage_by_stage(case128):
+    """Each of the seven stages of layer 0, checked from the engine's own inputs to that stage."""
+    geo, ogeo, cpu, dev = case128
+    arm = _arm(geo)
+    arm.bind(dev)
+    f = lambda x: x.float()
+    _, allowed = O.suffix_layout(cpu["prefix_mask"], 50)
+    keep = {}
+    for stage in range(1, 8):
+        arm.debug(stage, 0, -1)
+        _run(arm)
+        reg = lambda n, d, s: arm.region(n, d, s).clone()
+        if stage == 1:
+            an = f(reg("an_attn", torch.bfloat16, (50, 1024)))
+            rope = reg("rope", torch.int32, (50, 128))
+            cos = (rope & 0xffff).to(torch.int16).view(torch.bfloat16).float()
+            sin = ((rope >> 16) & 0xffff).to(torch.int16).view(torch.bfloat16).float()
+            cos, sin = torch.cat((cos, cos), -1)[:, None], torch.cat((sin, sin), -1)[:, None]
+            rot = lambda x: O.rb(O.rb(x * cos) + O.rb(torch.cat((-x[..., 128:], x[..., :128]), -1) * sin))
+            q = rot(O.rb(an @ f(dev["wq"][0]).T).view(50, 8, 256)).reshape(50, 2048)
+            k = rot(O.rb(an @ f(dev["wk"][0]).T).view(50, 1, 256)).reshape(50, 256)
+            v = O.rb(an @ f(dev["wv"][0]).T)
+            assert _rel(reg("q", torch.bfloat16, (50, 2048)), q) < 1e-3
+            assert _rel(reg("k", torch.bfloat16, (50, 256)), k) < 1e-3
+            assert _rel(reg("v", torch.bfloat16, (50, 256)), v) < 1e-3
+        elif stage == 2:
+            q = f(reg("q", torch.bfloat16, (50, 8, 256)))
+            keys = torch.cat((f(dev["prefix_k"][0][:, 0]), f(reg("k", torch.bfloat16, (50, 256)))))
+            vals = torch.cat((f(dev["prefix_v"][0][:, 0]), f(reg("v", torch.bfloat16, (50, 256)))))
+            s = O.rb(O.rb(torch.einsum("thd,kd->thk", q, keys)) * (1 / 16))
+            s = torch.where(allowed.cuda()[:, None, :], s, torch.full_like(s, float("-inf")))
+            e = torch.exp(s - s.max(-1, keepdim=True).values)
+            o = torch.einsum("thk,kd->thd", O.rb(e), vals) / e.sum(-1, keepdim=True)
+            assert _rel(reg("attn", torch.bfloat16, (50, 2048)), O.rb(o).reshape(50, 2048)) < 4e-3
+        elif stage == 3:
+            keep["o_acc"] = reg("o_acc", torch.float32, (50, 1024))
+            want = f(reg("attn", torch.bfloat16, (50, 2048))) @ f(dev["wo"][0]).T
+            assert _rel(keep["o_acc"], want) < 1e-4
+            keep["h"] = f(reg("h", torch.bfloat16, (50, 1024)))
+        elif stage == 4:
+            mod = reg("mod", torch.float32, (10, 37, 3072))
+            hn = O.rb(keep["h"] + O.rb(O.rb(keep["o_acc"]) * O.rb(mod[0, 0, 2048:])))
+            got_h = reg("h", torch.bfloat16, (50, 1024))
+            assert torch.equal(f(got_h), hn)
+            an, _ = O.ada_rms(got_h.cpu(), mod[0, 1].cpu(), O._cast(False))
+            assert _rel(reg("an_ffn", torch.bfloat16, (50, 1024)).cpu(), an) < 1e-3
+            assert float(reg("o_acc", torch.float32, (50, 1024)).abs().max()) == 0.0
+        elif stage == 5:
+            an = f(reg("an_ffn", torch.bfloat16, (50, 1024)))
+            g, u = O.rb(an @ f(dev["wg"][0]).T), O.rb(an @ f(dev["wu"][0]).T)
+            want = O.rb(O.rb(F.gelu(g, approximate="tanh")) * u)
+            assert _rel(reg("act", torch.bfloat16, (50, 4096)), want) < 1e-3
+        elif stage == 6:
+            keep["d_acc"] = reg("d_acc", torch.float32, (50, 1024))
+            want = f(reg("act", torch.bfloat16, (50, 4096))) @ f(dev["wd"][0]).T
+            assert _rel(keep["d_acc"], want) < 1e-4
+            keep["h"] = f(reg("h", torch.bfloat16, (50, 1024)))
+        elif stage == 7:
+            mod = reg("mod", torch.float32, (10, 37, 3072))
+            hn = O.rb(keep["h"] + O.rb(O.rb(keep["d_acc"]) * O.rb(mod[0, 1, 2048:])))
+            got_h = reg("h", torch.bfloat16, (50, 1024))
+            assert torch.equal(f(got_h), hn)
+            an, _ = O.ada_rms(got_h.cpu(), mod[0, 2].cpu(), O._cast(False))
+            assert _rel(reg("an_attn", torch.bfloat16, (50, 1024)).cpu(), an) < 1e-3
+    arm.close()
+
+
+@pytest.mark.parametrize("steps,layers", [(1, 1), (2, 2), (1, 18), (3, 5)])
+def test_truncated_chunks(case128, steps, layers):
+    geo, ogeo, cpu, dev = case128
+    arm = _arm(geo, f"b200-s{steps}-l{layers}")
+    arm.bind(dev)
+    got = _run(arm)
+    want, exact = O.chunk(cpu, ogeo, False, steps, layers), O.chunk(cpu, ogeo, True, steps, layers)
+    assert O.band(want, got, exact)["pass"]
+    arm.close()
+
+
+def test_band_three_seeds_in_place_refresh_mutation_idempotence():
+    """The reference harness's correctness protocol (bench.py:220-256): three seeds, inputs overwritten in
+    place between seeds, refresh_weights(), band against the FP32 oracle, a second launch, and the
+    (sum, abs-sum) fingerprints of every input unchanged."""
+    geo, ogeo = FX.Geometry(prefix=128), O.Geo(prefix=128)
+    cpu = FX.make_inputs(geo, FX.SEEDS[0], "cpu")
+    dev = {k: v.cuda() for k, v in cpu.items()}
+    arm = _arm(geo)
+    arm.bind(dev)
+    for n, seed in enumerate(FX.SEEDS):
+        if n:
+            cpu = FX.make_inputs(geo, seed, "cpu")
+            for k, v in cpu.items():
+                dev[k].copy_(v)
+            arm.refresh_weights()
+            torch.cuda.synchronize()
+        want, exact = O.chunk(cpu, ogeo, False), O.chunk(cpu, ogeo, True)
+        snap = O.snapshot(dev)
+        got = _run(arm)
+        d = O.band(want, got, exact)
+        assert d["pass"], (seed, d)
+        again = _run(arm)
+        # split-K partial sums meet in FP32 atomics, so a repeat may differ in the last bits of each layer;
+        # it has to stay inside the same band
+        assert O.band(want, again, exact)["pass"]
+        assert O.snapshot(dev) == snap
+    arm.close()
+
+
+@pytest.mark.parametrize("name", ["full_p128_s7301", "full_p128_s8917", "full_p128_s42811", "full_p256_pad"])
+def test_against_stored_reference_outputs(name):
+    """Band against actions the unmodified reference and its FP32 oracle produced (tests/golden)."""
+    geo, ogeo, seed, mask, fps, want, exact = load_full(name)
+    cpu = FX.make_inputs(geo, seed, "cpu", "pad" if "pad" in name else "full")
+    if not fingerprints_match(cpu, fps):
+        pytest.skip("this torch build draws different random inputs than the one that made the vectors")
+    assert torch.equal(cpu["prefix_mask"], mask)
+    arm = _arm(geo)
+    arm.bind({k: v.cuda() for k, v in cpu.items()})
+    got = _run(arm)
+    d = O.band(want, got, exact)
+    assert d["pass"], d
+    arm.close()
+
+
+@pytest.mark.parametrize("prefix,mask", [(1, "full"), (40, "scatter"), (64, "pad"), (65, "full"),
+                                         (512, "scatter"), (968, "pad")])
+def test_prefix_sweep_with_masks(prefix, mask):
+    """Runtime prefix length and general validity masks: one chunk-loop iteration, a ragged last chunk,
+    scattered and right-padded masks, the longest prefix.  Weights are shared with prefix 128 (same seed)."""
+    geo, ogeo = FX.Geometry(prefix=prefix), O.Geo(prefix=prefix)
+    cpu = FX.make_inputs(geo, FX.SEEDS[1], "cpu", mask)
+    arm = _arm(geo, "b200-s2-l3" if prefix not in (512, 968) else "b200")
+    arm.bind({k: v.cuda() for k, v in cpu.items()})
+    got = _run(arm)
+    want = O.chunk(cpu, ogeo, False, arm.steps, arm.layers)
+    exact = O.chunk(cpu, ogeo, True, arm.steps, arm.layers)
+    d = O.band(want, got, exact)
+    assert d["pass"], d
+    # masked-out keys must not matter
+    poisoned = dict(cpu)
+    k = cpu["prefix_k"].clone()
+    k[:, ~cpu["prefix_mask"]] = 50.0
+    poisoned["prefix_k"] = k
+    if not bool(cpu["prefix_mask"].all()):
+        arm2 = _arm(geo, arm.variant)
+        arm2.bind({k_: v.cuda() for k_, v in poisoned.items()})
+        d2 = O.band(want, _run(arm2), exact)
+        assert d2["pass"], d2
+        arm2.close()
+    arm.close()
+
+
+def test_wait_that_runs_out_reports_and_engine_recovers(case128):
+    """Failure detection without faulting the GPU: a stage-completion signal is withheld on purpose, the
+    bounded waits on it give up after ~20 ms, the kernel drains and exits, pi05_status reports which wait
+    and where, and the next launch on the same handle is correct again."""
+    geo, ogeo, cpu, dev = case128
+    arm = _arm(geo, "b200-s1-l2")
+    arm.bind(dev)
+    good = _run(arm)
+    arm.debug(-1, 40_000_000, _lib.EVENT_ATTENTION_DONE)
+    arm.launch()
+    with pytest.raises(_lib.EngineError) as info:
+        arm.status()
+    assert info.value.code == _lib.ERR_DEVICE_TIMEOUT
+    arm.debug(-1, WAIT_DEFAULT, -1)
+    again = _run(arm)
+    want, exact = O.chunk(cpu, ogeo, False, 1, 2), O.chunk(cpu, ogeo, True, 1, 2)
+    assert O.band(want, again, exact)["pass"]
+    assert float((again - good).abs().max()) < 1e-2
+    arm.close()
+
+
+def test_abi_state_errors(case128):
+    geo, ogeo, cpu, dev = case128
+    lib = _lib.load()
+    h = ctypes.c_void_p()
+    assert lib.pi05_create(0, 128, 1, 0, 1, ctypes.byref(h)) == _lib.OK
+    assert lib.pi05_launch(h, 10, 18, None, None) == _lib.ERR_NOT_BOUND
+    n = ctypes.c_size_t()
+    assert lib.pi05_workspace_bytes(h, ctypes.byref(n)) == _lib.OK and n.value > 4_000_000
+    ws = torch.empty(n.value, dtype=torch.uint8, device="cuda")
+    actions = torch.empty(50, 32, device="cuda")
+    ptrs = (ctypes.c_void_p * 25)(*[dev[k].data_ptr() for k in FX.ORDER])
+    assert lib.pi05_bind(h, ptrs, 129, 1, actions.data_ptr(), ws.data_ptr(), n.value) == _lib.ERR_ARGUMENT
+    assert lib.pi05_bind(h, ptrs, 128, 2, actions.data_ptr(), ws.data_ptr(), n.value) == _lib.ERR_UNSUPPORTED
+    assert lib.pi05_bind(h, ptrs, 128, 1, actions.data_ptr(), ws.data_ptr(), n.value - 1) == _lib.ERR_ARGUMENT
+    assert lib.pi05_bind(h, ptrs, 128, 1, actions.data_ptr(), ws.data_ptr() + 8, n.value) == _lib.ERR_ARGUMENT
+    bad = (ctypes.c_void_p * 25)(*[dev[k].data_ptr() for k in FX.ORDER])
+    bad[3] = None
+    assert lib.pi05_bind(h, bad, 128, 1, actions.data_ptr(), ws.data_ptr(), n.value) == _lib.ERR_ARGUMENT
+    assert lib.pi05_bind(h, ptrs, 128, 1, actions.data_ptr(), ws.data_ptr(), n.value) == _lib.OK
+    assert lib.pi05_launch(h, 11, 18, None, None) == _lib.ERR_ARGUMENT
+    assert lib.pi05_launch(h, 10, 18, None, None) == _lib.OK
+    code, where = ctypes.c_int(), ctypes.c_int()
+    assert lib.pi05_status(h, ctypes.byref(code), ctypes.byref(where)) == _lib.OK and code.value == 0
+    cnt = ctypes.c_ulonglong()
+    assert lib.pi05_launch_count(h, ctypes.byref(cnt)) == _lib.OK and cnt.value == 1
+    assert lib.pi05_destroy(h) == _lib.OK

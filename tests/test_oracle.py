@@ -1,0 +1,82 @@
+"""The CPU oracle against the golden vectors produced by the unmodified reference."""
+import pytest
+import torch
+
+from oracle import pi05_oracle as O
+from pi05_megakernel_b200 import fixture as FX
+from tests.helpers import fingerprints_match, load_full, load_small
+
+
+@pytest.mark.parametrize("name", ["small_gqa1", "small_gqa2", "small_full"])
+def test_small_cases_bit_exact(name):
+    geo, ogeo, inputs, want, exact = load_small(name)
+    assert torch.equal(O.chunk(inputs, ogeo, widen=False), want)      # reference/pi05.py::reference
+    assert torch.equal(O.chunk(inputs, ogeo, widen=True), exact)      # reference/oracle.py::fp32_reference
+
+
+def test_full_geometry_bit_exact():
+    """Full 18-layer, 10-step chunk at prefix 128, seed 7301, inputs regenerated from the seed."""
+    geo, ogeo, seed, mask, fps, want, exact = load_full("full_p128_s7301")
+    inputs = FX.make_inputs(geo, seed, "cpu", "full")
+    if not fingerprints_match(inputs, fps):
+        pytest.skip("this torch build draws different random inputs than the one that made the vectors")
+    assert torch.equal(O.chunk(inputs, ogeo, widen=False), want)
+    assert torch.equal(O.chunk(inputs, ogeo, widen=True), exact)
+
+
+def test_band_follows_reference_formula():
+    """fixture.py:105-120 on hand-made numbers."""
+    exact = torch.tensor([[1.0, -2.0], [0.5, 4.0]])
+    want = exact + torch.tensor([[0.01, 0.0], [0.0, -0.01]])
+    ok = O.band(want, exact + 0.02 * torch.sign(exact) * 0.5, exact)
+    scale = float(exact.double().norm())
+    assert ok["reference_relative_error"] == pytest.approx((2 * 0.01 ** 2) ** 0.5 / scale, rel=1e-5)
+    assert ok["pass"]
+    bad = O.band(want, exact + 0.1, exact)
+    assert not bad["pass"]
+    nan = exact.clone(); nan[0, 0] = float("nan")
+    assert not O.band(want, nan, exact)["pass"]
+
+
+def test_truncated_chunk_prefix_property():
+    """steps/layers truncation: with all steps and layers it is the full chunk."""
+    geo, ogeo, inputs, want, _ = load_small("small_gqa1")
+    assert torch.equal(O.chunk(inputs, ogeo, False, steps=ogeo.steps, layers=ogeo.layers), want)
+    one = O.chunk(inputs, ogeo, False, steps=1, layers=1)
+    assert one.shape == want.shape and not torch.equal(one, want)
+
+
+def test_masked_prefix_tokens_do_not_matter():
+    """Keys the mask excludes must not influence the result; only their count shifts nothing either
+    (positions come from the number of valid tokens)."""
+    geo, ogeo, inputs, want, _ = load_small("small_gqa1")
+    changed = dict(inputs)
+    k = inputs["prefix_k"].clone()
+    k[:, ~inputs["prefix_mask"]] = 7.0
+    changed["prefix_k"] = k
+    assert torch.equal(O.chunk(changed, ogeo, False), want)
+
+
+def test_stage_reference_tracks_the_chunk():
+    """The stage-level schedule (engine rounding points) stays inside the band of the graded schedule
+    over one layer."""
+    geo, ogeo, inputs, _, _ = load_small("small_full")
+    with torch.no_grad():
+        h = torch.nn.functional.linear(inputs["noise"], inputs["action_in_weight"],
+                                       inputs["action_in_bias"]).to(torch.bfloat16)
+        st = O.stages(inputs, ogeo, 0, 0, h)
+        pos, allowed = O.suffix_layout(inputs["prefix_mask"], ogeo.horizon)
+        cond = O.time_condition(inputs, torch.full((1,), 1.0), ogeo.hidden)
+        want = O.expert(inputs, ogeo, h, cond, pos, allowed, False, layers=1)
+        # compare the residual stream after one layer through the final norm of both
+        mod = torch.nn.functional.linear(cond, inputs["final_norm_weight"], inputs["final_norm_bias"])
+        got = O.ada_rms(st["h_out"].to(torch.bfloat16), mod, O._cast(False))[0]
+    assert float((got.float() - want.float()).abs().max()) < 0.1
+    assert float((got.float() - want.float()).norm() / want.float().norm()) < 0.01
+
+
+def test_sol_bytes_match_reference_numbers():
+    """bench.py:63-80: 6,726,352,896 B at prefix 128 and the sweep values."""
+    for prefix, want in ((128, 6_726_352_896), (256, 6_749_945_856), (512, 6_797_131_776), (968, 6_881_181_696)):
+        assert O.sol_bytes(O.Geo(prefix=prefix))["bytes_restream"] == want
+        assert FX.sol(FX.Geometry(prefix=prefix))["bytes_restream"] == want
