@@ -63,22 +63,23 @@ constexpr int TMEM_COLS = 128;     // two 64-column accumulators
 constexpr int OFF_RING = 0;
 constexpr int OFF_STAGE = OFF_RING + NSTG * STAGE_BYTES_ALL;   // epilogue exchange buffer; also the prologue's scratch
 constexpr int OFF_BARS = OFF_STAGE + STAGE_BYTES;
-constexpr int SMEM_BYTES = OFF_BARS + 512 + 1024;          // + barriers + alignment slack
 
-// attention shared-memory layout (row CTAs), all below OFF_STAGE
+// shared-memory layout of the row CTAs (attention + row operations).  It may overlap the prologue's scratch
+// (OFF_STAGE): the prologue is over before a row CTA touches it.
 constexpr int KV_STRIDE = HD + 8;                   // BF16 elements per K/V/Q row (528 B: conflict-free ldmatrix)
 constexpr int KV_STAGE_BYTES = 64 * KV_STRIDE * 2;  // one 64-key chunk of K or of V
-constexpr int P_STRIDE = 64 + 8;
+constexpr int ATT_STAGES = 3;                       // 192 keys resident: all of prefix 128 + the 50 suffix keys
+constexpr int P_STRIDE = ATT_STAGES * 64 + 8;
 constexpr int OFF_KS = 0;
-constexpr int OFF_VS = OFF_KS + 2 * KV_STAGE_BYTES;
-constexpr int OFF_QS = OFF_VS + 2 * KV_STAGE_BYTES;
+constexpr int OFF_VS = OFF_KS + ATT_STAGES * KV_STAGE_BYTES;
+constexpr int OFF_QS = OFF_VS + ATT_STAGES * KV_STAGE_BYTES;
 constexpr int OFF_PS = OFF_QS + 16 * KV_STRIDE * 2;
 constexpr int OFF_RED = OFF_PS + 16 * P_STRIDE * 2;          // float [8][16]
-constexpr int OFF_KVALID = OFF_RED + 8 * 16 * 4;             // uint8 [2][64]
-constexpr int OFF_ROWBUF = OFF_KVALID + 128;                 // row-op scratch: float [2][1024 + 64]
+constexpr int OFF_KVALID = OFF_RED + 8 * 16 * 4;             // uint8 [ATT_STAGES][64]
+constexpr int OFF_ROWBUF = OFF_KVALID + 256;                 // row-op scratch: float [2][1024 + 64]
 constexpr int ATT_SMEM_END = OFF_ROWBUF + 2 * (1024 + 64) * 4;
-static_assert(ATT_SMEM_END <= OFF_STAGE, "attention smem must not reach the prologue scratch");
-static_assert(SMEM_BYTES <= 232448, "over the 227 KB per-CTA limit");
+constexpr int SMEM_BYTES = (ATT_SMEM_END > OFF_BARS + 512 ? ATT_SMEM_END : OFF_BARS + 512) + 1024;   // + alignment slack
+static_assert(SMEM_BYTES <= 232448 - 256, "over the 227 KB per-CTA limit");
 
 // stages of one layer pass, in dependency order
 enum { ST_QKV = 0, ST_ATT = 1, ST_O = 2, ST_RATT = 3, ST_GU = 4, ST_DOWN = 5, ST_RFFN = 6, NSTAGE = 7 };
@@ -114,7 +115,7 @@ struct Params {
   // workspace
   unsigned int* ctrl;      // [0..3] status, [16 + e] event counters
   float *temb, *hid, *cond, *mod, *x, *o_acc, *d_acc;
-  uint32_t* rope;          // [T][128] (cos bf16 | sin bf16 << 16)
+  uint32_t* rope;          // [T/2][128][2]: {cos t, cos t+1}, {sin t, sin t+1} as BF16 pairs
   __nv_bfloat16 *h, *an_attn, *an_ffn, *q, *k, *v, *attn, *act;
   const Unit* sched;       // [grid][MAX_UNITS]
   const int* sched_n;      // [grid]
@@ -350,12 +351,14 @@ __device__ void prologue_tables(const Params& p, int cta, int ncta) {
     const double phase = (double)p.t_steps[s] * (1.0 / period * 2 * 3.141592653589793);
     p.temb[i] = (float)(j < W / 2 ? sin(phase) : cos(phase));
   }
-  for (int i = gtid; i < T * (HD / 2); i += gn) {
-    const int t = i / (HD / 2), j = i % (HD / 2);
+  for (int i = gtid; i < (T / 2) * (HD / 2); i += gn) {
+    // one entry per token pair (t, t + 1) and rotary index j: {cos t, cos t+1} and {sin t, sin t+1} as BF16 pairs
+    const int tp = i / (HD / 2), j = i % (HD / 2);
     const float e = (float)(2 * j) / (float)HD;
     const float inv = 1.0f / (float)pow(10000.0, (double)e);
-    const float phase = (float)(nvalid + t) * inv;
-    p.rope[i] = pack_bf16((float)cos((double)phase), (float)sin((double)phase));
+    const float ph0 = (float)(nvalid + 2 * tp) * inv, ph1 = (float)(nvalid + 2 * tp + 1) * inv;
+    p.rope[2 * i] = pack_bf16((float)cos((double)ph0), (float)cos((double)ph1));
+    p.rope[2 * i + 1] = pack_bf16((float)sin((double)ph0), (float)sin((double)ph1));
   }
   for (int i = gtid; i < T * W; i += gn) { p.o_acc[i] = 0.f; p.d_acc[i] = 0.f; }
 }
@@ -363,13 +366,37 @@ __device__ void prologue_tables(const Params& p, int cta, int ncta) {
 // ------------------------------------------------------------------------------------------- row operations
 enum { ROW_INIT = 0, ROW_ATT = 1, ROW_FFN = 2 };
 
-// Per-token work between GEMMs, two tokens per CTA, 128 threads per token, 8 columns per thread:
+// Modulation values a row operation needs; they depend only on the step and the layer, so they are fetched
+// before the wait for the GEMM that feeds the operation.
+struct RowMod { float gate[8], scale[8], shift[8]; };
+
+__device__ __forceinline__ void row_prefetch(const Params& p, int mode, int step, int layer, RowMod& rm) {
+  const int c0 = (threadIdx.x & 127) * 8;
+  const float* mod_s = p.mod + (size_t)step * NNORM * MODW;
+  int gate_norm, next_norm;
+  if (mode == ROW_ATT) { gate_norm = 2 * layer; next_norm = 2 * layer + 1; }
+  else { gate_norm = 2 * layer + 1; next_norm = (layer + 1 < p.n_layers) ? 2 * layer + 2 : NNORM - 1; }
+  const float* g = mod_s + (size_t)gate_norm * MODW + 2 * W + c0;
+  const float* n = mod_s + (size_t)next_norm * MODW + c0;
+#pragma unroll
+  for (int e = 0; e < 8; e += 4) {
+    const float4 a = *reinterpret_cast<const float4*>(g + e), b = *reinterpret_cast<const float4*>(n + e),
+                 d = *reinterpret_cast<const float4*>(n + W + e);
+    rm.gate[e] = a.x; rm.gate[e + 1] = a.y; rm.gate[e + 2] = a.z; rm.gate[e + 3] = a.w;
+    rm.scale[e] = b.x; rm.scale[e + 1] = b.y; rm.scale[e + 2] = b.z; rm.scale[e + 3] = b.w;
+    rm.shift[e] = d.x; rm.shift[e + 1] = d.y; rm.shift[e + 2] = d.z; rm.shift[e + 3] = d.w;
+  }
+}
+
+// Per-token work between GEMMs, two tokens per CTA, 128 threads per token, 8 columns per thread.  The thread
+// keeps its 8 values of the residual stream h in registers (hn) from one call to the next.
 //   ROW_ATT: h += bf16(bf16(o_acc) * gate_attn); an_ffn = adaRMS_ffn(h)
 //   ROW_FFN: h += bf16(bf16(d_acc) * gate_ffn); then either an_attn = adaRMS_attn[l+1](h), or at the last layer
 //            the step tail: final adaRMS, v = Wout n + b, x += dt v, and (unless it was the last step)
 //            h = bf16(Win x + b), an_attn = adaRMS_attn[0](h) with the next step's modulation.
 //   ROW_INIT: x = noise, h = bf16(Win x + b), an_attn = adaRMS_attn[0](h).
-__device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int step, int layer) {
+__device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int step, int layer, float (&hn)[8],
+                       const RowMod& rm) {
   const int tid = threadIdx.x, lane = tid & 31;
   const int half = tid >> 7, i = tid & 127, wq = (tid >> 5) & 3;
   const int t = unit * 2 + half;
@@ -377,9 +404,7 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
   float* rowbuf = reinterpret_cast<float*>(smem + OFF_ROWBUF) + half * (1024 + 64);
   float* red = rowbuf + 1024;      // [0..3] warp sums, [8..39] x row
   const int bar = 4 + half;
-  const float* mod_s = p.mod + (size_t)step * NNORM * MODW;
 
-  float hn[8];
   auto sumsq = [&](const float (&v)[8]) -> float {
     float ss = 0.f;
 #pragma unroll
@@ -390,19 +415,19 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
     ptx::named_bar_sync(bar, 128);
     return (red[0] + red[1]) + (red[2] + red[3]);
   };
-  auto ada_norm = [&](const float (&v)[8], const float* mod, __nv_bfloat16* dst) {
+  auto ada_norm = [&](const float (&v)[8], const float (&scale)[8], const float (&shift)[8], __nv_bfloat16* dst) {
     const float ss = sumsq(v);
     const float rs = 1.0f / sqrtf(ss * (1.0f / W) + EPS);
     uint32_t o[4];
 #pragma unroll
     for (int e = 0; e < 8; e += 2) {
-      const float a = __fadd_rn(__fmul_rn(__fmul_rn(v[e], rs), __fadd_rn(1.0f, mod[c0 + e])), mod[W + c0 + e]);
-      const float b = __fadd_rn(__fmul_rn(__fmul_rn(v[e + 1], rs), __fadd_rn(1.0f, mod[c0 + e + 1])), mod[W + c0 + e + 1]);
+      const float a = __fadd_rn(__fmul_rn(__fmul_rn(v[e], rs), __fadd_rn(1.0f, scale[e])), shift[e]);
+      const float b = __fadd_rn(__fmul_rn(__fmul_rn(v[e + 1], rs), __fadd_rn(1.0f, scale[e + 1])), shift[e + 1]);
       o[e >> 1] = pack_bf16(a, b);
     }
     *reinterpret_cast<uint4*>(dst + (size_t)t * W + c0) = make_uint4(o[0], o[1], o[2], o[3]);
   };
-  auto store_h = [&](const float (&v)[8]) {
+  auto store_h = [&](const float (&v)[8]) {   // the kernel itself never reads h back; kept for stage-level checks
     uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
     *reinterpret_cast<uint4*>(p.h + (size_t)t * W + c0) = o;
   };
@@ -421,66 +446,59 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
       hn[e] = rb(a + p.ain_b[c0 + e]);
     }
   };
+  auto next_step_norm = [&](int s) {          // attention norm of layer 0 with the modulation of step s
+    const float* m = p.mod + (size_t)s * NNORM * MODW + c0;
+    float sc[8], sh[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { sc[e] = m[e]; sh[e] = m[W + e]; }
+    ada_norm(hn, sc, sh, p.an_attn);
+  };
 
   if (mode == ROW_INIT) {
     if (i < ADIM) { const float xv = p.noise[t * ADIM + i]; p.x[t * ADIM + i] = xv; red[8 + i] = xv; }
     ptx::named_bar_sync(bar, 128);
     action_in();
     store_h(hn);
-    ada_norm(hn, mod_s, p.an_attn);
+    next_step_norm(0);
     return;
   }
 
   // gated residual
   float* acc = (mode == ROW_ATT ? p.o_acc : p.d_acc) + (size_t)t * W + c0;
-  const float* gate = mod_s + (size_t)(2 * layer + (mode == ROW_ATT ? 0 : 1)) * MODW + 2 * W + c0;
   {
-    const float4 a0 = *reinterpret_cast<const float4*>(acc), a1 = *reinterpret_cast<const float4*>(acc + 4);
+    const float4 a0 = __ldcg(reinterpret_cast<const float4*>(acc)), a1 = __ldcg(reinterpret_cast<const float4*>(acc + 4));
     *reinterpret_cast<float4*>(acc) = make_float4(0.f, 0.f, 0.f, 0.f);
     *reinterpret_cast<float4*>(acc + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-    const uint4 hv = *reinterpret_cast<const uint4*>(p.h + (size_t)t * W + c0);
     const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float hold = (e & 1) ? bf16_hi(hw[e >> 1]) : bf16_lo(hw[e >> 1]);
-      hn[e] = rb(hold + rb(rb(av[e]) * rb(gate[e])));
-    }
+    for (int e = 0; e < 8; ++e) hn[e] = rb(hn[e] + rb(rb(av[e]) * rb(rm.gate[e])));
   }
-  if (mode == ROW_ATT) {
-    store_h(hn);
-    ada_norm(hn, mod_s + (size_t)(2 * layer + 1) * MODW, p.an_ffn);
-    return;
-  }
-  if (layer + 1 < p.n_layers) {
-    store_h(hn);
-    ada_norm(hn, mod_s + (size_t)(2 * layer + 2) * MODW, p.an_attn);
-    return;
-  }
+  store_h(hn);
+  if (mode == ROW_ATT) { ada_norm(hn, rm.scale, rm.shift, p.an_ffn); return; }
+  if (layer + 1 < p.n_layers) { ada_norm(hn, rm.scale, rm.shift, p.an_attn); return; }
   // ---- step tail: final norm, action_out, Euler update
   {
-    const float* mod = mod_s + (size_t)(NNORM - 1) * MODW;
     const float ss = sumsq(hn);
     const float rs = 1.0f / sqrtf(ss * (1.0f / W) + EPS);
 #pragma unroll
     for (int e = 0; e < 8; ++e)
-      rowbuf[c0 + e] = rb(__fadd_rn(__fmul_rn(__fmul_rn(hn[e], rs), __fadd_rn(1.0f, mod[c0 + e])), mod[W + c0 + e]));
+      rowbuf[c0 + e] = rb(__fadd_rn(__fmul_rn(__fmul_rn(hn[e], rs), __fadd_rn(1.0f, rm.scale[e])), rm.shift[e]));
     ptx::named_bar_sync(bar, 128);
     // warp wq: outputs wq*8 .. wq*8+7
     for (int a = wq * 8; a < wq * 8 + 8; ++a) {
       const float* wr = p.aout_w + (size_t)a * W;
-      float s = 0.f;
+      float sdot = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int k = lane * 4 + j * 128;
         const float4 w4 = *reinterpret_cast<const float4*>(wr + k);
-        s = fmaf(w4.x, rowbuf[k], s); s = fmaf(w4.y, rowbuf[k + 1], s);
-        s = fmaf(w4.z, rowbuf[k + 2], s); s = fmaf(w4.w, rowbuf[k + 3], s);
+        sdot = fmaf(w4.x, rowbuf[k], sdot); sdot = fmaf(w4.y, rowbuf[k + 1], sdot);
+        sdot = fmaf(w4.z, rowbuf[k + 2], sdot); sdot = fmaf(w4.w, rowbuf[k + 3], sdot);
       }
-      for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      for (int o = 16; o; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
       if (lane == 0) {
-        const float vel = s + p.aout_b[a];
-        const float xn = p.x[t * ADIM + a] + p.dt * vel;
+        const float vel = sdot + p.aout_b[a];
+        const float xn = __fadd_rn(p.x[t * ADIM + a], __fmul_rn(p.dt, vel));
         p.x[t * ADIM + a] = xn;
         red[8 + a] = xn;
         if (step + 1 == p.n_steps) p.actions[t * ADIM + a] = xn;
@@ -490,20 +508,21 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
     if (step + 1 < p.n_steps) {
       action_in();
       store_h(hn);
-      ada_norm(hn, p.mod + (size_t)(step + 1) * NNORM * MODW, p.an_attn);
-    } else {
-      store_h(hn);
+      next_step_norm(step + 1);
     }
   }
 }
 
 // ------------------------------------------------------------------------------------------- attention
-// 16 query rows (2 tokens x 8 heads, all sharing the one KV head) against [prefix ; suffix] keys in 64-key chunks.
-// Scores: bf16(q.k) / 16, masked; running max; p = bf16(exp(s - m)); o += p V (FP32); out = bf16(o / sum exp).
+// 16 query rows (2 tokens x 8 heads, all sharing the one KV head) against [prefix ; suffix] keys.  Keys are
+// staged in shared memory in 64-key chunks, three chunks (192 keys) at a time; with a prefix of 128 that is
+// everything, in one pass.  Scores: bf16(q.k) / 16, masked; running max; p = bf16(exp(s - m)); o += p V (FP32);
+// out = bf16(o / sum exp).
 struct AttChunkIssue {
   const Params& p;
   uint8_t* smem;
   int layer, npc;
+  // chunk < npc: prefix keys [64*chunk, ...); chunk == npc: the 50 suffix keys; chunk > npc: nothing (stage off)
   __device__ void operator()(int chunk, int stage) const {
     const int tid = threadIdx.x;
     uint8_t* ks = smem + OFF_KS + stage * KV_STAGE_BYTES;
@@ -512,31 +531,54 @@ struct AttChunkIssue {
     const bool is_prefix = chunk < npc;
     const __nv_bfloat16* ksrc = is_prefix ? p.prefix_k + ((size_t)layer * p.prefix + (size_t)chunk * 64) * HD : p.k;
     const __nv_bfloat16* vsrc = is_prefix ? p.prefix_v + ((size_t)layer * p.prefix + (size_t)chunk * 64) * HD : p.v;
-    const int nrows = is_prefix ? min(64, p.prefix - chunk * 64) : T;
+    const int nrows = chunk > npc ? 0 : (is_prefix ? min(64, p.prefix - chunk * 64) : T);
     if (tid < 64) {
       uint8_t ok = 0;
       if (tid < nrows) ok = is_prefix ? (p.prefix_mask[chunk * 64 + tid] ? 1 : 0) : 1;
       kvalid[tid] = ok;
     }
-    // 64 rows x 32 16-byte pieces for K, then the same for V
-    for (int idx = tid; idx < 2 * 64 * 32; idx += THREADS) {
-      const int isv = idx >= 64 * 32;
-      const int r = (idx >> 5) & 63, cidx = idx & 31;
-      uint8_t* dst = (isv ? vs : ks) + r * (KV_STRIDE * 2) + cidx * 16;
-      if (r < nrows) ptx::cp_async_16(ptx::smem_u32(dst), (isv ? vsrc : ksrc) + (size_t)r * HD + cidx * 8);
-      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    if (nrows > 0) {
+      // 64 rows x 32 16-byte pieces for K, then the same for V; rows past the end are zero-filled
+      for (int idx = tid; idx < 2 * 64 * 32; idx += THREADS) {
+        const int isv = idx >= 64 * 32;
+        const int r = (idx >> 5) & 63, cidx = idx & 31;
+        uint8_t* dst = (isv ? vs : ks) + r * (KV_STRIDE * 2) + cidx * 16;
+        if (r < nrows) ptx::cp_async_16(ptx::smem_u32(dst), (isv ? vsrc : ksrc) + (size_t)r * HD + cidx * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
     }
     ptx::cp_async_commit();
   }
 };
 
-__device__ void attention_unit(const Params& p, uint8_t* smem, int unit, const AttChunkIssue& issue) {
+// S = Q K^T for this warp's 8 keys of one stage (two interleaved accumulation chains).
+__device__ __forceinline__ void att_qk(uint32_t qs, uint32_t ks, int warp, int lane, float (&s4)[4]) {
+  float e[4] = {0.f, 0.f, 0.f, 0.f}, o[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t qaddr0 = qs + ((lane & 15) * KV_STRIDE + (lane >> 4) * 8) * 2;
+  const uint32_t kaddr0 = ks + ((warp * 8 + (lane & 7)) * KV_STRIDE + (lane >> 3) * 8) * 2;
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; kk += 2) {
+    uint32_t a0, a1, a2, a3, a4, a5, a6, a7, b0, b1, b2, b3;
+    ptx::ldmatrix_x4(qaddr0 + kk * 32, a0, a1, a2, a3);
+    ptx::ldmatrix_x4(qaddr0 + kk * 32 + 32, a4, a5, a6, a7);
+    ptx::ldmatrix_x4(kaddr0 + kk * 32, b0, b1, b2, b3);
+    ptx::mma_16816(e, a0, a1, a2, a3, b0, b1);
+    ptx::mma_16816(o, a4, a5, a6, a7, b2, b3);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s4[i] = e[i] + o[i];
+}
+
+// `first_pending`: the cp.async groups of the first three chunks are still in flight, committed in the order
+// [chunks that were prefetched ...][Q][the rest]; n_late = how many of the three stages were issued after Q.
+__device__ void attention_unit(const Params& p, uint8_t* smem, int unit, const AttChunkIssue& issue, int n_late, bool tr) {
   const int npc = issue.npc;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, qd = lane & 3;
   const int nchunks = npc + 1;
   const uint32_t qs = ptx::smem_u32(smem + OFF_QS), ps = ptx::smem_u32(smem + OFF_PS);
   float* red = reinterpret_cast<float*>(smem + OFF_RED);
+  const float NEG = -INFINITY;
 
   float m_lo = -1e30f, m_hi = -1e30f, l_lo = 0.f, l_hi = 0.f;
   float o[4][4];
@@ -545,30 +587,42 @@ __device__ void attention_unit(const Params& p, uint8_t* smem, int unit, const A
 #pragma unroll
     for (int b = 0; b < 4; ++b) o[a][b] = 0.f;
 
-  for (int c = 0; c < nchunks; ++c) {
-    const int stage = c & 1;
-    const uint32_t ks = ptx::smem_u32(smem + OFF_KS + stage * KV_STAGE_BYTES);
-    const uint32_t vs = ptx::smem_u32(smem + OFF_VS + stage * KV_STAGE_BYTES);
-    const uint8_t* kvalid = smem + OFF_KVALID + stage * 64;
-    // ---- S = Q K^T for this warp's 8 keys
-    float s4[4] = {0.f, 0.f, 0.f, 0.f};
-    const int kb = warp * 8;
-#pragma unroll 4
-    for (int kk = 0; kk < HD / 16; kk += 2) {
-      uint32_t a0, a1, a2, a3, a4, a5, a6, a7, b0, b1, b2, b3;
-      const uint32_t qaddr = qs + ((lane & 15) * KV_STRIDE + kk * 16 + (lane >> 4) * 8) * 2;
-      ptx::ldmatrix_x4(qaddr, a0, a1, a2, a3);
-      ptx::ldmatrix_x4(qaddr + 32, a4, a5, a6, a7);
-      const uint32_t kaddr = ks + ((kb + (lane & 7)) * KV_STRIDE + kk * 16 + (lane >> 3) * 8) * 2;
-      ptx::ldmatrix_x4(kaddr, b0, b1, b2, b3);
-      ptx::mma_16816(s4, a0, a1, a2, a3, b0, b1);
-      ptx::mma_16816(s4, a4, a5, a6, a7, b2, b3);
+  for (int c0 = 0; c0 < nchunks; c0 += ATT_STAGES) {
+    const int nst = min(ATT_STAGES, nchunks - c0);
+    float sc[ATT_STAGES][4];
+    // ---- scores; in the first pass the stages issued before Q can be used while the late ones are still landing
+    const int early = (c0 == 0) ? nst - n_late : nst;
+    if (c0 == 0) {
+      if (n_late == 2) ptx::cp_async_wait<2>(); else if (n_late == 1) ptx::cp_async_wait<1>(); else ptx::cp_async_wait<0>();
+    } else {
+      ptx::cp_async_wait<0>();
     }
-    const bool v0 = kvalid[kb + 2 * qd] != 0, v1 = kvalid[kb + 2 * qd + 1] != 0;
-    const float NEG = -INFINITY;
-    float s_lo0 = v0 ? rb(s4[0]) * 0.0625f : NEG, s_lo1 = v1 ? rb(s4[1]) * 0.0625f : NEG;
-    float s_hi0 = v0 ? rb(s4[2]) * 0.0625f : NEG, s_hi1 = v1 ? rb(s4[3]) * 0.0625f : NEG;
-    float cm_lo = fmaxf(s_lo0, s_lo1), cm_hi = fmaxf(s_hi0, s_hi1);
+    __syncthreads();
+    if (tr && c0 == 0) p.stamps[224] = globaltimer();
+#pragma unroll
+    for (int j = 0; j < ATT_STAGES; ++j)
+      if (j < early) att_qk(qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
+    if (early < nst) {
+      ptx::cp_async_wait<0>();
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < ATT_STAGES; ++j)
+        if (j >= early && j < nst) att_qk(qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
+    }
+    if (tr && c0 == 0) p.stamps[225] = globaltimer();
+    // ---- mask, chunk max
+    float cm_lo = NEG, cm_hi = NEG;
+#pragma unroll
+    for (int j = 0; j < ATT_STAGES; ++j) {
+      if (j < nst) {
+        const uint8_t* kvalid = smem + OFF_KVALID + j * 64 + warp * 8 + 2 * qd;
+        const bool v0 = kvalid[0] != 0, v1 = kvalid[1] != 0;
+        sc[j][0] = v0 ? rb(sc[j][0]) * 0.0625f : NEG; sc[j][1] = v1 ? rb(sc[j][1]) * 0.0625f : NEG;
+        sc[j][2] = v0 ? rb(sc[j][2]) * 0.0625f : NEG; sc[j][3] = v1 ? rb(sc[j][3]) * 0.0625f : NEG;
+        cm_lo = fmaxf(cm_lo, fmaxf(sc[j][0], sc[j][1]));
+        cm_hi = fmaxf(cm_hi, fmaxf(sc[j][2], sc[j][3]));
+      }
+    }
     cm_lo = fmaxf(cm_lo, __shfl_xor_sync(0xffffffffu, cm_lo, 1));
     cm_lo = fmaxf(cm_lo, __shfl_xor_sync(0xffffffffu, cm_lo, 2));
     cm_hi = fmaxf(cm_hi, __shfl_xor_sync(0xffffffffu, cm_hi, 1));
@@ -581,47 +635,55 @@ __device__ void attention_unit(const Params& p, uint8_t* smem, int unit, const A
       mn_lo = fmaxf(mn_lo, red[w8 * 16 + g]);
       mn_hi = fmaxf(mn_hi, red[w8 * 16 + g + 8]);
     }
-    const float al_lo = expf(m_lo - mn_lo), al_hi = expf(m_hi - mn_hi);
+    const float al_lo = __expf(m_lo - mn_lo), al_hi = __expf(m_hi - mn_hi);
     m_lo = mn_lo; m_hi = mn_hi;
-    const float p00 = expf(s_lo0 - mn_lo), p01 = expf(s_lo1 - mn_lo);
-    const float p10 = expf(s_hi0 - mn_hi), p11 = expf(s_hi1 - mn_hi);
-    l_lo = l_lo * al_lo + (p00 + p01);
-    l_hi = l_hi * al_hi + (p10 + p11);
-    {
-      uint8_t* pbase = smem + OFF_PS;
-      *reinterpret_cast<uint32_t*>(pbase + (g * P_STRIDE + kb + 2 * qd) * 2) = pack_bf16(p00, p01);
-      *reinterpret_cast<uint32_t*>(pbase + ((g + 8) * P_STRIDE + kb + 2 * qd) * 2) = pack_bf16(p10, p11);
-    }
+    l_lo *= al_lo; l_hi *= al_hi;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) { o[nt][0] *= al_lo; o[nt][1] *= al_lo; o[nt][2] *= al_hi; o[nt][3] *= al_hi; }
+#pragma unroll
+    for (int j = 0; j < ATT_STAGES; ++j) {
+      if (j < nst) {
+        const float p00 = __expf(sc[j][0] - mn_lo), p01 = __expf(sc[j][1] - mn_lo);
+        const float p10 = __expf(sc[j][2] - mn_hi), p11 = __expf(sc[j][3] - mn_hi);
+        l_lo += p00 + p01;
+        l_hi += p10 + p11;
+        uint8_t* pbase = smem + OFF_PS + (j * 64 + warp * 8 + 2 * qd) * 2;
+        *reinterpret_cast<uint32_t*>(pbase + g * P_STRIDE * 2) = pack_bf16(p00, p01);
+        *reinterpret_cast<uint32_t*>(pbase + (g + 8) * P_STRIDE * 2) = pack_bf16(p10, p11);
+      }
+    }
     __syncthreads();
+    if (tr && c0 == 0) p.stamps[226] = globaltimer();
     // ---- O += P V for this warp's 32 output dims
     const int db = warp * 32;
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-      uint32_t a0, a1, a2, a3, r0, r1, r2, r3, r4, r5, r6, r7;
-      ptx::ldmatrix_x4(ps + ((lane & 15) * P_STRIDE + kk * 16 + (lane >> 4) * 8) * 2, a0, a1, a2, a3);
-      const uint32_t vaddr = vs + ((kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KV_STRIDE + db + (lane >> 4) * 8) * 2;
-      ptx::ldmatrix_x4_trans(vaddr, r0, r1, r2, r3);
-      ptx::ldmatrix_x4_trans(vaddr + 32, r4, r5, r6, r7);
-      ptx::mma_16816(o[0], a0, a1, a2, a3, r0, r1);
-      ptx::mma_16816(o[1], a0, a1, a2, a3, r2, r3);
-      ptx::mma_16816(o[2], a0, a1, a2, a3, r4, r5);
-      ptx::mma_16816(o[3], a0, a1, a2, a3, r6, r7);
+    for (int j = 0; j < ATT_STAGES; ++j) {
+      if (j < nst) {
+        const uint32_t vs = ptx::smem_u32(smem + OFF_VS + j * KV_STAGE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          uint32_t a0, a1, a2, a3, r0, r1, r2, r3, r4, r5, r6, r7;
+          ptx::ldmatrix_x4(ps + ((lane & 15) * P_STRIDE + j * 64 + kk * 16 + (lane >> 4) * 8) * 2, a0, a1, a2, a3);
+          const uint32_t vaddr = vs + ((kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KV_STRIDE + db + (lane >> 4) * 8) * 2;
+          ptx::ldmatrix_x4_trans(vaddr, r0, r1, r2, r3);
+          ptx::ldmatrix_x4_trans(vaddr + 32, r4, r5, r6, r7);
+          ptx::mma_16816(o[0], a0, a1, a2, a3, r0, r1);
+          ptx::mma_16816(o[1], a0, a1, a2, a3, r2, r3);
+          ptx::mma_16816(o[2], a0, a1, a2, a3, r4, r5);
+          ptx::mma_16816(o[3], a0, a1, a2, a3, r6, r7);
+        }
+      }
     }
-    __syncthreads();   // P, red and this K/V stage may be overwritten from here on
-    if (c + 2 < nchunks) {
-      // refill this stage with chunk c + 2, then make sure chunk c + 1 has landed
-      issue(c + 2, stage);
-      ptx::cp_async_wait<1>();
-    } else {
-      ptx::cp_async_wait<0>();
+    if (tr && c0 == 0) p.stamps[227] = globaltimer();
+    if (c0 + ATT_STAGES < nchunks) {
+      __syncthreads();   // every warp is done with P and these K/V stages
+      for (int j = 0; j < ATT_STAGES; ++j) issue(c0 + ATT_STAGES + j, j);
     }
-    __syncthreads();
   }
   // ---- normalise and store
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  __syncthreads();   // red[] still holds the last maxima
   if (qd == 0) { red[warp * 16 + g] = l_lo; red[warp * 16 + g + 8] = l_hi; }
   __syncthreads();
   float tl_lo = 0.f, tl_hi = 0.f;
@@ -855,16 +917,22 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
             const int d = j + (hi ? 128 : 0);
             __nv_bfloat16* dst = isq ? p.q + (un.tile >> 1) * HD + d : p.k + d;
             const int ld = isq ? QD : HD;
-            const uint32_t* __restrict__ rope = p.rope + j;
-            uint32_t cs[T];
+            // packed BF16 arithmetic on token pairs: every product and the sum are rounded to BF16, as the
+            // reference's BF16 tensor ops do (rotate_half: first half x*cos - y*sin, second half y*cos + x*sin)
+            const uint2* __restrict__ rope = reinterpret_cast<const uint2*>(p.rope) + j;
+            uint2 cs[T / 2];
 #pragma unroll
-            for (int t = 0; t < T; ++t) cs[t] = __ldcg(rope + t * (HD / 2));   // all loads in flight before the stores
+            for (int tp = 0; tp < T / 2; ++tp) cs[tp] = __ldcg(rope + tp * (HD / 2));   // all loads in flight first
 #pragma unroll
-            for (int t = 0; t < T; ++t) {
-              const float x = (t & 1) ? bf16_hi(pk[t >> 1]) : bf16_lo(pk[t >> 1]);
-              const float y = (t & 1) ? bf16_hi(po[t >> 1]) : bf16_lo(po[t >> 1]);
-              const float rot = hi ? y : -y;                       // rotate_half: (-x2, x1)
-              dst[(size_t)t * ld] = __float2bfloat16_rn(rb(x * bf16_lo(cs[t])) + rb(rot * bf16_hi(cs[t])));
+            for (int tp = 0; tp < T / 2; ++tp) {
+              const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&pk[tp]);
+              const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&po[tp]);
+              const __nv_bfloat162 co = *reinterpret_cast<const __nv_bfloat162*>(&cs[tp].x);
+              const __nv_bfloat162 si = *reinterpret_cast<const __nv_bfloat162*>(&cs[tp].y);
+              const __nv_bfloat162 rot = hi ? y : __hneg2(y);
+              const __nv_bfloat162 out = __hadd2_rn(__hmul2_rn(x, co), __hmul2_rn(rot, si));   // _rn: no contraction into FMA
+              dst[(size_t)(2 * tp) * ld] = __low2bfloat16(out);
+              dst[(size_t)(2 * tp + 1) * ld] = __high2bfloat16(out);
             }
           } else {
             __nv_bfloat16* dst = p.v + (un.tile - 18) * 128 + et;
@@ -900,7 +968,7 @@ __device__ void cta_signal(const Params& p, int ev) {
   if (threadIdx.x == 0 && ev != p.drop_event) signal_event(p.ctrl + 16 + ev);
 }
 
-__device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit) {
+__device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, float (&hn)[8]) {
   const int npass = p.n_steps * p.n_layers;
   const int npc = (p.prefix + 63) / 64;
   const bool stamp = p.stamps != nullptr && unit == 0 && threadIdx.x == 0;
@@ -910,11 +978,11 @@ __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit) 
     // ---- attention
     if (pass * NSTAGE + ST_ATT >= p.max_stage) return;
     AttChunkIssue issue{p, smem, layer, npc};
-    issue(0, 0);                       // prefix chunks do not depend on this layer's QKV: fetch before waiting
-    if (npc >= 2) issue(1, 1);
+    // prefix chunks do not depend on this layer's QKV: fetch them before waiting
+    const int nearly = min(npc, ATT_STAGES);
+    for (int j = 0; j < nearly; ++j) issue(j, j);
     if (!cta_wait_event(p, c, EV_QKV, p.n_units[G_QKV] * (pass + 1), pass * NSTAGE + ST_ATT)) return;
     if (stamp && sbase + ST_QKV < 64) p.stamps[sbase + ST_QKV] = globaltimer();
-    if (npc < 2) issue(1, 1);          // chunk 1 is the suffix chunk
     {
       const __nv_bfloat16* qsrc = p.q + (size_t)unit * 2 * QD;
       for (int idx = threadIdx.x; idx < 16 * 32; idx += THREADS) {
@@ -922,25 +990,33 @@ __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit) 
         ptx::cp_async_16(ptx::smem_u32(smem + OFF_QS + r * (KV_STRIDE * 2) + cidx * 16), qsrc + (size_t)r * HD + cidx * 8);
       }
       ptx::cp_async_commit();
-      ptx::cp_async_wait<0>();
-      __syncthreads();
     }
-    attention_unit(p, smem, unit, issue);
+    const int nfirst = min(npc + 1, ATT_STAGES);
+    for (int j = nearly; j < nfirst; ++j) issue(j, j);    // the suffix chunk, if it belongs to the first three
+    const bool tr = stamp && pass == 1;
+    attention_unit(p, smem, unit, issue, nfirst - nearly, tr);
+    if (tr) p.stamps[228] = globaltimer();
     cta_signal(p, EV_ATT);
+    if (tr) p.stamps[229] = globaltimer();
     if (stamp && sbase + ST_ATT < 64) p.stamps[sbase + ST_ATT] = globaltimer();
     // ---- residual + norm after the O projection
     if (pass * NSTAGE + ST_RATT >= p.max_stage) return;
+    RowMod rm;
+    row_prefetch(p, ROW_ATT, step, layer, rm);
     if (!cta_wait_event(p, c, EV_O, p.n_units[G_O] * (pass + 1), pass * NSTAGE + ST_RATT)) return;
     if (stamp && sbase + ST_O < 64) p.stamps[sbase + ST_O] = globaltimer();
-    row_op(p, smem, unit, ROW_ATT, step, layer);
+    row_op(p, smem, unit, ROW_ATT, step, layer, hn, rm);
+    if (tr) p.stamps[231] = globaltimer();
     ptx::fence_proxy_async_global();
     cta_signal(p, EV_ANF);
+    if (tr) p.stamps[232] = globaltimer();
     if (stamp && sbase + ST_RATT < 64) p.stamps[sbase + ST_RATT] = globaltimer();
     // ---- residual + norm (or step tail) after the down projection
     if (pass * NSTAGE + ST_RFFN >= p.max_stage) return;
+    row_prefetch(p, ROW_FFN, step, layer, rm);
     if (!cta_wait_event(p, c, EV_DOWN, p.n_units[G_DOWN] * (pass + 1), pass * NSTAGE + ST_RFFN)) return;
     if (stamp && sbase + ST_DOWN < 64) p.stamps[sbase + ST_DOWN] = globaltimer();
-    row_op(p, smem, unit, ROW_FFN, step, layer);
+    row_op(p, smem, unit, ROW_FFN, step, layer, hn, rm);
     ptx::fence_proxy_async_global();
     cta_signal(p, EV_ANA);
     if (stamp && sbase + ST_RFFN < 64) p.stamps[sbase + ST_RFFN] = globaltimer();
@@ -1021,11 +1097,13 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
       }
     } else {
       const int unit = cta - p.n_gemm_ctas;
-      row_op(p, smem, unit, ROW_INIT, 0, 0);
+      float hn[8];
+      RowMod none;
+      row_op(p, smem, unit, ROW_INIT, 0, 0, hn, none);
       ptx::fence_proxy_async_global();
       cta_signal(p, EV_ANA);
       if (stamp) p.stamps[5] = globaltimer();
-      row_cta(p, c, smem, unit);
+      row_cta(p, c, smem, unit, hn);
     }
   } else if (is_gemm && warp == 0 && lane == 0) {
     s_issued = prod.it;
@@ -1162,7 +1240,7 @@ Tp* region_ptr(const pi05_engine* h, const char* name) {
 // Static work schedule: which CTA runs which 128-row weight tile over which range of 128-wide K stages.
 //   gate/up: 64 tiles (64 gate rows + the matching 64 up rows), full K, one per CTA 0..63
 //   QKV:     20 tiles (16 q, 2 k, 2 v), full K, one per CTA 64..83
-//   O, down: 8 row tiles each, K split in contiguous runs over the remaining GEMM CTAs
+//   O, down: 8 row tiles each, K split in contiguous runs over all GEMM CTAs (partial sums meet in L2)
 bool build_schedule(pi05_engine* h) {
   const int ng = h->n_gemm;
   if (ng < 64 + 20 + 8) return false;
@@ -1170,18 +1248,14 @@ bool build_schedule(pi05_engine* h) {
   h->sched_n.assign(h->grid, 0);
   std::vector<std::vector<Unit>> per(h->grid);
   for (int u = 0; u < 20; ++u) per[64 + u].push_back(Unit{G_QKV, u, 0, W / KSTAGE});
-  const int od0 = 84, nod = ng - od0;
-  auto split = [&](int gemm, int tiles, int atoms_per_tile) {
-    const int total = tiles * atoms_per_tile;
-    for (int j = 0; j < nod; ++j) {
-      int a0 = (int)((long long)total * j / nod), a1 = (int)((long long)total * (j + 1) / nod);
-      while (a0 < a1) {
-        const int tile = a0 / atoms_per_tile, k0 = a0 % atoms_per_tile;
-        const int n = std::min(a1 - a0, atoms_per_tile - k0);
-        per[od0 + j].push_back(Unit{gemm, tile, k0, n});
-        a0 += n;
+  // every row tile gets the same number of CTAs and no CTA straddles two tiles (one unit, one epilogue per CTA)
+  const int per_tile = ng / (W / 128);
+  auto split = [&](int gemm, int tiles, int stages_per_tile) {
+    for (int t = 0; t < tiles; ++t)
+      for (int j = 0; j < per_tile; ++j) {
+        const int a0 = stages_per_tile * j / per_tile, a1 = stages_per_tile * (j + 1) / per_tile;
+        if (a1 > a0) per[t * per_tile + j].push_back(Unit{gemm, t, a0, a1 - a0});
       }
-    }
   };
   split(G_O, W / 128, QD / KSTAGE);
   for (int u = 0; u < 64; ++u) per[u].push_back(Unit{G_GU, u, 0, W / KSTAGE});

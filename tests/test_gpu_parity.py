@@ -3,8 +3,10 @@
 Tolerances: the engine's result must sit inside the reference harness's band (fixture.py:105-120): error
 against the FP32 oracle <= 2x the BF16 reference's own error + rtol 0.003 (relative L2), and max-abs <=
 2x reference max-abs + atol 0.003 + 0.003 * max|exact|.  Stage checks compare single stages computed from
-the engine's own inputs to that stage, where only summation order differs: BF16 buffers within 2 BF16 ulps
-(relative 2^-7 of the value scale), FP32 accumulators within 1e-4 relative L2.
+the engine's own inputs to that stage, where only summation order differs: BF16 buffers within 1e-3 relative L2
+(a BF16 ulp is 2^-8 relative), FP32 accumulators within 1e-4 relative L2.  Split-K partial sums meet in FP32
+atomics, so two launches may differ in the last bit of an accumulator; values derived from an accumulator of an
+earlier launch are therefore compared to one BF16 ulp, not bit for bit.
 """
 import ctypes
 
@@ -46,6 +48,22 @@ def _rel(got, want):
     return float((got - want).norm() / want.norm().clamp_min(1e-30))
 
 
+def _rope_tables(arm):
+    """cos / sin [50, 128] BF16 from the engine's table, stored as [25 token pairs][128][{cos t, cos t+1}, {sin ..}]."""
+    raw = arm.region("rope", torch.bfloat16, (25, 128, 2, 2)).clone()
+    cos = raw[:, :, 0, :].permute(0, 2, 1).reshape(50, 128)
+    sin = raw[:, :, 1, :].permute(0, 2, 1).reshape(50, 128)
+    return cos, sin
+
+
+def _assert_one_ulp(got, want):
+    """BF16 values that may differ by one unit in the last place of the largest operand (the sum h + delta can
+    cancel, so the unit is taken from the tensor's scale) and differ in at most 1 % of the places."""
+    diff = (got - want).abs()
+    assert float(diff.max()) <= 2 ** -7 * float(want.abs().max())
+    assert float((diff > 0).float().mean()) < 0.01
+
+
 def test_prologue_tables(case128):
     """Time embedding, time MLP, all 370 modulation vectors, RoPE table, first action_in and norm."""
     geo, ogeo, cpu, dev = case128
@@ -70,9 +88,8 @@ def test_prologue_tables(case128):
     pos, _ = O.suffix_layout(cpu["prefix_mask"], 50)
     inv = 1.0 / (O.ROPE_THETA ** (torch.arange(0, 256, 2, dtype=torch.int64).float() / 256))
     ph = pos.float()[:, None] * inv[None]
-    rope = arm.region("rope", torch.int32, (50, 128)).cpu()
-    rcos = (rope & 0xffff).to(torch.int16).view(torch.bfloat16)
-    rsin = ((rope >> 16) & 0xffff).to(torch.int16).view(torch.bfloat16)
+    rcos, rsin = _rope_tables(arm)
+    rcos, rsin = rcos.cpu(), rsin.cpu()
     # cos/sin of phases up to ~180 rad: allow a last-bit difference of the FP32 phase on a few entries
     assert float((rcos.float() - ph.cos().to(torch.bfloat16).float()).abs().max()) <= 2 ** -7
     assert float((rsin.float() - ph.sin().to(torch.bfloat16).float()).abs().max()) <= 2 ** -7
@@ -98,9 +115,8 @@ def test_one_layer_stage_by_stage(case128):
         reg = lambda n, d, s: arm.region(n, d, s).clone()
         if stage == 1:
             an = f(reg("an_attn", torch.bfloat16, (50, 1024)))
-            rope = reg("rope", torch.int32, (50, 128))
-            cos = (rope & 0xffff).to(torch.int16).view(torch.bfloat16).float()
-            sin = ((rope >> 16) & 0xffff).to(torch.int16).view(torch.bfloat16).float()
+            cos, sin = _rope_tables(arm)
+            cos, sin = cos.float(), sin.float()
             cos, sin = torch.cat((cos, cos), -1)[:, None], torch.cat((sin, sin), -1)[:, None]
             rot = lambda x: O.rb(O.rb(x * cos) + O.rb(torch.cat((-x[..., 128:], x[..., :128]), -1) * sin))
             q = rot(O.rb(an @ f(dev["wq"][0]).T).view(50, 8, 256)).reshape(50, 2048)
@@ -127,7 +143,7 @@ def test_one_layer_stage_by_stage(case128):
             mod = reg("mod", torch.float32, (10, 37, 3072))
             hn = O.rb(keep["h"] + O.rb(O.rb(keep["o_acc"]) * O.rb(mod[0, 0, 2048:])))
             got_h = reg("h", torch.bfloat16, (50, 1024))
-            assert torch.equal(f(got_h), hn)
+            _assert_one_ulp(f(got_h), hn)
             an, _ = O.ada_rms(got_h.cpu(), mod[0, 1].cpu(), O._cast(False))
             assert _rel(reg("an_ffn", torch.bfloat16, (50, 1024)).cpu(), an) < 1e-3
             assert float(reg("o_acc", torch.float32, (50, 1024)).abs().max()) == 0.0
@@ -145,7 +161,7 @@ def test_one_layer_stage_by_stage(case128):
             mod = reg("mod", torch.float32, (10, 37, 3072))
             hn = O.rb(keep["h"] + O.rb(O.rb(keep["d_acc"]) * O.rb(mod[0, 1, 2048:])))
             got_h = reg("h", torch.bfloat16, (50, 1024))
-            assert torch.equal(f(got_h), hn)
+            _assert_one_ulp(f(got_h), hn)
             an, _ = O.ada_rms(got_h.cpu(), mod[0, 2].cpu(), O._cast(False))
             assert _rel(reg("an_attn", torch.bfloat16, (50, 1024)).cpu(), an) < 1e-3
     arm.close()
