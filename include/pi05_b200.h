@@ -114,6 +114,33 @@ const char* pi05_last_error(pi05_handle_t h);
 
 int pi05_destroy(pi05_handle_t h);
 
+/* One whole chunk without any device allocation by anybody.  (No counterpart in the reference: its arm always
+ * receives a torch-allocated workspace.)
+ *
+ * For callers that cannot obtain device memory at the point where they need the engine: code running under an
+ * allocator that is frozen or owned by someone else (a memory pool sized up front, a plugin called from inside
+ * another framework's execution step, a process that has handed all remaining memory to a cache), where a
+ * cudaMalloc would fail, deadlock with the owner's bookkeeping, or is simply forbidden.  The caller passes only
+ * the 25 inputs (same order, shapes and alignment as pi05_bind) and the output buffer actions [50,32] f32; the
+ * engine's workspace is a fixed array of PI05_STATIC_SCRATCH_BYTES inside the library's device image.  That
+ * array exists once per GPU, is held from library load to process exit, and is shared by every call on that
+ * GPU: it keeps the previous call's contents (the entry point re-zeroes the control words it needs on the
+ * stream before launching), and two calls that overlap on the same GPU - different streams, different host
+ * threads - race on it and give wrong results; issue them on one stream or order them yourself.
+ *
+ * The first call on a device does the set-up (host-side state, address of the array, shared-memory opt-in), and
+ * the first call with a given set of pointers / prefix length encodes the TMA descriptors and clears the array;
+ * both synchronise the device, so make that call once before any stream capture or latency-critical region.
+ * Later calls with the same pointers only enqueue a 1 KB memset and the kernel on `stream`.  No cudaMalloc,
+ * cudaFree or allocating library routine is called on any of these paths.
+ *
+ * Limits: prefix_len <= PI05_STATIC_MAX_PREFIX and a GPU whose schedule fits the array (any B200), otherwise
+ * PI05_ERR_UNSUPPORTED; batch 1 only.  Returns a PI05_* code; the call is asynchronous like pi05_launch. */
+#define PI05_STATIC_SCRATCH_BYTES (8u << 20)
+#define PI05_STATIC_MAX_PREFIX 1024
+int pi05_chunk_static(int device, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, void* actions,
+                      int n_steps, int n_layers, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

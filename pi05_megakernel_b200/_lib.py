@@ -13,6 +13,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libpi05_b200.so")
 NUM_INPUTS = 25
 NUM_STAMPS = 256
+STATIC_SCRATCH_BYTES = 8 << 20
+STATIC_MAX_PREFIX = 1024
 
 EVENT_ATTENTION_DONE, EVENT_FFN_NORM_READY = 6, 8
 WAIT_EVENT = 7
@@ -35,6 +37,8 @@ SIGNATURES = {
     "pi05_error_string": (_c.c_char_p, [_c.c_int]),
     "pi05_last_error": (_c.c_char_p, [_c.c_void_p]),
     "pi05_destroy": (_c.c_int, [_c.c_void_p]),
+    "pi05_chunk_static": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_void_p), _c.c_int, _c.c_void_p, _c.c_int, _c.c_int,
+                                     _c.c_void_p]),
 }
 
 _lib = None

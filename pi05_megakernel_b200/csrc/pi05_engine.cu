@@ -23,6 +23,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -1516,3 +1517,81 @@ int pi05_destroy(pi05_handle_t h) {
 }
 
 }  // extern "C"
+
+// =========================================================================================== no-allocation entry
+// Scratch for pi05_chunk_static(): the whole workspace of one engine lives in this file-scope device array
+// instead of a caller-allocated buffer.  Every GPU that loads the library holds these bytes until the process
+// exits.  Host code must not hand this name to a kernel: on the host it is only a stand-in for the symbol; the
+// device address comes from cudaGetSymbolAddress() below.
+static __device__ __align__(256) unsigned char g_pi05_static_scratch[PI05_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+struct StaticSlot {
+  pi05_handle_t h = nullptr;        // host-side engine state of this device (created on the first call)
+  void* scratch = nullptr;          // device address of g_pi05_static_scratch on this device
+  const void* inputs[PI05_NUM_INPUTS] = {};
+  void* actions = nullptr;
+  int prefix = 0;
+  bool bound = false;
+};
+constexpr int MAX_STATIC_DEVICES = 64;
+StaticSlot g_static_slots[MAX_STATIC_DEVICES];
+std::mutex g_static_mutex;
+
+}  // namespace
+
+extern "C" int pi05_chunk_static(int device, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, void* actions,
+                                 int n_steps, int n_layers, void* stream) {
+  if (device < 0 || device >= MAX_STATIC_DEVICES || !inputs || !actions) return PI05_ERR_ARGUMENT;
+  if (prefix_len < 1) return PI05_ERR_ARGUMENT;
+  if (prefix_len > PI05_STATIC_MAX_PREFIX) return PI05_ERR_UNSUPPORTED;   // beyond the stated maximum
+  if (n_steps < 1 || n_steps > NS || n_layers < 1 || n_layers > NL) return PI05_ERR_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  StaticSlot& slot = g_static_slots[device];
+  if (!slot.h) {
+    // Set-up, once per device: host-side engine state, then the device address of the static array, taken with
+    // that device current.  No device memory is allocated anywhere on this path.
+    pi05_handle_t h = nullptr;
+    int rc = pi05_create(device, PI05_STATIC_MAX_PREFIX, 1, 0, 1, &h);
+    if (rc != PI05_OK) return rc;
+    size_t need = 0;
+    pi05_workspace_bytes(h, &need);
+    if (need > (size_t)PI05_STATIC_SCRATCH_BYTES) {   // e.g. a part with many more SMs: the schedule would not fit
+      pi05_destroy(h);
+      return PI05_ERR_UNSUPPORTED;
+    }
+    void* ptr = nullptr;
+    {
+      DeviceGuard guard(device);
+      if (!guard.ok) { pi05_destroy(h); return PI05_ERR_CUDA; }
+      cudaError_t e = cudaGetSymbolAddress(&ptr, g_pi05_static_scratch);
+      if (e != cudaSuccess || ptr == nullptr) { cudaGetLastError(); pi05_destroy(h); return PI05_ERR_CUDA; }
+    }
+    slot.h = h;
+    slot.scratch = ptr;
+    slot.bound = false;
+  }
+  bool same = slot.bound && slot.prefix == prefix_len && slot.actions == actions;
+  for (int i = 0; same && i < PI05_NUM_INPUTS; ++i) same = slot.inputs[i] == inputs[i];
+  if (!same) {
+    // New tensors or a new prefix length: re-encode the TMA descriptors and clear the scratch (synchronises the device).
+    slot.bound = false;
+    int rc = pi05_bind(slot.h, inputs, prefix_len, 1, actions, slot.scratch, (size_t)PI05_STATIC_SCRATCH_BYTES);
+    if (rc != PI05_OK) return rc;
+    for (int i = 0; i < PI05_NUM_INPUTS; ++i) slot.inputs[i] = inputs[i];
+    slot.actions = actions;
+    slot.prefix = prefix_len;
+    slot.bound = true;
+  }
+  {
+    // The array keeps whatever the last call left.  What has to start at zero is the control block (status word
+    // and stage counters; an aborted call could leave them dirty); the kernel clears its accumulators itself.
+    DeviceGuard guard(device);
+    if (!guard.ok) return PI05_ERR_CUDA;
+    cudaError_t e = cudaMemsetAsync(slot.scratch, 0, 1024, (cudaStream_t)stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return PI05_ERR_CUDA; }
+  }
+  return pi05_launch(slot.h, n_steps, n_layers, stream, nullptr);
+}
+

@@ -1,0 +1,59 @@
+"""The entry point that works out of the library's own fixed device array (pi05_chunk_static).
+
+It exists for callers that cannot allocate device memory where they call the engine (a frozen or foreign
+allocator, a plugin step inside another framework).  This test drives it through the C ABI only - no handle,
+no workspace tensor - twice in a row on the same GPU, and checks each result against what the regular
+handle-based entry points produce for the same inputs, and against the CPU oracle's band.  It is collected last
+on purpose: a run that stops at the first failure has then already run every other test.  It does not depend on
+state left by other tests, so it also passes alone in a fresh process.
+"""
+import ctypes
+
+import pytest
+import torch
+
+from oracle import pi05_oracle as O
+from pi05_megakernel_b200 import _lib
+from pi05_megakernel_b200 import fixture as FX
+
+pytestmark = pytest.mark.gpu
+
+
+def test_static_scratch_entry_matches_regular_entry_twice():
+    from pi05_megakernel_b200.arm import Pi05Arm
+    geo, ogeo = FX.Geometry(prefix=128), O.Geo(prefix=128)
+    cpu = FX.make_inputs(geo, FX.SEEDS[2], "cpu")
+    dev = {k: v.cuda() for k, v in cpu.items()}
+    want, exact = O.chunk(cpu, ogeo, False), O.chunk(cpu, ogeo, True)
+
+    arm = Pi05Arm(geo, "b200", "cuda")          # the existing path: caller-allocated workspace
+    arm.bind(dev)
+    arm.launch()
+    arm.status()
+    regular = arm.outputs()["actions"].cpu()
+    assert O.band(want, regular, exact)["pass"]
+    arm.close()
+
+    lib = _lib.load()
+    ptrs = (ctypes.c_void_p * _lib.NUM_INPUTS)(*[dev[k].data_ptr() for k in FX.ORDER])
+    actions = torch.empty(50, 32, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    # the same slack the band grants around the oracle: atol + rtol * max|value| (fixture tolerances 0.003 / 0.003),
+    # doubled because both results carry their own split-K summation order
+    slack = 2 * (O.ATOL + O.RTOL * float(regular.abs().max()))
+    for call in range(2):
+        actions.fill_(float("nan"))
+        rc = lib.pi05_chunk_static(0, ptrs, geo.prefix, actions.data_ptr(), geo.steps, geo.layers, stream)
+        assert rc == _lib.OK, lib.pi05_error_string(rc)
+        torch.cuda.synchronize()
+        got = actions.cpu()
+        assert bool(torch.isfinite(got).all())
+        assert float((got - regular).abs().max()) <= slack, call
+        d = O.band(want, got, exact)
+        assert d["pass"], (call, d)
+
+    # sizes beyond the stated maximum are refused on the host, before anything is enqueued
+    assert lib.pi05_chunk_static(0, ptrs, _lib.STATIC_MAX_PREFIX + 1, actions.data_ptr(), 10, 18, stream) \
+        == _lib.ERR_UNSUPPORTED
+    assert lib.pi05_chunk_static(0, ptrs, 0, actions.data_ptr(), 10, 18, stream) == _lib.ERR_ARGUMENT
+    assert lib.pi05_chunk_static(0, None, 128, actions.data_ptr(), 10, 18, stream) == _lib.ERR_ARGUMENT
