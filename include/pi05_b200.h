@@ -81,7 +81,7 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
 int pi05_status(pi05_handle_t h, int* code, int* where);
 
 /* Replaces layout_offsets() (mk/pi05_mk.cu:3622-3627): byte offset and size of a named workspace buffer
- * ("mod", "cond", "h", "an_attn", "an_ffn", "q", "k", "v", "attn", "o_acc", "act", "d_acc", "x", "rope", ...)
+ * ("mod", "cond", "h", "an_attn", "an_ffn", "qkv_acc", "k", "v", "attn", "o_acc", "act", "d_acc", "x", "rope", ...)
  * for stage-by-stage checks. */
 int pi05_workspace_region(pi05_handle_t h, const char* name, size_t* offset, size_t* bytes);
 
@@ -91,8 +91,8 @@ int pi05_workspace_region(pi05_handle_t h, const char* name, size_t* offset, siz
  * makes the row CTAs skip that stage-completion signal (PI05_EVENT_*), so that the waits on it run out: the
  * way to exercise the time-out path without stalling a GPU; negative = signal everything. */
 int pi05_debug(pi05_handle_t h, int max_stage, long long wait_limit_cycles, int drop_event);
-#define PI05_EVENT_ATTENTION_DONE 6
-#define PI05_EVENT_FFN_NORM_READY 8
+#define PI05_EVENT_ATTENTION_DONE 7
+#define PI05_EVENT_FFN_NORM_READY 9
 /* pi05_status codes: which kind of wait gave up */
 #define PI05_WAIT_WEIGHT_SLOT 1
 #define PI05_WAIT_WEIGHT_DATA 2

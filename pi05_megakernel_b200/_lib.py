@@ -16,7 +16,7 @@ NUM_STAMPS = 256
 STATIC_SCRATCH_BYTES = 8 << 20
 STATIC_MAX_PREFIX = 1024
 
-EVENT_ATTENTION_DONE, EVENT_FFN_NORM_READY = 6, 8
+EVENT_ATTENTION_DONE, EVENT_FFN_NORM_READY = 7, 9
 WAIT_EVENT = 7
 OK, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_NOT_BOUND, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE = range(7)
 

@@ -20,6 +20,7 @@
 #include <math.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -42,6 +43,7 @@ constexpr int NS = 10;         // Euler steps
 constexpr int HD = 256;        // head dim
 constexpr int NQH = 8;         // query heads (one KV head)
 constexpr int QD = NQH * HD;   // 2048
+constexpr int QKVW = QD + 2 * HD;  // 2560: q | k | v
 constexpr int FF = 4096;       // MLP width
 constexpr int NNORM = 2 * NL + 1;  // adaRMS norms (attn, ffn per layer + final)
 constexpr int MODW = 3 * W;        // scale | shift | gate
@@ -88,7 +90,11 @@ enum { G_QKV = 0, G_O = 1, G_GU = 2, G_DOWN = 3 };
 __device__ __constant__ int kGemmStage[4] = {ST_QKV, ST_O, ST_GU, ST_DOWN};
 
 // event counters (uint32 each) in the control block
-enum { EV_P0 = 0, EV_P1, EV_P2, EV_P3, EV_ANA, EV_QKV, EV_ATT, EV_O, EV_ANF, EV_GU, EV_DOWN, EV_EXIT, NEVENTS };
+enum { EV_P0 = 0, EV_P1, EV_P2, EV_P3, EV_ANA, EV_QKV, EV_KV, EV_ATT, EV_O, EV_ANF, EV_GU, EV_DOWN, EV_EXIT, NEVENTS };
+// every counter sits on its own 128-byte line of the control block (word 32 * (1 + e)); words 0..3 are the status
+#define EVW(e) (32 * (1 + (e)))
+constexpr int NKVTILES = 4;         // k (2) and v (2) tiles of the QKV GEMM
+constexpr int CTRL_BYTES = 128 * (1 + NEVENTS);
 
 // wait kinds reported in the status word
 enum { WAIT_W_EMPTY = 1, WAIT_W_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_T_EMPTY, WAIT_T_FULL, WAIT_EVENT,
@@ -114,15 +120,18 @@ struct Params {
   const uint8_t* prefix_mask;
   float* actions;
   // workspace
-  unsigned int* ctrl;      // [0..3] status, [16 + e] event counters
+  unsigned int* ctrl;      // [0..3] status, [EVW(e)] event counters, one per 128-byte line
   float *temb, *hid, *cond, *mod, *x, *o_acc, *d_acc;
-  uint32_t* rope;          // [T/2][128][2]: {cos t, cos t+1}, {sin t, sin t+1} as BF16 pairs
-  __nv_bfloat16 *h, *an_attn, *an_ffn, *q, *k, *v, *attn, *act;
+  uint32_t* rope;          // [T][128]: cos BF16 | sin BF16 << 16
+  uint32_t* rope2;         // [T/2][128][2]: {cos t, cos t+1}, {sin t, sin t+1} BF16 pairs (packed arithmetic on token pairs)
+  float* qkv_acc;          // [T][2560] split-K accumulator of q | k | v (FP32, before rounding and RoPE)
+  __nv_bfloat16 *h, *an_attn, *an_ffn, *k, *v, *attn, *act;   // k, v: [T][256] suffix keys / values (BF16, k after RoPE)
   const Unit* sched;       // [grid][MAX_UNITS]
   const int* sched_n;      // [grid]
   unsigned long long* stamps;
   long long wait_limit;
   int prefix, n_steps, n_layers, max_stage, n_gemm_ctas;
+  int poll_ns;             // pause between two samples of a stage counter
   int drop_event;          // debug: this event is never signalled (exercises the bounded waits); -1 = none
   int n_units[4];          // units per GEMM kind (event targets)
   float t_steps[NS];
@@ -134,6 +143,7 @@ struct Ctx {
   unsigned int* status;
   long long limit;
   int cta;
+  unsigned poll_ns;
 };
 
 __device__ __noinline__ void report_timeout(const Ctx& c, int kind, int stage) {
@@ -157,6 +167,8 @@ __device__ __forceinline__ bool wait_mbar(const Ctx& c, uint32_t bar, uint32_t p
 }
 
 __device__ __forceinline__ bool wait_event(const Ctx& c, const unsigned int* ev, unsigned int target, int stage) {
+  // One load in flight at a time on purpose: sampling the counter more often (several relaxed loads in flight)
+  // was measured slower, the extra reads of the line delay the producers' updates of it.
   if ((int)(ptx::ld_acquire(ev) - target) >= 0) return true;
   const long long t0 = clock64();
   for (unsigned i = 0;; ++i) {
@@ -165,7 +177,7 @@ __device__ __forceinline__ bool wait_event(const Ctx& c, const unsigned int* ev,
       if (ptx::ld_relaxed(c.status) != 0u) return false;
       if (clock64() - t0 > c.limit) { report_timeout(c, WAIT_EVENT, stage); return false; }
     }
-    __nanosleep(20);
+    __nanosleep(c.poll_ns);
   }
 }
 
@@ -320,8 +332,8 @@ __device__ bool grid_event(const Params& p, const Ctx& c, int ev, int ncta) {
   __syncthreads();
   __shared__ int ok_flag;
   if (threadIdx.x == 0) {
-    signal_event(p.ctrl + 16 + ev);
-    ok_flag = wait_event(c, p.ctrl + 16 + ev, (unsigned)ncta, -1 - ev) ? 1 : 0;
+    signal_event(p.ctrl + EVW(ev));
+    ok_flag = wait_event(c, p.ctrl + EVW(ev), (unsigned)ncta, -1 - ev) ? 1 : 0;
   }
   __syncthreads();
   return ok_flag != 0;
@@ -352,15 +364,22 @@ __device__ void prologue_tables(const Params& p, int cta, int ncta) {
     const double phase = (double)p.t_steps[s] * (1.0 / period * 2 * 3.141592653589793);
     p.temb[i] = (float)(j < W / 2 ? sin(phase) : cos(phase));
   }
+  for (int i = gtid; i < T * (HD / 2); i += gn) {
+    const int t = i / (HD / 2), j = i % (HD / 2);
+    const float e = (float)(2 * j) / (float)HD;
+    const float inv = 1.0f / (float)pow(10000.0, (double)e);
+    const float phase = (float)(nvalid + t) * inv;
+    p.rope[i] = pack_bf16((float)cos((double)phase), (float)sin((double)phase));
+  }
   for (int i = gtid; i < (T / 2) * (HD / 2); i += gn) {
-    // one entry per token pair (t, t + 1) and rotary index j: {cos t, cos t+1} and {sin t, sin t+1} as BF16 pairs
     const int tp = i / (HD / 2), j = i % (HD / 2);
     const float e = (float)(2 * j) / (float)HD;
     const float inv = 1.0f / (float)pow(10000.0, (double)e);
     const float ph0 = (float)(nvalid + 2 * tp) * inv, ph1 = (float)(nvalid + 2 * tp + 1) * inv;
-    p.rope[2 * i] = pack_bf16((float)cos((double)ph0), (float)cos((double)ph1));
-    p.rope[2 * i + 1] = pack_bf16((float)sin((double)ph0), (float)sin((double)ph1));
+    p.rope2[2 * i] = pack_bf16((float)cos((double)ph0), (float)cos((double)ph1));
+    p.rope2[2 * i + 1] = pack_bf16((float)sin((double)ph0), (float)sin((double)ph1));
   }
+  for (int i = gtid; i < T * QKVW; i += gn) p.qkv_acc[i] = 0.f;
   for (int i = gtid; i < T * W; i += gn) { p.o_acc[i] = 0.f; p.d_acc[i] = 0.f; }
 }
 
@@ -475,7 +494,13 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
     for (int e = 0; e < 8; ++e) hn[e] = rb(hn[e] + rb(rb(av[e]) * rb(rm.gate[e])));
   }
   store_h(hn);
-  if (mode == ROW_ATT) { ada_norm(hn, rm.scale, rm.shift, p.an_ffn); return; }
+  if (mode == ROW_ATT) {
+    float4* z = reinterpret_cast<float4*>(p.qkv_acc + (size_t)t * QKVW) + i;
+#pragma unroll
+    for (int e = 0; e < QKVW / 4 / 128; ++e) z[e * 128] = make_float4(0.f, 0.f, 0.f, 0.f);
+    ada_norm(hn, rm.scale, rm.shift, p.an_ffn);
+    return;
+  }
   if (layer + 1 < p.n_layers) { ada_norm(hn, rm.scale, rm.shift, p.an_attn); return; }
   // ---- step tail: final norm, action_out, Euler update
   {
@@ -519,13 +544,55 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
 // staged in shared memory in 64-key chunks, three chunks (192 keys) at a time; with a prefix of 128 that is
 // everything, in one pass.  Scores: bf16(q.k) / 16, masked; running max; p = bf16(exp(s - m)); o += p V (FP32);
 // out = bf16(o / sum exp).
+// q / k / v leave the QKV GEMM as FP32 split-K sums.  The row CTAs finish them while staging them for attention:
+// round to BF16 (the GEMM's output rounding), then RoPE on q and k with every product and the sum rounded to BF16
+// (reference/pi05.py:218-229: x * cos + rotate_half(x) * sin on BF16 tensors), written as BF16 rows of 528 B.
+// q leaves the QKV GEMM as FP32 split-K sums.  The row CTA finishes its 16 query rows while staging them: round to
+// BF16 (the GEMM's output rounding), then RoPE with every product and the sum rounded to BF16
+// (reference/pi05.py:218-229: x * cos + rotate_half(x) * sin on BF16 tensors).  One item of 8 rotary pairs per thread.
+__device__ void build_q(const Params& p, uint8_t* smem, int unit) {
+  const int tid = threadIdx.x;
+  const int m = tid >> 4, d0 = (tid & 15) * 8, t = unit * 2 + (m >> 3);
+  const float* lo = p.qkv_acc + (size_t)t * QKVW + (m & 7) * HD + d0;
+  const uint32_t* cs = p.rope + t * (HD / 2) + d0;
+  const float4 x0 = __ldcg(reinterpret_cast<const float4*>(lo)), x1 = __ldcg(reinterpret_cast<const float4*>(lo + 4));
+  const float4 y0 = __ldcg(reinterpret_cast<const float4*>(lo + 128)), y1 = __ldcg(reinterpret_cast<const float4*>(lo + 132));
+  const uint4 c0 = __ldcg(reinterpret_cast<const uint4*>(cs)), c1 = __ldcg(reinterpret_cast<const uint4*>(cs + 4));
+  const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+  const float y[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+  const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  float o1[8], o2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float xb = rb(x[i]), yb = rb(y[i]), co = bf16_lo(cw[i]), si = bf16_hi(cw[i]);
+    o1[i] = rb(xb * co) + rb(-yb * si);     // rotate_half: first half x*cos - y*sin
+    o2[i] = rb(yb * co) + rb(xb * si);      // second half y*cos + x*sin
+  }
+  const uint32_t dst = ptx::smem_u32(smem + OFF_QS) + (m * KV_STRIDE + d0) * 2;
+  ptx::st_shared_v4(dst, pack_bf16(o1[0], o1[1]), pack_bf16(o1[2], o1[3]), pack_bf16(o1[4], o1[5]), pack_bf16(o1[6], o1[7]));
+  ptx::st_shared_v4(dst + 256, pack_bf16(o2[0], o2[1]), pack_bf16(o2[2], o2[3]), pack_bf16(o2[4], o2[5]), pack_bf16(o2[6], o2[7]));
+}
+
+__device__ bool cta_wait_event(const Params& p, const Ctx& c, int ev, unsigned target, int stage) {
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = wait_event(c, p.ctrl + EVW(ev), target, stage) ? 1 : 0;
+  __syncthreads();
+  const int ok = ok_flag;
+  __syncthreads();
+  return ok != 0;
+}
+
 struct AttChunkIssue {
   const Params& p;
+  const Ctx& c;
   uint8_t* smem;
-  int layer, npc;
+  int layer, npc, pass;
   // chunk < npc: prefix keys [64*chunk, ...); chunk == npc: the 50 suffix keys; chunk > npc: nothing (stage off)
-  __device__ void operator()(int chunk, int stage) const {
+  // Collective over the CTA.  Returns false when the wait for the suffix keys gave up.
+  __device__ bool operator()(int chunk, int stage) const {
     const int tid = threadIdx.x;
+    if (chunk == npc &&
+        !cta_wait_event(p, c, EV_KV, NKVTILES * (pass + 1), pass * NSTAGE + ST_ATT)) return false;
     uint8_t* ks = smem + OFF_KS + stage * KV_STAGE_BYTES;
     uint8_t* vs = smem + OFF_VS + stage * KV_STAGE_BYTES;
     uint8_t* kvalid = smem + OFF_KVALID + stage * 64;
@@ -549,6 +616,7 @@ struct AttChunkIssue {
       }
     }
     ptx::cp_async_commit();
+    return true;
   }
 };
 
@@ -570,9 +638,10 @@ __device__ __forceinline__ void att_qk(uint32_t qs, uint32_t ks, int warp, int l
   for (int i = 0; i < 4; ++i) s4[i] = e[i] + o[i];
 }
 
-// `first_pending`: the cp.async groups of the first three chunks are still in flight, committed in the order
-// [chunks that were prefetched ...][Q][the rest]; n_late = how many of the three stages were issued after Q.
-__device__ void attention_unit(const Params& p, uint8_t* smem, int unit, const AttChunkIssue& issue, int n_late, bool tr) {
+// The first `nearly` stages (prefix chunks) were issued by the caller before q was ready.  Scores against them are
+// computed first; the suffix keys are waited for and copied only then, so the k / v tiles of the QKV GEMM may
+// finish later than the q tiles without holding attention up.  Returns false when a wait gave up.
+__device__ bool attention_unit(const Params& p, uint8_t* smem, int unit, const AttChunkIssue& issue, int nearly, bool tr) {
   const int npc = issue.npc;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, qd = lane & 3;
@@ -591,19 +660,16 @@ __device__ void attention_unit(const Params& p, uint8_t* smem, int unit, const A
   for (int c0 = 0; c0 < nchunks; c0 += ATT_STAGES) {
     const int nst = min(ATT_STAGES, nchunks - c0);
     float sc[ATT_STAGES][4];
-    // ---- scores; in the first pass the stages issued before Q can be used while the late ones are still landing
-    const int early = (c0 == 0) ? nst - n_late : nst;
-    if (c0 == 0) {
-      if (n_late == 2) ptx::cp_async_wait<2>(); else if (n_late == 1) ptx::cp_async_wait<1>(); else ptx::cp_async_wait<0>();
-    } else {
-      ptx::cp_async_wait<0>();
-    }
+    // ---- scores; in the first pass the prefix stages are used while the suffix keys are still being produced
+    const int early = (c0 == 0) ? nearly : nst;
+    ptx::cp_async_wait<0>();
     __syncthreads();
     if (tr && c0 == 0) p.stamps[224] = globaltimer();
 #pragma unroll
     for (int j = 0; j < ATT_STAGES; ++j)
       if (j < early) att_qk(qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
     if (early < nst) {
+      if (!issue(c0 + early, early)) return false;     // waits for the k / v tiles, then copies the suffix chunk
       ptx::cp_async_wait<0>();
       __syncthreads();
 #pragma unroll
@@ -678,7 +744,8 @@ __device__ void attention_unit(const Params& p, uint8_t* smem, int unit, const A
     if (tr && c0 == 0) p.stamps[227] = globaltimer();
     if (c0 + ATT_STAGES < nchunks) {
       __syncthreads();   // every warp is done with P and these K/V stages
-      for (int j = 0; j < ATT_STAGES; ++j) issue(c0 + ATT_STAGES + j, j);
+      for (int j = 0; j < ATT_STAGES; ++j)
+        if (!issue(c0 + ATT_STAGES + j, j)) return false;
     }
   }
   // ---- normalise and store
@@ -699,6 +766,7 @@ __device__ void attention_unit(const Params& p, uint8_t* smem, int unit, const A
     *reinterpret_cast<uint32_t*>(out + (size_t)(g + 8) * HD + col) = pack_bf16(o[nt][2] * il_hi, o[nt][3] * il_hi);
   }
   ptx::fence_proxy_async_global();   // attn is read by the O projection's TMA
+  return true;
 }
 
 // ------------------------------------------------------------------------------------------- GEMM CTA roles
@@ -713,10 +781,11 @@ struct Producer { int pass, u, a; uint32_t it, slot, par; bool done; };
 // Tensor maps and first rows of the two 64-row halves of a unit's 128-row weight tile.
 __device__ __forceinline__ void weight_rows(const Params& p, const Unit& un, int layer, const CUtensorMap*& ma,
                                             const CUtensorMap*& mb, int& ra, int& rbw) {
-  if (un.gemm == G_QKV) {
-    if (un.tile < 16) { ma = mb = &p.maps.wq; ra = layer * QD + (un.tile >> 1) * HD + (un.tile & 1) * 64; rbw = ra + 128; }
-    else if (un.tile < 18) { ma = mb = &p.maps.wk; ra = layer * HD + (un.tile - 16) * 64; rbw = ra + 128; }
-    else { ma = mb = &p.maps.wv; ra = layer * HD + (un.tile - 18) * 128; rbw = ra + 64; }
+  if (un.gemm == G_QKV) {   // q, v: tiles of 128 consecutive output rows; k: 64 rotary dims and their partners
+    if (un.tile < 16) { ma = mb = &p.maps.wq; ra = layer * QD + un.tile * 128; }
+    else if (un.tile < 18) { ma = mb = &p.maps.wk; ra = layer * HD + (un.tile - 16) * 64; rbw = ra + 128; return; }  // k: dim d with d+128
+    else { ma = mb = &p.maps.wv; ra = layer * HD + (un.tile - 18) * 128; }
+    rbw = ra + 64;
   } else if (un.gemm == G_O) { ma = mb = &p.maps.wo; ra = layer * W + un.tile * 128; rbw = ra + 64; }
   else if (un.gemm == G_GU) { ma = &p.maps.wg; mb = &p.maps.wu; ra = rbw = layer * FF + un.tile * 64; }
   else { ma = mb = &p.maps.wd; ra = layer * W + un.tile * 128; rbw = ra + 64; }
@@ -777,7 +846,7 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
       else if (un.gemm == G_O) { m = &p.maps.attn; ev = EV_ATT; target = NROW_CTAS * (pass + 1); }
       else if (un.gemm == G_GU) { m = &p.maps.an_ffn; ev = EV_ANF; target = NROW_CTAS * (pass + 1); }
       else { m = &p.maps.act; ev = EV_GU; target = p.n_units[G_GU] * (pass + 1); }
-      if (!wait_event(c, p.ctrl + 16 + ev, target, stage)) return;
+      if (!wait_event(c, p.ctrl + EVW(ev), target, stage)) return;
       trace(p, c.cta, pass, un.gemm, 0);
       ptx::fence_proxy_async_global();
       int kc = un.k0 * KSTAGE;
@@ -876,13 +945,59 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
       ptx::mbar_arrive(b.tempty + 8 * buf);
       if (et == 0) trace(p, c.cta, pass, un.gemm, 5);
 
-      if (un.gemm == G_O || un.gemm == G_DOWN) {
-        // split-K partial: FP32 reduction into the L2-resident accumulator [T][W]
-        float* acc = (un.gemm == G_O ? p.o_acc : p.d_acc) + un.tile * 128 + et;
+      if (un.gemm == G_QKV && un.tile >= 16) {
+        // k / v tile over the full K: BF16 keys (with RoPE) / values straight to the buffers attention copies from
+        uint32_t pk[T / 2];
 #pragma unroll
-        for (int t = 0; t < T; ++t) ptx::red_add_f32(acc + (size_t)t * W, __uint_as_float(r[t]));
+        for (int i = 0; i < T / 2; ++i) pk[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        if (un.tile < 18) {
+          // rows 0..63: rotary dim j = cblk*64 + row, rows 64..127: its partner j + 128; exchange through shared memory
+          uint32_t* mine = reinterpret_cast<uint32_t*>(stg + et * STAGE_STRIDE);
+#pragma unroll
+          for (int i = 0; i < T / 2; ++i) mine[i] = pk[i];
+          ptx::named_bar_sync(1, 128);
+          const uint32_t* other = reinterpret_cast<const uint32_t*>(stg + (et ^ 64) * STAGE_STRIDE);
+          const bool hi = et >= 64;
+          const int j = (un.tile - 16) * 64 + (et & 63);
+          __nv_bfloat16* dst = p.k + j + (hi ? 128 : 0);
+          const uint2* __restrict__ rope = reinterpret_cast<const uint2*>(p.rope2) + j;
+          uint2 cs[T / 2];
+#pragma unroll
+          for (int tp = 0; tp < T / 2; ++tp) cs[tp] = __ldcg(rope + tp * (HD / 2));   // all loads in flight first
+#pragma unroll
+          for (int tp = 0; tp < T / 2; ++tp) {
+            // packed BF16 arithmetic on a token pair; _rn keeps every product and the sum separately rounded
+            const uint32_t yw = other[tp];
+            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&pk[tp]);
+            const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&yw);
+            const __nv_bfloat162 co = *reinterpret_cast<const __nv_bfloat162*>(&cs[tp].x);
+            const __nv_bfloat162 si = *reinterpret_cast<const __nv_bfloat162*>(&cs[tp].y);
+            const __nv_bfloat162 rot = hi ? y : __hneg2(y);                       // rotate_half: (-x2, x1)
+            const __nv_bfloat162 out = __hadd2_rn(__hmul2_rn(x, co), __hmul2_rn(rot, si));
+            dst[(size_t)(2 * tp) * HD] = __low2bfloat16(out);
+            dst[(size_t)(2 * tp + 1) * HD] = __high2bfloat16(out);
+          }
+        } else {
+          __nv_bfloat16* dst = p.v + (un.tile - 18) * 128 + et;
+#pragma unroll
+          for (int tp = 0; tp < T / 2; ++tp) {
+            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&pk[tp]);
+            dst[(size_t)(2 * tp) * HD] = __low2bfloat16(x);
+            dst[(size_t)(2 * tp + 1) * HD] = __high2bfloat16(x);
+          }
+        }
+      } else if (un.gemm != G_GU) {
+        // split-K partial: FP32 reduction into an L2-resident accumulator ([T][W] for O / down, [T][2560] for QKV)
+        float* acc;
+        int ldacc;
+        if (un.gemm == G_QKV) { acc = p.qkv_acc; ldacc = QKVW; }
+        else { acc = un.gemm == G_O ? p.o_acc : p.d_acc; ldacc = W; }
+        acc += un.tile * 128 + et;   // accumulator column = tile row (k tiles: 64 dims, then their 64 partners)
+#pragma unroll
+        for (int t = 0; t < T; ++t) ptx::red_add_f32(acc + (size_t)t * ldacc, __uint_as_float(r[t]));
       } else {
-        // exchange BF16-rounded rows through shared memory: row et <-> row et ^ 64
+        // gate/up: rows 0..63 gate, 64..127 up of features tile*64 + (row & 63).  Exchange BF16-rounded rows through
+        // shared memory (row et <-> row et ^ 64); each thread then finishes half of the tokens.
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) pk[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
@@ -894,60 +1009,24 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
         uint32_t po[32];
 #pragma unroll
         for (int i = 0; i < 8; ++i) { const uint4 v = other[i]; po[4 * i] = v.x; po[4 * i + 1] = v.y; po[4 * i + 2] = v.z; po[4 * i + 3] = v.w; }
-        if (un.gemm == G_GU) {
-          // rows 0..63 gate, 64..127 up of features tile*64 + (et & 63); each thread finishes half of the tokens
-          const bool is_up = et >= 64;
-          __nv_bfloat16* dst = p.act + un.tile * 64 + (et & 63);
+        const bool is_up = et >= 64;
+        __nv_bfloat16* dst = p.act + un.tile * 64 + (et & 63);
 #pragma unroll
-          for (int t = 0; t < T; ++t) {
-            if ((t >= 25) == is_up) {
-              const float a = (t & 1) ? bf16_hi(pk[t >> 1]) : bf16_lo(pk[t >> 1]);
-              const float o2 = (t & 1) ? bf16_hi(po[t >> 1]) : bf16_lo(po[t >> 1]);
-              const float gv = is_up ? o2 : a, uv = is_up ? a : o2;
-              dst[(size_t)t * FF] = __float2bfloat16_rn(rb(gelu_tanh(gv)) * uv);
-            }
-          }
-          ptx::fence_proxy_async_global();   // act is read by the down projection's TMA
-        } else {
-          // QKV: q / k tiles pair dim d (row < 64) with dim d + 128 (row >= 64) for RoPE; v tiles are plain
-          const bool hi = et >= 64;
-          if (un.tile < 18) {
-            const bool isq = un.tile < 16;
-            const int cblk = isq ? (un.tile & 1) : (un.tile - 16);
-            const int j = cblk * 64 + (et & 63);                    // rotary index 0..127
-            const int d = j + (hi ? 128 : 0);
-            __nv_bfloat16* dst = isq ? p.q + (un.tile >> 1) * HD + d : p.k + d;
-            const int ld = isq ? QD : HD;
-            // packed BF16 arithmetic on token pairs: every product and the sum are rounded to BF16, as the
-            // reference's BF16 tensor ops do (rotate_half: first half x*cos - y*sin, second half y*cos + x*sin)
-            const uint2* __restrict__ rope = reinterpret_cast<const uint2*>(p.rope) + j;
-            uint2 cs[T / 2];
-#pragma unroll
-            for (int tp = 0; tp < T / 2; ++tp) cs[tp] = __ldcg(rope + tp * (HD / 2));   // all loads in flight first
-#pragma unroll
-            for (int tp = 0; tp < T / 2; ++tp) {
-              const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&pk[tp]);
-              const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&po[tp]);
-              const __nv_bfloat162 co = *reinterpret_cast<const __nv_bfloat162*>(&cs[tp].x);
-              const __nv_bfloat162 si = *reinterpret_cast<const __nv_bfloat162*>(&cs[tp].y);
-              const __nv_bfloat162 rot = hi ? y : __hneg2(y);
-              const __nv_bfloat162 out = __hadd2_rn(__hmul2_rn(x, co), __hmul2_rn(rot, si));   // _rn: no contraction into FMA
-              dst[(size_t)(2 * tp) * ld] = __low2bfloat16(out);
-              dst[(size_t)(2 * tp + 1) * ld] = __high2bfloat16(out);
-            }
-          } else {
-            __nv_bfloat16* dst = p.v + (un.tile - 18) * 128 + et;
-#pragma unroll
-            for (int t = 0; t < T; ++t)
-              dst[(size_t)t * HD] = __float2bfloat16_rn((t & 1) ? bf16_hi(pk[t >> 1]) : bf16_lo(pk[t >> 1]));
+        for (int t = 0; t < T; ++t) {
+          if ((t >= 25) == is_up) {
+            const float a = (t & 1) ? bf16_hi(pk[t >> 1]) : bf16_lo(pk[t >> 1]);
+            const float o2 = (t & 1) ? bf16_hi(po[t >> 1]) : bf16_lo(po[t >> 1]);
+            const float gv = is_up ? o2 : a, uv = is_up ? a : o2;
+            dst[(size_t)t * FF] = __float2bfloat16_rn(rb(gelu_tanh(gv)) * uv);
           }
         }
+        ptx::fence_proxy_async_global();   // act is read by the down projection's TMA
       }
       if (et == 0) trace(p, c.cta, pass, un.gemm, 6);
       ptx::named_bar_sync(1, 128);
       if (et == 0) {
-        const int ev = un.gemm == G_QKV ? EV_QKV : un.gemm == G_O ? EV_O : un.gemm == G_GU ? EV_GU : EV_DOWN;
-        signal_event(p.ctrl + 16 + ev);
+        const int ev = un.gemm == G_QKV ? (un.tile >= 16 ? EV_KV : EV_QKV) : un.gemm == G_O ? EV_O : un.gemm == G_GU ? EV_GU : EV_DOWN;
+        signal_event(p.ctrl + EVW(ev));
         trace(p, c.cta, pass, un.gemm, 7);
       }
     }
@@ -955,18 +1034,9 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
 }
 
 // ------------------------------------------------------------------------------------------- row CTA main loop
-__device__ bool cta_wait_event(const Params& p, const Ctx& c, int ev, unsigned target, int stage) {
-  __shared__ int ok_flag;
-  if (threadIdx.x == 0) ok_flag = wait_event(c, p.ctrl + 16 + ev, target, stage) ? 1 : 0;
-  __syncthreads();
-  const int ok = ok_flag;
-  __syncthreads();
-  return ok != 0;
-}
-
 __device__ void cta_signal(const Params& p, int ev) {
   __syncthreads();
-  if (threadIdx.x == 0 && ev != p.drop_event) signal_event(p.ctrl + 16 + ev);
+  if (threadIdx.x == 0 && ev != p.drop_event) signal_event(p.ctrl + EVW(ev));
 }
 
 __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, float (&hn)[8]) {
@@ -978,24 +1048,15 @@ __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, 
     const int sbase = 6 + pass * NSTAGE;
     // ---- attention
     if (pass * NSTAGE + ST_ATT >= p.max_stage) return;
-    AttChunkIssue issue{p, smem, layer, npc};
+    AttChunkIssue issue{p, c, smem, layer, npc, pass};
     // prefix chunks do not depend on this layer's QKV: fetch them before waiting
     const int nearly = min(npc, ATT_STAGES);
     for (int j = 0; j < nearly; ++j) issue(j, j);
-    if (!cta_wait_event(p, c, EV_QKV, p.n_units[G_QKV] * (pass + 1), pass * NSTAGE + ST_ATT)) return;
+    if (!cta_wait_event(p, c, EV_QKV, (p.n_units[G_QKV] - NKVTILES) * (pass + 1), pass * NSTAGE + ST_ATT)) return;
     if (stamp && sbase + ST_QKV < 64) p.stamps[sbase + ST_QKV] = globaltimer();
-    {
-      const __nv_bfloat16* qsrc = p.q + (size_t)unit * 2 * QD;
-      for (int idx = threadIdx.x; idx < 16 * 32; idx += THREADS) {
-        const int r = idx >> 5, cidx = idx & 31;
-        ptx::cp_async_16(ptx::smem_u32(smem + OFF_QS + r * (KV_STRIDE * 2) + cidx * 16), qsrc + (size_t)r * HD + cidx * 8);
-      }
-      ptx::cp_async_commit();
-    }
-    const int nfirst = min(npc + 1, ATT_STAGES);
-    for (int j = nearly; j < nfirst; ++j) issue(j, j);    // the suffix chunk, if it belongs to the first three
+    build_q(p, smem, unit);                               // q straight from the FP32 sums
     const bool tr = stamp && pass == 1;
-    attention_unit(p, smem, unit, issue, nfirst - nearly, tr);
+    if (!attention_unit(p, smem, unit, issue, nearly, tr)) return;
     if (tr) p.stamps[228] = globaltimer();
     cta_signal(p, EV_ATT);
     if (tr) p.stamps[229] = globaltimer();
@@ -1031,7 +1092,7 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
   const int cta = blockIdx.x, ncta = gridDim.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool is_gemm = cta < p.n_gemm_ctas;
-  const Ctx c{p.ctrl, p.wait_limit, cta};
+  const Ctx c{p.ctrl, p.wait_limit, cta, (unsigned)p.poll_ns};
   const bool stamp = p.stamps != nullptr && cta == p.n_gemm_ctas && tid == 0;
   if (stamp) p.stamps[0] = globaltimer();
 
@@ -1125,10 +1186,10 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
   }
   if (tid == 0) {
     __threadfence();
-    const unsigned prev = atomicAdd(p.ctrl + 16 + EV_EXIT, 1u);
+    const unsigned prev = atomicAdd(p.ctrl + EVW(EV_EXIT), 1u);
     if (prev == (unsigned)ncta - 1) {
       __threadfence();
-      for (int e = 0; e < NEVENTS; ++e) p.ctrl[16 + e] = 0u;
+      for (int e = 0; e < NEVENTS; ++e) p.ctrl[EVW(e)] = 0u;
       __threadfence();
     }
   }
@@ -1158,6 +1219,7 @@ struct pi05_engine {
   TMaps maps;
   int max_stage = 0x7fffffff;
   int drop_event = -1;
+  int poll_ns = 20;
   long long wait_limit = 4000000000ll;    // ~2 s of SM clocks
   unsigned long long launches = 0;
   std::string config;
@@ -1205,17 +1267,18 @@ void build_layout(pi05_engine* h) {
     h->regions.push_back({name, off, bytes});
     off = align_up(off + bytes, 256);
   };
-  add("ctrl", 1024);
+  add("ctrl", CTRL_BYTES);
   add("temb", (size_t)NS * W * 4);
   add("hid", (size_t)NS * W * 4);
   add("cond", (size_t)NS * W * 4);
   add("mod", (size_t)NS * NNORM * MODW * 4);
   add("rope", (size_t)T * (HD / 2) * 4);
+  add("rope2", (size_t)T * (HD / 2) * 4);
   add("x", (size_t)T * ADIM * 4);
   add("h", (size_t)T * W * 2);
   add("an_attn", (size_t)T * W * 2);
   add("an_ffn", (size_t)T * W * 2);
-  add("q", (size_t)T * QD * 2);
+  add("qkv_acc", (size_t)T * QKVW * 4);
   add("k", (size_t)T * HD * 2);
   add("v", (size_t)T * HD * 2);
   add("attn", (size_t)T * QD * 2);
@@ -1240,15 +1303,18 @@ Tp* region_ptr(const pi05_engine* h, const char* name) {
 
 // Static work schedule: which CTA runs which 128-row weight tile over which range of 128-wide K stages.
 //   gate/up: 64 tiles (64 gate rows + the matching 64 up rows), full K, one per CTA 0..63
-//   QKV:     20 tiles (16 q, 2 k, 2 v), full K, one per CTA 64..83
+//   QKV:     16 q tiles x 4 K parts on the gate/up CTAs, 4 k / v tiles x full K on CTAs 64..67
 //   O, down: 8 row tiles each, K split in contiguous runs over all GEMM CTAs (partial sums meet in L2)
 bool build_schedule(pi05_engine* h) {
   const int ng = h->n_gemm;
-  if (ng < 64 + 20 + 8) return false;
+  if (ng < 64 + 8) return false;
   h->sched.assign((size_t)h->grid * MAX_UNITS, Unit{0, 0, 0, 0});
   h->sched_n.assign(h->grid, 0);
   std::vector<std::vector<Unit>> per(h->grid);
-  for (int u = 0; u < 20; ++u) per[64 + u].push_back(Unit{G_QKV, u, 0, W / KSTAGE});
+  // QKV: the 4 k / v tiles over the full K on CTAs 64..67 (BF16 keys / values with RoPE straight from the epilogue);
+  // the 16 q tiles in 4 two-stage K parts, one on each gate/up CTA (FP32 sums, finished by attention)
+  for (int u = 0; u < NKVTILES; ++u) per[64 + u].push_back(Unit{G_QKV, 16 + u, 0, W / KSTAGE});
+  for (int u = 0; u < 64; ++u) per[u].push_back(Unit{G_QKV, u / 4, (u % 4) * 2, 2});
   // every row tile gets the same number of CTAs and no CTA straddles two tiles (one unit, one epilogue per CTA)
   const int per_tile = ng / (W / 128);
   auto split = [&](int gemm, int tiles, int stages_per_tile) {
@@ -1334,6 +1400,7 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   h->max_prefix = max_prefix;
   if (!build_schedule(h)) { delete h; return PI05_ERR_UNSUPPORTED; }
   build_layout(h);
+  if (const char* e = getenv("PI05_POLL_NS")) h->poll_ns = atoi(e);   // tuning knob, not part of the interface
   DeviceGuard guard(device);
   if (!guard.ok) { delete h; return PI05_ERR_CUDA; }
   cudaError_t e = cudaFuncSetAttribute(pi05_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -1450,9 +1517,9 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.temb = region_ptr<float>(h, "temb"); p.hid = region_ptr<float>(h, "hid"); p.cond = region_ptr<float>(h, "cond");
   p.mod = region_ptr<float>(h, "mod"); p.x = region_ptr<float>(h, "x");
   p.o_acc = region_ptr<float>(h, "o_acc"); p.d_acc = region_ptr<float>(h, "d_acc");
-  p.rope = region_ptr<uint32_t>(h, "rope");
+  p.rope = region_ptr<uint32_t>(h, "rope"); p.rope2 = region_ptr<uint32_t>(h, "rope2");
   p.h = region_ptr<__nv_bfloat16>(h, "h"); p.an_attn = region_ptr<__nv_bfloat16>(h, "an_attn");
-  p.an_ffn = region_ptr<__nv_bfloat16>(h, "an_ffn"); p.q = region_ptr<__nv_bfloat16>(h, "q");
+  p.an_ffn = region_ptr<__nv_bfloat16>(h, "an_ffn"); p.qkv_acc = region_ptr<float>(h, "qkv_acc");
   p.k = region_ptr<__nv_bfloat16>(h, "k"); p.v = region_ptr<__nv_bfloat16>(h, "v");
   p.attn = region_ptr<__nv_bfloat16>(h, "attn"); p.act = region_ptr<__nv_bfloat16>(h, "act");
   p.sched = region_ptr<Unit>(h, "sched"); p.sched_n = region_ptr<int>(h, "sched_n");
@@ -1461,6 +1528,7 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.prefix = h->prefix; p.n_steps = n_steps; p.n_layers = n_layers; p.max_stage = h->max_stage;
   p.n_gemm_ctas = h->n_gemm;
   p.drop_event = h->drop_event;
+  p.poll_ns = h->poll_ns;
   for (int g = 0; g < 4; ++g) p.n_units[g] = h->n_units[g];
   const double dt = -1.0 / NS;
   for (int s = 0; s < NS; ++s) p.t_steps[s] = (float)(1.0 + s * dt);
@@ -1486,7 +1554,7 @@ int pi05_status(pi05_handle_t h, int* code, int* where) {
   *code = (int)st[0];
   *where = (int)st[1];
   if (st[0]) {
-    e = cudaMemset(h->ws, 0, 1024);   // status and every counter: the next launch starts clean
+    e = cudaMemset(h->ws, 0, CTRL_BYTES);   // status and every counter: the next launch starts clean
     if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(status)", e);
     return PI05_ERR_DEVICE_TIMEOUT;
   }
@@ -1589,7 +1657,7 @@ extern "C" int pi05_chunk_static(int device, const void* const inputs[PI05_NUM_I
     // and stage counters; an aborted call could leave them dirty); the kernel clears its accumulators itself.
     DeviceGuard guard(device);
     if (!guard.ok) return PI05_ERR_CUDA;
-    cudaError_t e = cudaMemsetAsync(slot.scratch, 0, 1024, (cudaStream_t)stream);
+    cudaError_t e = cudaMemsetAsync(slot.scratch, 0, CTRL_BYTES, (cudaStream_t)stream);
     if (e != cudaSuccess) { cudaGetLastError(); return PI05_ERR_CUDA; }
   }
   return pi05_launch(slot.h, n_steps, n_layers, stream, nullptr);

@@ -49,11 +49,9 @@ def _rel(got, want):
 
 
 def _rope_tables(arm):
-    """cos / sin [50, 128] BF16 from the engine's table, stored as [25 token pairs][128][{cos t, cos t+1}, {sin ..}]."""
-    raw = arm.region("rope", torch.bfloat16, (25, 128, 2, 2)).clone()
-    cos = raw[:, :, 0, :].permute(0, 2, 1).reshape(50, 128)
-    sin = raw[:, :, 1, :].permute(0, 2, 1).reshape(50, 128)
-    return cos, sin
+    """cos / sin [50, 128] BF16 from the engine's table (one 32-bit word per entry: cos | sin << 16)."""
+    raw = arm.region("rope", torch.bfloat16, (50, 128, 2)).clone()
+    return raw[:, :, 0], raw[:, :, 1]
 
 
 def _assert_one_ulp(got, want):
@@ -114,19 +112,19 @@ def test_one_layer_stage_by_stage(case128):
         _run(arm)
         reg = lambda n, d, s: arm.region(n, d, s).clone()
         if stage == 1:
+            # QKV GEMM: q as FP32 split-K sums (rounded and rotated later, by attention); k (with RoPE) and v as BF16
             an = f(reg("an_attn", torch.bfloat16, (50, 1024)))
+            keep["q_acc"] = reg("qkv_acc", torch.float32, (50, 2560))[:, :2048].clone()
+            assert _rel(keep["q_acc"], an @ f(dev["wq"][0]).T) < 1e-4
             cos, sin = _rope_tables(arm)
-            cos, sin = cos.float(), sin.float()
-            cos, sin = torch.cat((cos, cos), -1)[:, None], torch.cat((sin, sin), -1)[:, None]
-            rot = lambda x: O.rb(O.rb(x * cos) + O.rb(torch.cat((-x[..., 128:], x[..., :128]), -1) * sin))
-            q = rot(O.rb(an @ f(dev["wq"][0]).T).view(50, 8, 256)).reshape(50, 2048)
-            k = rot(O.rb(an @ f(dev["wk"][0]).T).view(50, 1, 256)).reshape(50, 256)
-            v = O.rb(an @ f(dev["wv"][0]).T)
-            assert _rel(reg("q", torch.bfloat16, (50, 2048)), q) < 1e-3
+            cos, sin = torch.cat((cos, cos), -1)[:, None].float(), torch.cat((sin, sin), -1)[:, None].float()
+            keep["rot"] = lambda x: O.rb(O.rb(x * cos) + O.rb(torch.cat((-x[..., 128:], x[..., :128]), -1) * sin))
+            k = keep["rot"](O.rb(an @ f(dev["wk"][0]).T).view(50, 1, 256)).reshape(50, 256)
             assert _rel(reg("k", torch.bfloat16, (50, 256)), k) < 1e-3
-            assert _rel(reg("v", torch.bfloat16, (50, 256)), v) < 1e-3
+            assert _rel(reg("v", torch.bfloat16, (50, 256)), O.rb(an @ f(dev["wv"][0]).T)) < 1e-3
         elif stage == 2:
-            q = f(reg("q", torch.bfloat16, (50, 8, 256)))
+            # attention from the engine's own q sums (round, RoPE with BF16 products and sum) and its k / v
+            q = keep["rot"](O.rb(keep["q_acc"]).view(50, 8, 256))
             keys = torch.cat((f(dev["prefix_k"][0][:, 0]), f(reg("k", torch.bfloat16, (50, 256)))))
             vals = torch.cat((f(dev["prefix_v"][0][:, 0]), f(reg("v", torch.bfloat16, (50, 256)))))
             s = O.rb(O.rb(torch.einsum("thd,kd->thk", q, keys)) * (1 / 16))
@@ -147,6 +145,7 @@ def test_one_layer_stage_by_stage(case128):
             an, _ = O.ada_rms(got_h.cpu(), mod[0, 1].cpu(), O._cast(False))
             assert _rel(reg("an_ffn", torch.bfloat16, (50, 1024)).cpu(), an) < 1e-3
             assert float(reg("o_acc", torch.float32, (50, 1024)).abs().max()) == 0.0
+            assert float(reg("qkv_acc", torch.float32, (50, 2560)).abs().max()) == 0.0   # cleared for the next layer
         elif stage == 5:
             an = f(reg("an_ffn", torch.bfloat16, (50, 1024)))
             g, u = O.rb(an @ f(dev["wg"][0]).T), O.rb(an @ f(dev["wu"][0]).T)
