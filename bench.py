@@ -98,6 +98,32 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def stage_times(arm, flush) -> None:
+    """One stamped chunk: globaltimer values written by the kernel at stage boundaries (row CTA 0) and at the
+    pipeline points of three GEMM CTAs in the second layer pass; printed as microseconds since kernel start."""
+    arm.enable_stamps(True)
+    flush.zero_()
+    arm.launch()
+    arm.status()
+    st = arm.stamps.cpu().tolist()
+    arm.enable_stamps(False)
+    us = lambda x: round((x - st[0]) / 1e3, 2) if x else None
+    out = {"prologue_us": {n: us(st[i]) for i, n in enumerate(
+        ["start", "tables", "time_mlp_in", "time_mlp_out", "modulation", "first_norm"])}}
+    names = ["qkv_seen", "attention_done", "o_seen", "residual_norm_1_done", None, "down_seen", "residual_norm_2_done"]
+    for ps in range(1, 4):
+        out[f"pass{ps}_us"] = {n: us(st[6 + 7 * ps + i]) for i, n in enumerate(names) if n}
+    pts = ["inputs_seen", "acts_issued", "first_operands", "mma_issued", "acc_ready", "acc_in_regs", "stored", "signalled"]
+    for which, cta in enumerate(["cta0", "cta64", "cta84"]):
+        for g, gn in enumerate(["qkv", "o", "gate_up", "down"]):
+            row = st[64 + 64 * which + g * 8: 64 + 64 * which + g * 8 + 8]
+            if any(row):
+                out[f"{cta}_{gn}_pass1_us"] = {pt: us(x) for pt, x in zip(pts, row)}
+    out["row_cta0_attention_pass1_us"] = {n: us(st[224 + i]) for i, n in enumerate(
+        ["prefix_landed", "scores_done", "softmax_done", "pv_done", "stored", "signalled"])}
+    print("stage_times " + json.dumps(out), file=sys.stderr, flush=True)
+
+
 def cpu_chunks_per_sec(geo, inputs_cpu, runs: int) -> tuple[float, int]:
     """The eager BF16 chunk of the CPU oracle (the restatement of reference/pi05.py::reference)."""
     from oracle import pi05_oracle as O
@@ -148,6 +174,8 @@ def main() -> int:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--prefix", type=int, default=128)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--stage-times", action="store_true",
+                    help="also print (stderr) the in-kernel stage timeline of one L2-flushed chunk")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -271,6 +299,8 @@ def main() -> int:
             line["cpu_baseline"] = {"value": cps, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": "5 whole chunks of the same workload (eager BF16 schedule)"}
         print(json.dumps(line), flush=True)
+    if args.stage_times and rank == 0:
+        stage_times(arm, flush)
     arm.close()
     if dist_on:
         dist.destroy_process_group()
