@@ -29,6 +29,7 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
+from pi05_megakernel_b200 import dp as DP  # noqa: E402
 from pi05_megakernel_b200 import fixture as FX  # noqa: E402
 
 METRIC = "action chunks/sec, whole box (B=1 per GPU, prefix 128, L2 flushed before every chunk)"
@@ -195,7 +196,7 @@ def main() -> int:
 
     geo = FX.Geometry(prefix=args.prefix)
     weights = FX.make_weights(geo, FX.SEEDS[0])
-    obs = FX.make_observation(geo, FX.SEEDS[0] + 1000 * rank)        # every GPU: its own observation
+    obs = FX.make_observation(geo, DP.observation_seed(FX.SEEDS[0], rank))   # every GPU: its own observation
     cpu = {k: {**weights, **obs}[k] for k in FX.ORDER}
     dev = {k: v.to(device) for k, v in cpu.items()}
     arm = Pi05Arm(geo, "b200", str(device))
@@ -261,10 +262,7 @@ def main() -> int:
     barrier()
     e2e_step_ms = sum(e2e_ms) / len(e2e_ms)
 
-    if dist_on:
-        t = torch.tensor([ms_step, e2e_step_ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step, e2e_step_ms = float(t[0]), float(t[1])
+    ms_step, e2e_step_ms = DP.max_over_ranks([ms_step, e2e_step_ms], device)
 
     if rank == 0:
         peak_gbs, peak_kind = measured_peaks()
@@ -272,7 +270,7 @@ def main() -> int:
         alg_bytes = floor["bytes_restream"]
         achieved = alg_bytes / (ms_step * 1e-3) / 1e9
         line = {
-            "metric": METRIC, "value": world * 1e3 / ms_step, "unit": UNIT, "n_gpus": world,
+            "metric": METRIC, "value": DP.chunks_per_second(world, ms_step), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": (1e3 / ms_step) / (1e3 / SOTA_GRAPH_MS) if world == 1 else None,
             "dtype": "bf16", "data": "synthetic",
@@ -287,7 +285,7 @@ def main() -> int:
             "x_hbm_floor_measured": ms_step / (alg_bytes / (peak_gbs * 1e9) * 1e3),
             "vs_baseline_note": f"value / (1000 / {SOTA_GRAPH_MS} ms), the reference's published sota-graph arm on one B200",
             "clocks": clocks,
-            "e2e": {"value": world * 1e3 / e2e_step_ms, "unit": UNIT, "ms_per_chunk": e2e_step_ms,
+            "e2e": {"value": DP.chunks_per_second(world, e2e_step_ms), "unit": UNIT, "ms_per_chunk": e2e_step_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
