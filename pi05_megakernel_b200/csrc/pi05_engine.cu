@@ -57,6 +57,8 @@ constexpr int W_ATOM_BYTES = 128 * 128;  // 128 weight rows x 64 k
 constexpr int A_ATOM_BYTES = 64 * 128;   // 64 token rows x 64 k
 constexpr int W_STAGE_BYTES = 2 * W_ATOM_BYTES;
 constexpr int A_STAGE_BYTES = 2 * A_ATOM_BYTES;
+constexpr int A_BOX_ROWS = 50;           // token rows actually copied per activation box
+constexpr int A_STAGE_TX = 2 * A_BOX_ROWS * 128;   // bytes a stage's activation half brings in
 constexpr int STAGE_BYTES_ALL = W_STAGE_BYTES + A_STAGE_BYTES;   // 48 KB: weights, then activations
 constexpr int NSTG = 4;            // pipeline depth (192 KB)
 constexpr int STAGE_STRIDE = 72;   // BF16 elements per row of the epilogue exchange buffer (144 B)
@@ -106,7 +108,7 @@ constexpr long long DRAIN_CYCLES = 400000;          // exit-time grace period fo
 
 struct alignas(64) TMaps {
   CUtensorMap wq, wk, wv, wo, wg, wu, wd;   // weights: {K, L*rows} BF16, box {64, 64}, 128-B swizzle
-  CUtensorMap an_attn, an_ffn, attn, act;   // activations: {K, 50} BF16, box {64, 64}, rows >= 50 read as zero
+  CUtensorMap an_attn, an_ffn, attn, act;   // activations: {K, 50} BF16, box {64, 50}; slot rows 50..63 are never written
 };
 
 struct Params {
@@ -218,46 +220,55 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 }
 
 // ------------------------------------------------------------------------------------------- prologue
-// Sum ten per-lane partials over the 32 lanes with 12 shuffles; lanes with an even index end up holding
-// the total of value `idx` (idx < 0: nothing).  The order of additions is fixed.
-__device__ __forceinline__ float reduce10(float (&v)[10], int lane, int& idx) {
+// Sum ten per-lane partials over the 32 lanes with 12 shuffles, for R independent rows at once (the rows give the
+// scheduler independent shuffle chains to overlap).  Lanes with an even index end up holding in v[r][0] the total
+// of value `idx` of row r (idx < 0: nothing).  The order of additions is fixed.
+template <int R>
+__device__ __forceinline__ int reduce10(float (&v)[R][10], int lane) {
   const unsigned full = 0xffffffffu;
   const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4, b1 = lane & 2;
 #pragma unroll
-  for (int i = 0; i < 5; ++i) {
-    const float send = b4 ? v[i] : v[i + 5];
-    const float keep = b4 ? v[i + 5] : v[i];
-    v[i] = keep + __shfl_xor_sync(full, send, 16);
+  for (int i = 0; i < 5; ++i)
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float send = b4 ? v[r][i] : v[r][i + 5];
+      const float keep = b4 ? v[r][i + 5] : v[r][i];
+      v[r][i] = keep + __shfl_xor_sync(full, send, 16);
+    }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const float s0 = b3 ? v[r][0] : v[r][3], k0 = b3 ? v[r][3] : v[r][0];
+    const float s1 = b3 ? v[r][1] : v[r][4], k1 = b3 ? v[r][4] : v[r][1];
+    const float s2 = b3 ? v[r][2] : 0.f, k2 = b3 ? 0.f : v[r][2];
+    v[r][0] = k0 + __shfl_xor_sync(full, s0, 8);
+    v[r][1] = k1 + __shfl_xor_sync(full, s1, 8);
+    v[r][2] = k2 + __shfl_xor_sync(full, s2, 8);
   }
-  {
-    const float s0 = b3 ? v[0] : v[3], k0 = b3 ? v[3] : v[0];
-    const float s1 = b3 ? v[1] : v[4], k1 = b3 ? v[4] : v[1];
-    const float s2 = b3 ? v[2] : 0.f, k2 = b3 ? 0.f : v[2];
-    v[0] = k0 + __shfl_xor_sync(full, s0, 8);
-    v[1] = k1 + __shfl_xor_sync(full, s1, 8);
-    v[2] = k2 + __shfl_xor_sync(full, s2, 8);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const float s0 = b2 ? v[r][0] : v[r][2], k0 = b2 ? v[r][2] : v[r][0];
+    const float s1 = b2 ? v[r][1] : 0.f, k1 = b2 ? 0.f : v[r][1];
+    v[r][0] = k0 + __shfl_xor_sync(full, s0, 4);
+    v[r][1] = k1 + __shfl_xor_sync(full, s1, 4);
   }
-  {
-    const float s0 = b2 ? v[0] : v[2], k0 = b2 ? v[2] : v[0];
-    const float s1 = b2 ? v[1] : 0.f, k1 = b2 ? 0.f : v[1];
-    v[0] = k0 + __shfl_xor_sync(full, s0, 4);
-    v[1] = k1 + __shfl_xor_sync(full, s1, 4);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const float s0 = b1 ? v[r][0] : v[r][1], k0 = b1 ? v[r][1] : v[r][0];
+    v[r][0] = k0 + __shfl_xor_sync(full, s0, 2);
   }
-  {
-    const float s0 = b1 ? v[0] : v[1], k0 = b1 ? v[1] : v[0];
-    v[0] = k0 + __shfl_xor_sync(full, s0, 2);
-  }
-  v[0] += __shfl_xor_sync(full, v[0], 1);
-  int in5 = b3 ? (b2 ? -1 : 3 + (b1 ? 1 : 0)) : (b2 ? (b1 ? -1 : 2) : (b1 ? 1 : 0));
-  idx = in5 < 0 ? -1 : in5 + (b4 ? 5 : 0);
-  return v[0];
+#pragma unroll
+  for (int r = 0; r < R; ++r) v[r][0] += __shfl_xor_sync(full, v[r][0], 1);
+  const int in5 = b3 ? (b2 ? -1 : 3 + (b1 ? 1 : 0)) : (b2 ? (b1 ? -1 : 2) : (b1 ? 1 : 0));
+  return in5 < 0 ? -1 : in5 + (b4 ? 5 : 0);
 }
 
 // out[s][row] = f(W[row][:] . in[s][:] + bias[row]) for the ten time steps at once; FP32 weights streamed from
 // HBM exactly once.  Four warps share a row (a quarter of K each, the ten input vectors of that quarter live in
-// registers), eight rows per batch.  MODE 0/1: time MLP layers (SiLU).  MODE 2: the 37 modulation layers.
+// registers), four rows per batch, and the loads of the next batch are issued before the current one is reduced, so
+// every warp keeps 4-8 KB in flight.  MODE 0/1: time MLP layers (SiLU).  MODE 2: the 37 modulation layers.
 template <int MODE>
 __device__ void matvec10(const Params& p, const float* __restrict__ in, uint8_t* smem, int cta, int ncta) {
+  constexpr int RB = 4;                      // rows per batch
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = warp >> 2, quarter = warp & 3;
   const int koff = quarter * 256 + lane * 4;
@@ -269,36 +280,44 @@ __device__ void matvec10(const Params& p, const float* __restrict__ in, uint8_t*
     c[s][0] = a.x; c[s][1] = a.y; c[s][2] = a.z; c[s][3] = a.w;
     c[s][4] = b.x; c[s][5] = b.y; c[s][6] = b.z; c[s][7] = b.w;
   }
-  float* part = reinterpret_cast<float*>(smem + OFF_STAGE);  // [2 buf][2 group][4 quarter][8 row][10]
+  float* part = reinterpret_cast<float*>(smem + OFF_STAGE);  // [2 buf][2 group][4 quarter][RB row][10]
   const int nrows = (MODE == 2) ? NNORM * MODW : W;
-  const int nbatch = nrows / 8;
-  int it = 0;
-  for (int b = cta * 2 + group; b < nbatch; b += ncta * 2, ++it) {
-    const int row0 = b * 8;
-    const float* wbase;
-    const float* bias;
-    float* out;      // out[s * ostride + r]
-    int ostride;
-    if (MODE == 0) { wbase = p.tin_w + (size_t)row0 * W; bias = p.tin_b + row0; out = p.hid + row0; ostride = W; }
-    else if (MODE == 1) { wbase = p.tout_w + (size_t)row0 * W; bias = p.tout_b + row0; out = p.cond + row0; ostride = W; }
-    else {
-      const int n = row0 / MODW, j = row0 % MODW;
-      if (n == NNORM - 1) { wbase = p.fin_nw + (size_t)j * W; bias = p.fin_nb + j; }
-      else if (n & 1) { wbase = p.ffn_nw + ((size_t)(n >> 1) * MODW + j) * W; bias = p.ffn_nb + (size_t)(n >> 1) * MODW + j; }
-      else { wbase = p.attn_nw + ((size_t)(n >> 1) * MODW + j) * W; bias = p.attn_nb + (size_t)(n >> 1) * MODW + j; }
-      out = p.mod + (size_t)n * MODW + j;
-      ostride = NNORM * MODW;
-    }
-    float4 w[8][2];
+  const int nbatch = nrows / RB;
+  const int stride = ncta * 2;
+
+  auto weight_base = [&](int row0) -> const float* {
+    if (MODE == 0) return p.tin_w + (size_t)row0 * W;
+    if (MODE == 1) return p.tout_w + (size_t)row0 * W;
+    const int n = row0 / MODW, j = row0 % MODW;
+    if (n == NNORM - 1) return p.fin_nw + (size_t)j * W;
+    return ((n & 1) ? p.ffn_nw : p.attn_nw) + ((size_t)(n >> 1) * MODW + j) * W;
+  };
+  auto load = [&](float4 (&w)[RB][2], int b) {
+    const float* wbase = weight_base(b * RB) + koff;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      w[r][0] = ptx::ldg_stream_f4(wbase + (size_t)r * W + koff);
-      w[r][1] = ptx::ldg_stream_f4(wbase + (size_t)r * W + koff + 128);
+    for (int r = 0; r < RB; ++r) {
+      w[r][0] = ptx::ldg_stream_f4(wbase + (size_t)r * W);
+      w[r][1] = ptx::ldg_stream_f4(wbase + (size_t)r * W + 128);
     }
-    float* pb = part + (((it & 1) * 2 + group) * 4 + quarter) * 80;
+  };
+  auto reduce_store = [&](const float4 (&w)[RB][2], int b, int it) {
+    // the bias of the output this thread will write is fetched first, so that its latency hides behind the FMAs
+    const int i = tid & 127, orow = b * RB + i / 10, os = i % 10;
+    float bias = 0.f;
+    float* out = nullptr;
+    if (i < RB * 10) {
+      if (MODE == 0) { bias = p.tin_b[orow]; out = p.hid + (size_t)os * W + orow; }
+      else if (MODE == 1) { bias = p.tout_b[orow]; out = p.cond + (size_t)os * W + orow; }
+      else {
+        const int n = orow / MODW, j = orow % MODW;
+        bias = n == NNORM - 1 ? p.fin_nb[j] : ((n & 1) ? p.ffn_nb : p.attn_nb)[(size_t)(n >> 1) * MODW + j];
+        out = p.mod + ((size_t)os * NNORM + n) * MODW + j;
+      }
+    }
+    float* pb = part + (((it & 1) * 2 + group) * 4 + quarter) * (RB * 10);
+    float acc[RB][10];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      float acc[10];
+    for (int r = 0; r < RB; ++r)
 #pragma unroll
       for (int s = 0; s < NS; ++s) {
         float a = w[r][0].x * c[s][0];
@@ -309,21 +328,33 @@ __device__ void matvec10(const Params& p, const float* __restrict__ in, uint8_t*
         a = fmaf(w[r][1].y, c[s][5], a);
         a = fmaf(w[r][1].z, c[s][6], a);
         a = fmaf(w[r][1].w, c[s][7], a);
-        acc[s] = a;
+        acc[r][s] = a;
       }
-      int idx;
-      const float tot = reduce10(acc, lane, idx);
-      if (!(lane & 1) && idx >= 0) pb[r * 10 + idx] = tot;
+    const int idx = reduce10<RB>(acc, lane);
+    if (!(lane & 1) && idx >= 0) {
+#pragma unroll
+      for (int r = 0; r < RB; ++r) pb[r * 10 + idx] = acc[r][0];
     }
     ptx::named_bar_sync(2 + group, 128);
-    const int i = tid & 127;
-    if (i < 80) {
-      const int r = i / 10, s = i % 10;
-      const float* q0 = part + (((it & 1) * 2 + group) * 4) * 80 + r * 10 + s;
-      float v = ((q0[0] + q0[80]) + (q0[160] + q0[240])) + bias[r];
-      if (MODE != 2) v = silu(v);
-      out[(size_t)s * ostride + r] = v;
+    if (i < RB * 10) {
+      const float* q0 = part + (((it & 1) * 2 + group) * 4) * (RB * 10) + i;
+      const float v = ((q0[0] + q0[RB * 10]) + (q0[2 * RB * 10] + q0[3 * RB * 10])) + bias;
+      *out = (MODE == 2) ? v : silu(v);
     }
+  };
+
+  float4 wa[RB][2], wb[RB][2];
+  int b = cta * 2 + group, it = 0;
+  if (b < nbatch) load(wa, b);
+  while (b < nbatch) {
+    const int b1 = b + stride;
+    if (b1 < nbatch) load(wb, b1);
+    reduce_store(wa, b, it++);
+    if (b1 >= nbatch) break;
+    const int b2 = b1 + stride;
+    if (b2 < nbatch) load(wa, b2);
+    reduce_store(wb, b1, it++);
+    b = b2;
   }
 }
 
@@ -605,15 +636,18 @@ struct AttChunkIssue {
       if (tid < nrows) ok = is_prefix ? (p.prefix_mask[chunk * 64 + tid] ? 1 : 0) : 1;
       kvalid[tid] = ok;
     }
-    if (nrows > 0) {
-      // 64 rows x 32 16-byte pieces for K, then the same for V; rows past the end are zero-filled
-      for (int idx = tid; idx < 2 * 64 * 32; idx += THREADS) {
-        const int isv = idx >= 64 * 32;
-        const int r = (idx >> 5) & 63, cidx = idx & 31;
-        uint8_t* dst = (isv ? vs : ks) + r * (KV_STRIDE * 2) + cidx * 16;
-        if (r < nrows) ptx::cp_async_16(ptx::smem_u32(dst), (isv ? vsrc : ksrc) + (size_t)r * HD + cidx * 8);
-        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    // 64 rows x 32 16-byte pieces for K, then the same for V; rows past the end are zero-filled.  The suffix chunk
+    // is the one attention waits for, so its keys and its values are separate groups: scoring starts on the keys.
+    for (int isv = 0; isv < 2; ++isv) {
+      if (nrows > 0) {
+        for (int idx = tid; idx < 64 * 32; idx += THREADS) {
+          const int r = idx >> 5, cidx = idx & 31;
+          uint8_t* dst = (isv ? vs : ks) + r * (KV_STRIDE * 2) + cidx * 16;
+          if (r < nrows) ptx::cp_async_16(ptx::smem_u32(dst), (isv ? vsrc : ksrc) + (size_t)r * HD + cidx * 8);
+          else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
       }
+      if (chunk == npc && isv == 0) ptx::cp_async_commit();
     }
     ptx::cp_async_commit();
     return true;
@@ -670,7 +704,7 @@ __device__ bool attention_unit(const Params& p, uint8_t* smem, int unit, const A
       if (j < early) att_qk(qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
     if (early < nst) {
       if (!issue(c0 + early, early)) return false;     // waits for the k / v tiles, then copies the suffix chunk
-      ptx::cp_async_wait<0>();
+      ptx::cp_async_wait<1>();                         // its keys have landed; its values may still be in flight
       __syncthreads();
 #pragma unroll
       for (int j = 0; j < ATT_STAGES; ++j)
@@ -705,6 +739,7 @@ __device__ bool attention_unit(const Params& p, uint8_t* smem, int unit, const A
     const float al_lo = __expf(m_lo - mn_lo), al_hi = __expf(m_hi - mn_hi);
     m_lo = mn_lo; m_hi = mn_hi;
     l_lo *= al_lo; l_hi *= al_hi;
+    ptx::cp_async_wait<0>();                           // suffix values (ordered for everyone by the barrier below)
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) { o[nt][0] *= al_lo; o[nt][1] *= al_lo; o[nt][2] *= al_hi; o[nt][3] *= al_hi; }
 #pragma unroll
@@ -854,7 +889,7 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
         if (!wait_mbar(c, b.empty + 8 * slot, par ^ 1, WAIT_A_EMPTY, stage)) return;
         const uint32_t full = b.full + 8 * slot;
         const uint32_t dst = ring + slot * STAGE_BYTES_ALL + W_STAGE_BYTES;
-        ptx::mbar_expect_tx(full, A_STAGE_BYTES);
+        ptx::mbar_expect_tx(full, A_STAGE_TX);
         ptx::tma_load_2d(dst, m, full, kc, 0);
         ptx::tma_load_2d(dst + A_ATOM_BYTES, m, full, kc + KATOM, 0);
         if (++slot == NSTG) { slot = 0; par ^= 1; }
@@ -1339,12 +1374,12 @@ bool build_schedule(pi05_engine* h) {
   return true;
 }
 
-int encode_2d(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows) {
+int encode_2d(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, uint32_t box_rows = 64) {
   EncodeTiledFn enc = get_encode();
   if (!enc) { h->last_error = "cuTensorMapEncodeTiled is not available from this driver"; return PI05_ERR_CUDA; }
   cuuint64_t dims[2] = {inner, rows};
   cuuint64_t strides[1] = {inner * 2};
-  cuuint32_t box[2] = {KATOM, 64};
+  cuuint32_t box[2] = {KATOM, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1466,10 +1501,10 @@ int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int pr
   if ((rc = encode_2d(h, &h->maps.wg, inputs[12], W, (uint64_t)NL * FF))) return rc;
   if ((rc = encode_2d(h, &h->maps.wu, inputs[13], W, (uint64_t)NL * FF))) return rc;
   if ((rc = encode_2d(h, &h->maps.wd, inputs[14], FF, (uint64_t)NL * W))) return rc;
-  if ((rc = encode_2d(h, &h->maps.an_attn, region_ptr<void>(h, "an_attn"), W, T))) return rc;
-  if ((rc = encode_2d(h, &h->maps.an_ffn, region_ptr<void>(h, "an_ffn"), W, T))) return rc;
-  if ((rc = encode_2d(h, &h->maps.attn, region_ptr<void>(h, "attn"), QD, T))) return rc;
-  if ((rc = encode_2d(h, &h->maps.act, region_ptr<void>(h, "act"), FF, T))) return rc;
+  if ((rc = encode_2d(h, &h->maps.an_attn, region_ptr<void>(h, "an_attn"), W, T, A_BOX_ROWS))) return rc;
+  if ((rc = encode_2d(h, &h->maps.an_ffn, region_ptr<void>(h, "an_ffn"), W, T, A_BOX_ROWS))) return rc;
+  if ((rc = encode_2d(h, &h->maps.attn, region_ptr<void>(h, "attn"), QD, T, A_BOX_ROWS))) return rc;
+  if ((rc = encode_2d(h, &h->maps.act, region_ptr<void>(h, "act"), FF, T, A_BOX_ROWS))) return rc;
   e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceSynchronize", e);
   h->bound = true;
