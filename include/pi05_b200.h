@@ -43,12 +43,16 @@ enum {
  * 17 ffn_norm_weight  [18,3072,1024] f32  18 ffn_norm_bias  [18,3072] f32
  * 19 final_norm_weight [3072,1024] f32    20 final_norm_bias [3072] f32
  * 21 noise [50,32] f32   22 prefix_k [18,P,1,256] bf16   23 prefix_v [18,P,1,256] bf16
- * 24 prefix_mask [P] bool (one byte per token, non-zero = valid)                              */
+ * 24 prefix_mask [P] bool (one byte per token, non-zero = valid)
+ * With a batch of B > 1 observations, tensors 21-24 (and the actions output) carry a leading index [B, ...]:
+ * every observation has its own noise, prefix cache and mask; tensors 0-20 (the weights) are shared.          */
 #define PI05_NUM_INPUTS 25
 
 /* Replaces setup(device) (mk/pi05_mk.cu:3363-3380).  max_prefix bounds the prefix length accepted by
- * pi05_bind; max_batch, tp_rank and tp_size select the batched / tensor-parallel builds (only
- * max_batch = 1, tp_size = 1 exist today; anything else returns PI05_ERR_UNSUPPORTED). */
+ * pi05_bind; max_batch (1..16) is the largest number of independent observations one launch may serve (the
+ * workspace grows with it; the weights are streamed from HBM once per launch for all of them); tp_rank and
+ * tp_size select the tensor-parallel build (only tp_size = 1 exists today; anything else returns
+ * PI05_ERR_UNSUPPORTED). */
 int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_size, pi05_handle_t* out);
 
 /* Replaces workspace_bytes() (mk/pi05_mk.cu:3659-3660): size of the scratch buffer the caller allocates
@@ -58,7 +62,8 @@ int pi05_workspace_bytes(pi05_handle_t h, size_t* bytes);
 /* Replaces the tensor-list half of launch() (mk/pi05_mk.cu:3523-3557) and MegakernelArm.bind
  * (megakernel.py:167-176): records the 25 device pointers (caller-owned, read-only, kept across launches and
  * across in-place refills), the output buffer actions [50,32] f32 and the workspace, clears the workspace and
- * encodes the TMA descriptors.  prefix_len is P (1..max_prefix).  Synchronises the device. */
+ * encodes the TMA descriptors.  prefix_len is P (1..max_prefix), batch the number of observations (1..max_batch).
+ * Synchronises the device. */
 int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, int batch,
               void* actions, void* workspace, size_t workspace_bytes);
 

@@ -5,7 +5,7 @@ holds the geometry and the seeded synthetic inputs.  The native library is loade
 when an arm is created and its absence is an error (no CPU path exists).
 """
 
-from .fixture import ORDER, SEEDS, Geometry, make_inputs, sol  # noqa: F401
+from .fixture import ORDER, SEEDS, Geometry, make_batch, make_inputs, sol  # noqa: F401
 
 
 def __getattr__(name):

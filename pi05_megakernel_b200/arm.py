@@ -4,7 +4,8 @@ Same surface as the reference's ``MegakernelArm`` (megakernel.py:117-186) as the
 harness uses it (bench.py:123-135, 209-216, 234-252): ``Arm(geo, variant,
 device)``, ``bind(inputs)``, ``launch()`` (asynchronous on the current stream,
 one whole chunk), ``outputs()["actions"]`` (a persistent [50, 32] FP32 buffer
-the arm owns), optional ``refresh_weights()``, ``config`` and ``close()``.
+the arm owns; [batch, 50, 32] when the arm was created with ``batch`` > 1, in which
+case noise, prefix_k, prefix_v and prefix_mask carry a leading batch index), optional ``refresh_weights()``, ``config`` and ``close()``.
 torch only supplies device memory and the current stream; the work is done by
 ``libpi05_b200.so``.
 """
@@ -17,7 +18,7 @@ import json
 import torch
 
 from . import _lib
-from .fixture import ORDER, Geometry, shapes
+from .fixture import OBSERVATION, ORDER, Geometry, shapes
 
 
 def parse_variant(variant: str) -> dict:
@@ -40,13 +41,15 @@ def parse_variant(variant: str) -> dict:
 class Pi05Arm:
     name = "b200-megakernel"
 
-    def __init__(self, geo: Geometry, variant: str = "b200", device: str = "cuda") -> None:
+    def __init__(self, geo: Geometry, variant: str = "b200", device: str = "cuda", batch: int = 1) -> None:
         if (geo.horizon, geo.action_dim, geo.layers, geo.steps, geo.hidden, geo.intermediate,
                 geo.q_heads, geo.kv_heads, geo.head_dim) != (50, 32, 18, 10, 1024, 4096, 8, 1, 256):
             raise ValueError("the engine is specialised for horizon 50, action 32, 18 layers, 10 steps, "
                              "width 1024/4096, 8 query heads over 1 KV head of 256")
         pv = parse_variant(variant)
-        self.geo, self.variant = geo, variant
+        if not 1 <= batch <= 16:
+            raise ValueError("batch must be 1..16 observations per launch")
+        self.geo, self.variant, self.batch = geo, variant, batch
         self.steps = geo.steps if pv["steps"] is None else pv["steps"]
         self.layers = geo.layers if pv["layers"] is None else pv["layers"]
         if not (1 <= self.steps <= geo.steps and 1 <= self.layers <= geo.layers):
@@ -58,16 +61,17 @@ class Pi05Arm:
         index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.device = torch.device("cuda", index)
         handle = ctypes.c_void_p()
-        _lib.check(self.lib, None, self.lib.pi05_create(index, geo.prefix, 1, 0, 1, ctypes.byref(handle)))
+        _lib.check(self.lib, None, self.lib.pi05_create(index, geo.prefix, batch, 0, 1, ctypes.byref(handle)))
         self.handle = handle
         nbytes = ctypes.c_size_t()
         _lib.check(self.lib, handle, self.lib.pi05_workspace_bytes(handle, ctypes.byref(nbytes)))
         self.ws = torch.empty(nbytes.value, dtype=torch.uint8, device=self.device)
-        self.actions = torch.zeros((geo.horizon, geo.action_dim), dtype=torch.float32, device=self.device)
+        shape = (geo.horizon, geo.action_dim) if batch == 1 else (batch, geo.horizon, geo.action_dim)
+        self.actions = torch.zeros(shape, dtype=torch.float32, device=self.device)
         self.tensors: list[torch.Tensor] | None = None
         self.stamps: torch.Tensor | None = None
         self.config = json.loads(self.lib.pi05_config_json(handle).decode())
-        self.config.update(prefix=geo.prefix, steps=self.steps, layers=self.layers)
+        self.config.update(prefix=geo.prefix, steps=self.steps, layers=self.layers, batch=batch)
 
     # ------------------------------------------------------------------ arm protocol
     def bind(self, inputs: dict) -> None:
@@ -76,6 +80,8 @@ class Pi05Arm:
         for name in ORDER:
             value = inputs[name]
             shape, dtype = want[name]
+            if self.batch > 1 and name in OBSERVATION:
+                shape = (self.batch, *shape)          # one observation per leading index, weights shared
             if tuple(value.shape) != tuple(shape) or value.dtype != dtype:
                 raise ValueError(f"{name}: expected {shape} {dtype}, got {tuple(value.shape)} {value.dtype}")
             if not value.is_contiguous():
@@ -85,7 +91,7 @@ class Pi05Arm:
             tensors.append(value)
         ptrs = (ctypes.c_void_p * _lib.NUM_INPUTS)(*[t.data_ptr() for t in tensors])
         _lib.check(self.lib, self.handle, self.lib.pi05_bind(
-            self.handle, ptrs, self.geo.prefix, 1, self.actions.data_ptr(), self.ws.data_ptr(),
+            self.handle, ptrs, self.geo.prefix, self.batch, self.actions.data_ptr(), self.ws.data_ptr(),
             self.ws.numel()))
         self.tensors = tensors
 

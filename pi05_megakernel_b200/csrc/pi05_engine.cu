@@ -93,10 +93,12 @@ __device__ __constant__ int kGemmStage[4] = {ST_QKV, ST_O, ST_GU, ST_DOWN};
 
 // event counters (uint32 each) in the control block
 enum { EV_P0 = 0, EV_P1, EV_P2, EV_P3, EV_ANA, EV_QKV, EV_KV, EV_ATT, EV_O, EV_ANF, EV_GU, EV_DOWN, EV_EXIT, NEVENTS };
-// every counter sits on its own 128-byte line of the control block (word 32 * (1 + e)); words 0..3 are the status
-#define EVW(e) (32 * (1 + (e)))
+// every counter sits on its own 128-byte line of the control block; words 0..3 are the status
+constexpr int MAXB = 16;            // observations per launch (weights are streamed from HBM once for all of them)
+#define EVB(e, b) (32 * (1 + (e) * MAXB + (b)))   // counter of event e for observation b
+#define EVW(e) EVB(e, 0)
 constexpr int NKVTILES = 4;         // k (2) and v (2) tiles of the QKV GEMM
-constexpr int CTRL_BYTES = 128 * (1 + NEVENTS);
+constexpr int CTRL_BYTES = 128 * (1 + NEVENTS * MAXB);
 
 // wait kinds reported in the status word
 enum { WAIT_W_EMPTY = 1, WAIT_W_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_T_EMPTY, WAIT_T_FULL, WAIT_EVENT,
@@ -111,34 +113,54 @@ struct alignas(64) TMaps {
   CUtensorMap an_attn, an_ffn, attn, act;   // activations: {K, 50} BF16, box {64, 50}; slot rows 50..63 are never written
 };
 
+// Pointers that differ from one observation of the batch to the next (b = 0 in Params; obs() advances them).
+struct ObsPtrs {
+  const float* noise;                       // [T][32]
+  const __nv_bfloat16 *prefix_k, *prefix_v; // [L][P][256]
+  const uint8_t* prefix_mask;               // [P]
+  float* actions;                           // [T][32]
+  float *x, *o_acc, *d_acc;                 // [T][32], [T][W], [T][W]
+  float* qkv_acc;                           // [T][2560] split-K accumulator of q (FP32, before rounding and RoPE)
+  uint32_t* rope;                           // [T][128]: cos BF16 | sin BF16 << 16
+  uint32_t* rope2;                          // [T/2][128][2]: {cos t, cos t+1}, {sin t, sin t+1} BF16 pairs
+  __nv_bfloat16 *h, *an_attn, *an_ffn, *k, *v, *attn, *act;   // k, v: [T][256] suffix keys (after RoPE) / values
+  int b;
+};
+
 struct Params {
   TMaps maps;
-  // inputs
+  // inputs shared by the whole batch
   const float *ain_w, *ain_b, *tin_w, *tin_b, *tout_w, *tout_b, *aout_w, *aout_b;
   const float *attn_nw, *attn_nb, *ffn_nw, *ffn_nb, *fin_nw, *fin_nb;
-  const float* noise;
   const __nv_bfloat16 *wq, *wk, *wv, *wo, *wg, *wu, *wd;
-  const __nv_bfloat16 *prefix_k, *prefix_v;
-  const uint8_t* prefix_mask;
-  float* actions;
-  // workspace
-  unsigned int* ctrl;      // [0..3] status, [EVW(e)] event counters, one per 128-byte line
-  float *temb, *hid, *cond, *mod, *x, *o_acc, *d_acc;
-  uint32_t* rope;          // [T][128]: cos BF16 | sin BF16 << 16
-  uint32_t* rope2;         // [T/2][128][2]: {cos t, cos t+1}, {sin t, sin t+1} BF16 pairs (packed arithmetic on token pairs)
-  float* qkv_acc;          // [T][2560] split-K accumulator of q | k | v (FP32, before rounding and RoPE)
-  __nv_bfloat16 *h, *an_attn, *an_ffn, *k, *v, *attn, *act;   // k, v: [T][256] suffix keys / values (BF16, k after RoPE)
+  ObsPtrs ob;
+  // workspace shared by the whole batch
+  unsigned int* ctrl;      // [0..3] status, [EVB(e, b)] event counters, one per 128-byte line
+  float *temb, *hid, *cond, *mod;
   const Unit* sched;       // [grid][MAX_UNITS]
   const int* sched_n;      // [grid]
   unsigned long long* stamps;
   long long wait_limit;
-  int prefix, n_steps, n_layers, max_stage, n_gemm_ctas;
+  int prefix, n_steps, n_layers, max_stage, n_gemm_ctas, batch;
   int poll_ns;             // pause between two samples of a stage counter
   int drop_event;          // debug: this event is never signalled (exercises the bounded waits); -1 = none
   int n_units[4];          // units per GEMM kind (event targets)
   float t_steps[NS];
   float dt;
 };
+
+__device__ __forceinline__ ObsPtrs obs(const Params& p, int b) {
+  ObsPtrs o = p.ob;
+  const size_t kv = (size_t)NL * p.prefix * HD;
+  o.noise += (size_t)b * T * ADIM; o.actions += (size_t)b * T * ADIM; o.x += (size_t)b * T * ADIM;
+  o.prefix_k += b * kv; o.prefix_v += b * kv; o.prefix_mask += (size_t)b * p.prefix;
+  o.o_acc += (size_t)b * T * W; o.d_acc += (size_t)b * T * W; o.qkv_acc += (size_t)b * T * QKVW;
+  o.rope += (size_t)b * T * (HD / 2); o.rope2 += (size_t)b * T * (HD / 2);
+  o.h += (size_t)b * T * W; o.an_attn += (size_t)b * T * W; o.an_ffn += (size_t)b * T * W;
+  o.k += (size_t)b * T * HD; o.v += (size_t)b * T * HD; o.attn += (size_t)b * T * QD; o.act += (size_t)b * T * FF;
+  o.b = b;
+  return o;
+}
 
 // ------------------------------------------------------------------------------------------- bounded waits
 struct Ctx {
@@ -370,22 +392,22 @@ __device__ bool grid_event(const Params& p, const Ctx& c, int ev, int ncta) {
   return ok_flag != 0;
 }
 
-__device__ int count_valid(const Params& p) {
+__device__ int count_valid(const Params& p, const ObsPtrs& o) {
   __shared__ int s_cnt;
+  __syncthreads();
   if (threadIdx.x == 0) s_cnt = 0;
   __syncthreads();
   int n = 0;
-  for (int i = threadIdx.x; i < p.prefix; i += THREADS) n += p.prefix_mask[i] ? 1 : 0;
-  for (int o = 16; o; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+  for (int i = threadIdx.x; i < p.prefix; i += THREADS) n += o.prefix_mask[i] ? 1 : 0;
+  for (int sh = 16; sh; sh >>= 1) n += __shfl_xor_sync(0xffffffffu, n, sh);
   if ((threadIdx.x & 31) == 0 && n) atomicAdd(&s_cnt, n);
   __syncthreads();
   return s_cnt;
 }
 
-// Time embedding (FP64, reference/pi05.py:232-237), RoPE table (reference/pi05.py:218-229) and clearing of the
-// split-K accumulators.
+// Time embedding (FP64, reference/pi05.py:232-237), and per observation the RoPE tables (reference/pi05.py:218-229;
+// positions start at that observation's number of valid prefix tokens) and the clearing of its split-K accumulators.
 __device__ void prologue_tables(const Params& p, int cta, int ncta) {
-  const int nvalid = count_valid(p);
   const int gtid = cta * THREADS + threadIdx.x, gn = ncta * THREADS;
   for (int i = gtid; i < NS * W; i += gn) {
     const int s = i / W, j = i % W, f = j % (W / 2);
@@ -395,23 +417,27 @@ __device__ void prologue_tables(const Params& p, int cta, int ncta) {
     const double phase = (double)p.t_steps[s] * (1.0 / period * 2 * 3.141592653589793);
     p.temb[i] = (float)(j < W / 2 ? sin(phase) : cos(phase));
   }
-  for (int i = gtid; i < T * (HD / 2); i += gn) {
-    const int t = i / (HD / 2), j = i % (HD / 2);
-    const float e = (float)(2 * j) / (float)HD;
-    const float inv = 1.0f / (float)pow(10000.0, (double)e);
-    const float phase = (float)(nvalid + t) * inv;
-    p.rope[i] = pack_bf16((float)cos((double)phase), (float)sin((double)phase));
+  for (int b = 0; b < p.batch; ++b) {
+    const ObsPtrs o = obs(p, b);
+    const int nvalid = count_valid(p, o);
+    for (int i = gtid; i < T * (HD / 2); i += gn) {
+      const int t = i / (HD / 2), j = i % (HD / 2);
+      const float e = (float)(2 * j) / (float)HD;
+      const float inv = 1.0f / (float)pow(10000.0, (double)e);
+      const float phase = (float)(nvalid + t) * inv;
+      o.rope[i] = pack_bf16((float)cos((double)phase), (float)sin((double)phase));
+    }
+    for (int i = gtid; i < (T / 2) * (HD / 2); i += gn) {
+      const int tp = i / (HD / 2), j = i % (HD / 2);
+      const float e = (float)(2 * j) / (float)HD;
+      const float inv = 1.0f / (float)pow(10000.0, (double)e);
+      const float ph0 = (float)(nvalid + 2 * tp) * inv, ph1 = (float)(nvalid + 2 * tp + 1) * inv;
+      o.rope2[2 * i] = pack_bf16((float)cos((double)ph0), (float)cos((double)ph1));
+      o.rope2[2 * i + 1] = pack_bf16((float)sin((double)ph0), (float)sin((double)ph1));
+    }
+    for (int i = gtid; i < T * QKVW; i += gn) o.qkv_acc[i] = 0.f;
+    for (int i = gtid; i < T * W; i += gn) { o.o_acc[i] = 0.f; o.d_acc[i] = 0.f; }
   }
-  for (int i = gtid; i < (T / 2) * (HD / 2); i += gn) {
-    const int tp = i / (HD / 2), j = i % (HD / 2);
-    const float e = (float)(2 * j) / (float)HD;
-    const float inv = 1.0f / (float)pow(10000.0, (double)e);
-    const float ph0 = (float)(nvalid + 2 * tp) * inv, ph1 = (float)(nvalid + 2 * tp + 1) * inv;
-    p.rope2[2 * i] = pack_bf16((float)cos((double)ph0), (float)cos((double)ph1));
-    p.rope2[2 * i + 1] = pack_bf16((float)sin((double)ph0), (float)sin((double)ph1));
-  }
-  for (int i = gtid; i < T * QKVW; i += gn) p.qkv_acc[i] = 0.f;
-  for (int i = gtid; i < T * W; i += gn) { p.o_acc[i] = 0.f; p.d_acc[i] = 0.f; }
 }
 
 // ------------------------------------------------------------------------------------------- row operations
@@ -446,8 +472,8 @@ __device__ __forceinline__ void row_prefetch(const Params& p, int mode, int step
 //            the step tail: final adaRMS, v = Wout n + b, x += dt v, and (unless it was the last step)
 //            h = bf16(Win x + b), an_attn = adaRMS_attn[0](h) with the next step's modulation.
 //   ROW_INIT: x = noise, h = bf16(Win x + b), an_attn = adaRMS_attn[0](h).
-__device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int step, int layer, float (&hn)[8],
-                       const RowMod& rm) {
+__device__ void row_op(const Params& p, const ObsPtrs& o, uint8_t* smem, int unit, int mode, int step, int layer,
+                       float (&hn)[8], const RowMod& rm) {
   const int tid = threadIdx.x, lane = tid & 31;
   const int half = tid >> 7, i = tid & 127, wq = (tid >> 5) & 3;
   const int t = unit * 2 + half;
@@ -460,7 +486,7 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
     float ss = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
-    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    for (int sh = 16; sh; sh >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sh);
     ptx::named_bar_sync(bar, 128);          // previous use of red[] is over
     if (lane == 0) red[wq] = ss;
     ptx::named_bar_sync(bar, 128);
@@ -469,18 +495,18 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
   auto ada_norm = [&](const float (&v)[8], const float (&scale)[8], const float (&shift)[8], __nv_bfloat16* dst) {
     const float ss = sumsq(v);
     const float rs = 1.0f / sqrtf(ss * (1.0f / W) + EPS);
-    uint32_t o[4];
+    uint32_t ow[4];
 #pragma unroll
     for (int e = 0; e < 8; e += 2) {
       const float a = __fadd_rn(__fmul_rn(__fmul_rn(v[e], rs), __fadd_rn(1.0f, scale[e])), shift[e]);
       const float b = __fadd_rn(__fmul_rn(__fmul_rn(v[e + 1], rs), __fadd_rn(1.0f, scale[e + 1])), shift[e + 1]);
-      o[e >> 1] = pack_bf16(a, b);
+      ow[e >> 1] = pack_bf16(a, b);
     }
-    *reinterpret_cast<uint4*>(dst + (size_t)t * W + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(dst + (size_t)t * W + c0) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
   };
   auto store_h = [&](const float (&v)[8]) {   // the kernel itself never reads h back; kept for stage-level checks
-    uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-    *reinterpret_cast<uint4*>(p.h + (size_t)t * W + c0) = o;
+    const uint4 packed = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+    *reinterpret_cast<uint4*>(o.h + (size_t)t * W + c0) = packed;
   };
   // h = bf16(Win x + b) for this thread's 8 columns; x row in red[8..39]
   auto action_in = [&]() {
@@ -502,11 +528,11 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
     float sc[8], sh[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) { sc[e] = m[e]; sh[e] = m[W + e]; }
-    ada_norm(hn, sc, sh, p.an_attn);
+    ada_norm(hn, sc, sh, o.an_attn);
   };
 
   if (mode == ROW_INIT) {
-    if (i < ADIM) { const float xv = p.noise[t * ADIM + i]; p.x[t * ADIM + i] = xv; red[8 + i] = xv; }
+    if (i < ADIM) { const float xv = o.noise[t * ADIM + i]; o.x[t * ADIM + i] = xv; red[8 + i] = xv; }
     ptx::named_bar_sync(bar, 128);
     action_in();
     store_h(hn);
@@ -514,8 +540,15 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
     return;
   }
 
-  // gated residual
-  float* acc = (mode == ROW_ATT ? p.o_acc : p.d_acc) + (size_t)t * W + c0;
+  // gated residual.  With a batch of one the residual stream stays in this thread's registers between row
+  // operations; with more observations it is re-read from memory.
+  if (p.batch > 1) {
+    const uint4 hv = *reinterpret_cast<const uint4*>(o.h + (size_t)t * W + c0);
+    const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) hn[e] = (e & 1) ? bf16_hi(hw[e >> 1]) : bf16_lo(hw[e >> 1]);
+  }
+  float* acc = (mode == ROW_ATT ? o.o_acc : o.d_acc) + (size_t)t * W + c0;
   {
     const float4 a0 = __ldcg(reinterpret_cast<const float4*>(acc)), a1 = __ldcg(reinterpret_cast<const float4*>(acc + 4));
     *reinterpret_cast<float4*>(acc) = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -526,13 +559,13 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
   }
   store_h(hn);
   if (mode == ROW_ATT) {
-    float4* z = reinterpret_cast<float4*>(p.qkv_acc + (size_t)t * QKVW) + i;
+    float4* z = reinterpret_cast<float4*>(o.qkv_acc + (size_t)t * QKVW) + i;
 #pragma unroll
     for (int e = 0; e < QKVW / 4 / 128; ++e) z[e * 128] = make_float4(0.f, 0.f, 0.f, 0.f);
-    ada_norm(hn, rm.scale, rm.shift, p.an_ffn);
+    ada_norm(hn, rm.scale, rm.shift, o.an_ffn);
     return;
   }
-  if (layer + 1 < p.n_layers) { ada_norm(hn, rm.scale, rm.shift, p.an_attn); return; }
+  if (layer + 1 < p.n_layers) { ada_norm(hn, rm.scale, rm.shift, o.an_attn); return; }
   // ---- step tail: final norm, action_out, Euler update
   {
     const float ss = sumsq(hn);
@@ -552,13 +585,13 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
         sdot = fmaf(w4.x, rowbuf[k], sdot); sdot = fmaf(w4.y, rowbuf[k + 1], sdot);
         sdot = fmaf(w4.z, rowbuf[k + 2], sdot); sdot = fmaf(w4.w, rowbuf[k + 3], sdot);
       }
-      for (int o = 16; o; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
+      for (int sh = 16; sh; sh >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, sh);
       if (lane == 0) {
         const float vel = sdot + p.aout_b[a];
-        const float xn = __fadd_rn(p.x[t * ADIM + a], __fmul_rn(p.dt, vel));
-        p.x[t * ADIM + a] = xn;
+        const float xn = __fadd_rn(o.x[t * ADIM + a], __fmul_rn(p.dt, vel));
+        o.x[t * ADIM + a] = xn;
         red[8 + a] = xn;
-        if (step + 1 == p.n_steps) p.actions[t * ADIM + a] = xn;
+        if (step + 1 == p.n_steps) o.actions[t * ADIM + a] = xn;
       }
     }
     ptx::named_bar_sync(bar, 128);
@@ -581,11 +614,11 @@ __device__ void row_op(const Params& p, uint8_t* smem, int unit, int mode, int s
 // q leaves the QKV GEMM as FP32 split-K sums.  The row CTA finishes its 16 query rows while staging them: round to
 // BF16 (the GEMM's output rounding), then RoPE with every product and the sum rounded to BF16
 // (reference/pi05.py:218-229: x * cos + rotate_half(x) * sin on BF16 tensors).  One item of 8 rotary pairs per thread.
-__device__ void build_q(const Params& p, uint8_t* smem, int unit) {
+__device__ void build_q(const ObsPtrs& o, uint8_t* smem, int unit) {
   const int tid = threadIdx.x;
   const int m = tid >> 4, d0 = (tid & 15) * 8, t = unit * 2 + (m >> 3);
-  const float* lo = p.qkv_acc + (size_t)t * QKVW + (m & 7) * HD + d0;
-  const uint32_t* cs = p.rope + t * (HD / 2) + d0;
+  const float* lo = o.qkv_acc + (size_t)t * QKVW + (m & 7) * HD + d0;
+  const uint32_t* cs = o.rope + t * (HD / 2) + d0;
   const float4 x0 = __ldcg(reinterpret_cast<const float4*>(lo)), x1 = __ldcg(reinterpret_cast<const float4*>(lo + 4));
   const float4 y0 = __ldcg(reinterpret_cast<const float4*>(lo + 128)), y1 = __ldcg(reinterpret_cast<const float4*>(lo + 132));
   const uint4 c0 = __ldcg(reinterpret_cast<const uint4*>(cs)), c1 = __ldcg(reinterpret_cast<const uint4*>(cs + 4));
@@ -604,9 +637,9 @@ __device__ void build_q(const Params& p, uint8_t* smem, int unit) {
   ptx::st_shared_v4(dst + 256, pack_bf16(o2[0], o2[1]), pack_bf16(o2[2], o2[3]), pack_bf16(o2[4], o2[5]), pack_bf16(o2[6], o2[7]));
 }
 
-__device__ bool cta_wait_event(const Params& p, const Ctx& c, int ev, unsigned target, int stage) {
+__device__ bool cta_wait_event(const Params& p, const Ctx& c, int word, unsigned target, int stage) {
   __shared__ int ok_flag;
-  if (threadIdx.x == 0) ok_flag = wait_event(c, p.ctrl + EVW(ev), target, stage) ? 1 : 0;
+  if (threadIdx.x == 0) ok_flag = wait_event(c, p.ctrl + word, target, stage) ? 1 : 0;
   __syncthreads();
   const int ok = ok_flag;
   __syncthreads();
@@ -615,6 +648,7 @@ __device__ bool cta_wait_event(const Params& p, const Ctx& c, int ev, unsigned t
 
 struct AttChunkIssue {
   const Params& p;
+  const ObsPtrs& o;
   const Ctx& c;
   uint8_t* smem;
   int layer, npc, pass;
@@ -623,17 +657,17 @@ struct AttChunkIssue {
   __device__ bool operator()(int chunk, int stage) const {
     const int tid = threadIdx.x;
     if (chunk == npc &&
-        !cta_wait_event(p, c, EV_KV, NKVTILES * (pass + 1), pass * NSTAGE + ST_ATT)) return false;
+        !cta_wait_event(p, c, EVB(EV_KV, o.b), NKVTILES * (pass + 1), pass * NSTAGE + ST_ATT)) return false;
     uint8_t* ks = smem + OFF_KS + stage * KV_STAGE_BYTES;
     uint8_t* vs = smem + OFF_VS + stage * KV_STAGE_BYTES;
     uint8_t* kvalid = smem + OFF_KVALID + stage * 64;
     const bool is_prefix = chunk < npc;
-    const __nv_bfloat16* ksrc = is_prefix ? p.prefix_k + ((size_t)layer * p.prefix + (size_t)chunk * 64) * HD : p.k;
-    const __nv_bfloat16* vsrc = is_prefix ? p.prefix_v + ((size_t)layer * p.prefix + (size_t)chunk * 64) * HD : p.v;
+    const __nv_bfloat16* ksrc = is_prefix ? o.prefix_k + ((size_t)layer * p.prefix + (size_t)chunk * 64) * HD : o.k;
+    const __nv_bfloat16* vsrc = is_prefix ? o.prefix_v + ((size_t)layer * p.prefix + (size_t)chunk * 64) * HD : o.v;
     const int nrows = chunk > npc ? 0 : (is_prefix ? min(64, p.prefix - chunk * 64) : T);
     if (tid < 64) {
       uint8_t ok = 0;
-      if (tid < nrows) ok = is_prefix ? (p.prefix_mask[chunk * 64 + tid] ? 1 : 0) : 1;
+      if (tid < nrows) ok = is_prefix ? (o.prefix_mask[chunk * 64 + tid] ? 1 : 0) : 1;
       kvalid[tid] = ok;
     }
     // 64 rows x 32 16-byte pieces for K, then the same for V; rows past the end are zero-filled.  The suffix chunk
@@ -675,7 +709,8 @@ __device__ __forceinline__ void att_qk(uint32_t qs, uint32_t ks, int warp, int l
 // The first `nearly` stages (prefix chunks) were issued by the caller before q was ready.  Scores against them are
 // computed first; the suffix keys are waited for and copied only then, so the k / v tiles of the QKV GEMM may
 // finish later than the q tiles without holding attention up.  Returns false when a wait gave up.
-__device__ bool attention_unit(const Params& p, uint8_t* smem, int unit, const AttChunkIssue& issue, int nearly, bool tr) {
+__device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem, int unit, const AttChunkIssue& issue,
+                               int nearly, bool tr) {
   const int npc = issue.npc;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, qd = lane & 3;
@@ -685,11 +720,11 @@ __device__ bool attention_unit(const Params& p, uint8_t* smem, int unit, const A
   const float NEG = -INFINITY;
 
   float m_lo = -1e30f, m_hi = -1e30f, l_lo = 0.f, l_hi = 0.f;
-  float o[4][4];
+  float oa[4][4];
 #pragma unroll
   for (int a = 0; a < 4; ++a)
 #pragma unroll
-    for (int b = 0; b < 4; ++b) o[a][b] = 0.f;
+    for (int b = 0; b < 4; ++b) oa[a][b] = 0.f;
 
   for (int c0 = 0; c0 < nchunks; c0 += ATT_STAGES) {
     const int nst = min(ATT_STAGES, nchunks - c0);
@@ -741,7 +776,7 @@ __device__ bool attention_unit(const Params& p, uint8_t* smem, int unit, const A
     l_lo *= al_lo; l_hi *= al_hi;
     ptx::cp_async_wait<0>();                           // suffix values (ordered for everyone by the barrier below)
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) { o[nt][0] *= al_lo; o[nt][1] *= al_lo; o[nt][2] *= al_hi; o[nt][3] *= al_hi; }
+    for (int nt = 0; nt < 4; ++nt) { oa[nt][0] *= al_lo; oa[nt][1] *= al_lo; oa[nt][2] *= al_hi; oa[nt][3] *= al_hi; }
 #pragma unroll
     for (int j = 0; j < ATT_STAGES; ++j) {
       if (j < nst) {
@@ -769,10 +804,10 @@ __device__ bool attention_unit(const Params& p, uint8_t* smem, int unit, const A
           const uint32_t vaddr = vs + ((kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KV_STRIDE + db + (lane >> 4) * 8) * 2;
           ptx::ldmatrix_x4_trans(vaddr, r0, r1, r2, r3);
           ptx::ldmatrix_x4_trans(vaddr + 32, r4, r5, r6, r7);
-          ptx::mma_16816(o[0], a0, a1, a2, a3, r0, r1);
-          ptx::mma_16816(o[1], a0, a1, a2, a3, r2, r3);
-          ptx::mma_16816(o[2], a0, a1, a2, a3, r4, r5);
-          ptx::mma_16816(o[3], a0, a1, a2, a3, r6, r7);
+          ptx::mma_16816(oa[0], a0, a1, a2, a3, r0, r1);
+          ptx::mma_16816(oa[1], a0, a1, a2, a3, r2, r3);
+          ptx::mma_16816(oa[2], a0, a1, a2, a3, r4, r5);
+          ptx::mma_16816(oa[3], a0, a1, a2, a3, r6, r7);
         }
       }
     }
@@ -793,12 +828,12 @@ __device__ bool attention_unit(const Params& p, uint8_t* smem, int unit, const A
 #pragma unroll
   for (int w8 = 0; w8 < 8; ++w8) { tl_lo += red[w8 * 16 + g]; tl_hi += red[w8 * 16 + g + 8]; }
   const float il_lo = 1.0f / tl_lo, il_hi = 1.0f / tl_hi;
-  __nv_bfloat16* out = p.attn + (size_t)unit * 2 * QD;   // rows m = token_local * 8 + head are contiguous
+  __nv_bfloat16* out = o.attn + (size_t)unit * 2 * QD;   // rows m = token_local * 8 + head are contiguous
 #pragma unroll
   for (int nt = 0; nt < 4; ++nt) {
     const int col = warp * 32 + nt * 8 + 2 * qd;
-    *reinterpret_cast<uint32_t*>(out + (size_t)g * HD + col) = pack_bf16(o[nt][0] * il_lo, o[nt][1] * il_lo);
-    *reinterpret_cast<uint32_t*>(out + (size_t)(g + 8) * HD + col) = pack_bf16(o[nt][2] * il_hi, o[nt][3] * il_hi);
+    *reinterpret_cast<uint32_t*>(out + (size_t)g * HD + col) = pack_bf16(oa[nt][0] * il_lo, oa[nt][1] * il_lo);
+    *reinterpret_cast<uint32_t*>(out + (size_t)(g + 8) * HD + col) = pack_bf16(oa[nt][2] * il_hi, oa[nt][3] * il_hi);
   }
   ptx::fence_proxy_async_global();   // attn is read by the O projection's TMA
   return true;
@@ -811,7 +846,7 @@ struct Bars {
 
 __device__ __forceinline__ int stage_of(int pass, int gemm) { return pass * NSTAGE + kGemmStage[gemm]; }
 
-struct Producer { int pass, u, a; uint32_t it, slot, par; bool done; };
+struct Producer { int pass, u, b, a; uint32_t it, slot, par; bool done; };
 
 // Tensor maps and first rows of the two 64-row halves of a unit's 128-row weight tile.
 __device__ __forceinline__ void weight_rows(const Params& p, const Unit& un, int layer, const CUtensorMap*& ma,
@@ -834,6 +869,7 @@ __device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units
                                 const Bars& b, Producer& st, uint32_t until, uint64_t policy) {
   const int npass = p.n_steps * p.n_layers;
   if (nunits == 0) { st.done = true; return; }
+  const bool once = p.batch == 1;     // one observation: every weight byte is used once, mark it evict-first in L2
   while (!st.done && st.it < until) {
     if (st.pass >= npass) { st.done = true; break; }
     const Unit un = units[st.u];
@@ -850,16 +886,26 @@ __device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units
       const uint32_t full = b.full + 8 * slot;
       const uint32_t dst = ring + slot * STAGE_BYTES_ALL;
       ptx::mbar_expect_tx(full, W_STAGE_BYTES);
-      ptx::tma_load_2d_hint(dst, ma, full, kc, ra, policy);
-      ptx::tma_load_2d_hint(dst + W_ATOM_BYTES / 2, mb, full, kc, rbw, policy);
-      ptx::tma_load_2d_hint(dst + W_ATOM_BYTES, ma, full, kc + KATOM, ra, policy);
-      ptx::tma_load_2d_hint(dst + W_ATOM_BYTES + W_ATOM_BYTES / 2, mb, full, kc + KATOM, rbw, policy);
+      if (once) {
+        ptx::tma_load_2d_hint(dst, ma, full, kc, ra, policy);
+        ptx::tma_load_2d_hint(dst + W_ATOM_BYTES / 2, mb, full, kc, rbw, policy);
+        ptx::tma_load_2d_hint(dst + W_ATOM_BYTES, ma, full, kc + KATOM, ra, policy);
+        ptx::tma_load_2d_hint(dst + W_ATOM_BYTES + W_ATOM_BYTES / 2, mb, full, kc + KATOM, rbw, policy);
+      } else {                        // the unit's weights come again for the next observation: keep them in L2
+        ptx::tma_load_2d(dst, ma, full, kc, ra);
+        ptx::tma_load_2d(dst + W_ATOM_BYTES / 2, mb, full, kc, rbw);
+        ptx::tma_load_2d(dst + W_ATOM_BYTES, ma, full, kc + KATOM, ra);
+        ptx::tma_load_2d(dst + W_ATOM_BYTES + W_ATOM_BYTES / 2, mb, full, kc + KATOM, rbw);
+      }
       if (++slot == NSTG) { slot = 0; par ^= 1; }
     }
     st.slot = slot; st.par = par; st.it = it; st.a = a;
     if (a >= un.nk) {
       st.a = 0;
-      if (++st.u >= nunits) { st.u = 0; ++st.pass; }
+      if (++st.b >= p.batch) {        // same unit again for the next observation, then the next unit
+        st.b = 0;
+        if (++st.u >= nunits) { st.u = 0; ++st.pass; }
+      }
     }
   }
 }
@@ -870,7 +916,8 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
   const int npass = p.n_steps * p.n_layers;
   uint32_t slot = 0, par = 0;
   for (int pass = 0; pass < npass; ++pass) {
-    for (int u = 0; u < nunits; ++u) {
+    for (int u = 0; u < nunits; ++u)
+    for (int ob = 0; ob < p.batch; ++ob) {
       const Unit un = units[u];
       const int stage = stage_of(pass, un.gemm);
       if (stage >= p.max_stage) return;
@@ -881,8 +928,8 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
       else if (un.gemm == G_O) { m = &p.maps.attn; ev = EV_ATT; target = NROW_CTAS * (pass + 1); }
       else if (un.gemm == G_GU) { m = &p.maps.an_ffn; ev = EV_ANF; target = NROW_CTAS * (pass + 1); }
       else { m = &p.maps.act; ev = EV_GU; target = p.n_units[G_GU] * (pass + 1); }
-      if (!wait_event(c, p.ctrl + EVW(ev), target, stage)) return;
-      trace(p, c.cta, pass, un.gemm, 0);
+      if (!wait_event(c, p.ctrl + EVB(ev, ob), target, stage)) return;
+      if (ob == 0) trace(p, c.cta, pass, un.gemm, 0);
       ptx::fence_proxy_async_global();
       int kc = un.k0 * KSTAGE;
       for (int a = 0; a < un.nk; ++a, kc += KSTAGE) {
@@ -890,11 +937,11 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
         const uint32_t full = b.full + 8 * slot;
         const uint32_t dst = ring + slot * STAGE_BYTES_ALL + W_STAGE_BYTES;
         ptx::mbar_expect_tx(full, A_STAGE_TX);
-        ptx::tma_load_2d(dst, m, full, kc, 0);
-        ptx::tma_load_2d(dst + A_ATOM_BYTES, m, full, kc + KATOM, 0);
+        ptx::tma_load_2d(dst, m, full, kc, ob * T);          // rows of observation ob
+        ptx::tma_load_2d(dst + A_ATOM_BYTES, m, full, kc + KATOM, ob * T);
         if (++slot == NSTG) { slot = 0; par ^= 1; }
       }
-      trace(p, c.cta, pass, un.gemm, 1);
+      if (ob == 0) trace(p, c.cta, pass, un.gemm, 1);
     }
   }
 }
@@ -909,7 +956,8 @@ __device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units,
   const uint64_t adesc0 = ptx::umma_smem_desc(ring), bdesc0 = ptx::umma_smem_desc(ring + W_STAGE_BYTES);
   uint32_t it = 0, uit = 0, slot = 0, par = 0;
   for (int pass = 0; pass < npass; ++pass) {
-    for (int u = 0; u < nunits; ++u, ++uit) {
+    for (int u = 0; u < nunits; ++u)
+    for (int ob = 0; ob < p.batch; ++ob, ++uit) {
       const Unit un = units[u];
       const int stage = stage_of(pass, un.gemm);
       if (stage >= p.max_stage) return it;
@@ -920,7 +968,7 @@ __device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units,
       uint32_t accumulate = 0;
       for (int a = 0; a < un.nk; ++a, ++it) {
         if (!wait_mbar(c, b.full + 8 * slot, par, WAIT_W_FULL, stage)) return it;
-        if (a == 0) trace(p, c.cta, pass, un.gemm, 2);
+        if (a == 0 && ob == 0) trace(p, c.cta, pass, un.gemm, 2);
         ptx::tc_fence_after();
         const uint64_t ad = adesc0 + (uint64_t)(slot * (STAGE_BYTES_ALL >> 4));
         const uint64_t bd = bdesc0 + (uint64_t)(slot * (STAGE_BYTES_ALL >> 4));
@@ -937,7 +985,7 @@ __device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units,
         if (++slot == NSTG) { slot = 0; par ^= 1; }
       }
       ptx::umma_commit(b.tfull + 8 * buf);
-      trace(p, c.cta, pass, un.gemm, 3);
+      if (ob == 0) trace(p, c.cta, pass, un.gemm, 3);
     }
   }
   return it;
@@ -952,8 +1000,10 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
   __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + OFF_STAGE);
   uint32_t uit = 0;
   for (int pass = 0; pass < npass; ++pass) {
-    for (int u = 0; u < nunits; ++u, ++uit) {
+    for (int u = 0; u < nunits; ++u)
+    for (int ob = 0; ob < p.batch; ++ob, ++uit) {
       const Unit un = units[u];
+      const ObsPtrs o = obs(p, ob);
       const int stage = stage_of(pass, un.gemm);
       if (stage >= p.max_stage) return;
       const uint32_t buf = uit & 1;
@@ -964,7 +1014,7 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
                      : "=r"(any_fail) : "r"(ok ? 0 : 1) : "memory");
         if (any_fail) return;
       }
-      if (et == 0) trace(p, c.cta, pass, un.gemm, 4);
+      if (et == 0 && ob == 0) trace(p, c.cta, pass, un.gemm, 4);
       ptx::tc_fence_after();
       uint32_t r[64];
       {
@@ -978,7 +1028,7 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
       }
       ptx::tc_fence_before();
       ptx::mbar_arrive(b.tempty + 8 * buf);
-      if (et == 0) trace(p, c.cta, pass, un.gemm, 5);
+      if (et == 0 && ob == 0) trace(p, c.cta, pass, un.gemm, 5);
 
       if (un.gemm == G_QKV && un.tile >= 16) {
         // k / v tile over the full K: BF16 keys (with RoPE) / values straight to the buffers attention copies from
@@ -994,8 +1044,8 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
           const uint32_t* other = reinterpret_cast<const uint32_t*>(stg + (et ^ 64) * STAGE_STRIDE);
           const bool hi = et >= 64;
           const int j = (un.tile - 16) * 64 + (et & 63);
-          __nv_bfloat16* dst = p.k + j + (hi ? 128 : 0);
-          const uint2* __restrict__ rope = reinterpret_cast<const uint2*>(p.rope2) + j;
+          __nv_bfloat16* dst = o.k + j + (hi ? 128 : 0);
+          const uint2* __restrict__ rope = reinterpret_cast<const uint2*>(o.rope2) + j;
           uint2 cs[T / 2];
 #pragma unroll
           for (int tp = 0; tp < T / 2; ++tp) cs[tp] = __ldcg(rope + tp * (HD / 2));   // all loads in flight first
@@ -1013,7 +1063,7 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
             dst[(size_t)(2 * tp + 1) * HD] = __high2bfloat16(out);
           }
         } else {
-          __nv_bfloat16* dst = p.v + (un.tile - 18) * 128 + et;
+          __nv_bfloat16* dst = o.v + (un.tile - 18) * 128 + et;
 #pragma unroll
           for (int tp = 0; tp < T / 2; ++tp) {
             const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&pk[tp]);
@@ -1025,8 +1075,8 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
         // split-K partial: FP32 reduction into an L2-resident accumulator ([T][W] for O / down, [T][2560] for QKV)
         float* acc;
         int ldacc;
-        if (un.gemm == G_QKV) { acc = p.qkv_acc; ldacc = QKVW; }
-        else { acc = un.gemm == G_O ? p.o_acc : p.d_acc; ldacc = W; }
+        if (un.gemm == G_QKV) { acc = o.qkv_acc; ldacc = QKVW; }
+        else { acc = un.gemm == G_O ? o.o_acc : o.d_acc; ldacc = W; }
         acc += un.tile * 128 + et;   // accumulator column = tile row (k tiles: 64 dims, then their 64 partners)
 #pragma unroll
         for (int t = 0; t < T; ++t) ptx::red_add_f32(acc + (size_t)t * ldacc, __uint_as_float(r[t]));
@@ -1045,7 +1095,7 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
 #pragma unroll
         for (int i = 0; i < 8; ++i) { const uint4 v = other[i]; po[4 * i] = v.x; po[4 * i + 1] = v.y; po[4 * i + 2] = v.z; po[4 * i + 3] = v.w; }
         const bool is_up = et >= 64;
-        __nv_bfloat16* dst = p.act + un.tile * 64 + (et & 63);
+        __nv_bfloat16* dst = o.act + un.tile * 64 + (et & 63);
 #pragma unroll
         for (int t = 0; t < T; ++t) {
           if ((t >= 25) == is_up) {
@@ -1057,66 +1107,78 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
         }
         ptx::fence_proxy_async_global();   // act is read by the down projection's TMA
       }
-      if (et == 0) trace(p, c.cta, pass, un.gemm, 6);
+      if (et == 0 && ob == 0) trace(p, c.cta, pass, un.gemm, 6);
       ptx::named_bar_sync(1, 128);
       if (et == 0) {
         const int ev = un.gemm == G_QKV ? (un.tile >= 16 ? EV_KV : EV_QKV) : un.gemm == G_O ? EV_O : un.gemm == G_GU ? EV_GU : EV_DOWN;
-        signal_event(p.ctrl + EVW(ev));
-        trace(p, c.cta, pass, un.gemm, 7);
+        signal_event(p.ctrl + EVB(ev, ob));
+        if (ob == 0) trace(p, c.cta, pass, un.gemm, 7);
       }
     }
   }
 }
 
 // ------------------------------------------------------------------------------------------- row CTA main loop
-__device__ void cta_signal(const Params& p, int ev) {
+__device__ void cta_signal(const Params& p, int ev, int b) {
   __syncthreads();
-  if (threadIdx.x == 0 && ev != p.drop_event) signal_event(p.ctrl + EVW(ev));
+  if (threadIdx.x == 0 && ev != p.drop_event) signal_event(p.ctrl + EVB(ev, b));
 }
 
 __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, float (&hn)[8]) {
   const int npass = p.n_steps * p.n_layers;
   const int npc = (p.prefix + 63) / 64;
-  const bool stamp = p.stamps != nullptr && unit == 0 && threadIdx.x == 0;
+  const bool stamp0 = p.stamps != nullptr && unit == 0 && threadIdx.x == 0;
   for (int pass = 0; pass < npass; ++pass) {
     const int layer = pass % p.n_layers, step = pass / p.n_layers;
     const int sbase = 6 + pass * NSTAGE;
-    // ---- attention
+    // ---- attention, one observation after the other (each as soon as its own q is complete)
     if (pass * NSTAGE + ST_ATT >= p.max_stage) return;
-    AttChunkIssue issue{p, c, smem, layer, npc, pass};
-    // prefix chunks do not depend on this layer's QKV: fetch them before waiting
-    const int nearly = min(npc, ATT_STAGES);
-    for (int j = 0; j < nearly; ++j) issue(j, j);
-    if (!cta_wait_event(p, c, EV_QKV, (p.n_units[G_QKV] - NKVTILES) * (pass + 1), pass * NSTAGE + ST_ATT)) return;
-    if (stamp && sbase + ST_QKV < 64) p.stamps[sbase + ST_QKV] = globaltimer();
-    build_q(p, smem, unit);                               // q straight from the FP32 sums
-    const bool tr = stamp && pass == 1;
-    if (!attention_unit(p, smem, unit, issue, nearly, tr)) return;
-    if (tr) p.stamps[228] = globaltimer();
-    cta_signal(p, EV_ATT);
-    if (tr) p.stamps[229] = globaltimer();
-    if (stamp && sbase + ST_ATT < 64) p.stamps[sbase + ST_ATT] = globaltimer();
+    for (int ob = 0; ob < p.batch; ++ob) {
+      const ObsPtrs o = obs(p, ob);
+      const bool stamp = stamp0 && ob == 0;
+      AttChunkIssue issue{p, o, c, smem, layer, npc, pass};
+      // prefix chunks do not depend on this layer's QKV: fetch them before waiting
+      const int nearly = min(npc, ATT_STAGES);
+      for (int j = 0; j < nearly; ++j) issue(j, j);
+      if (!cta_wait_event(p, c, EVB(EV_QKV, ob), (p.n_units[G_QKV] - NKVTILES) * (pass + 1), pass * NSTAGE + ST_ATT)) return;
+      if (stamp && sbase + ST_QKV < 64) p.stamps[sbase + ST_QKV] = globaltimer();
+      build_q(o, smem, unit);                               // q straight from the FP32 sums
+      const bool tr = stamp && pass == 1;
+      if (!attention_unit(p, o, smem, unit, issue, nearly, tr)) return;
+      if (tr) p.stamps[228] = globaltimer();
+      cta_signal(p, EV_ATT, ob);
+      if (tr) p.stamps[229] = globaltimer();
+      if (stamp && sbase + ST_ATT < 64) p.stamps[sbase + ST_ATT] = globaltimer();
+    }
     // ---- residual + norm after the O projection
     if (pass * NSTAGE + ST_RATT >= p.max_stage) return;
     RowMod rm;
     row_prefetch(p, ROW_ATT, step, layer, rm);
-    if (!cta_wait_event(p, c, EV_O, p.n_units[G_O] * (pass + 1), pass * NSTAGE + ST_RATT)) return;
-    if (stamp && sbase + ST_O < 64) p.stamps[sbase + ST_O] = globaltimer();
-    row_op(p, smem, unit, ROW_ATT, step, layer, hn, rm);
-    if (tr) p.stamps[231] = globaltimer();
-    ptx::fence_proxy_async_global();
-    cta_signal(p, EV_ANF);
-    if (tr) p.stamps[232] = globaltimer();
-    if (stamp && sbase + ST_RATT < 64) p.stamps[sbase + ST_RATT] = globaltimer();
+    for (int ob = 0; ob < p.batch; ++ob) {
+      const ObsPtrs o = obs(p, ob);
+      const bool stamp = stamp0 && ob == 0;
+      if (!cta_wait_event(p, c, EVB(EV_O, ob), p.n_units[G_O] * (pass + 1), pass * NSTAGE + ST_RATT)) return;
+      if (stamp && sbase + ST_O < 64) p.stamps[sbase + ST_O] = globaltimer();
+      row_op(p, o, smem, unit, ROW_ATT, step, layer, hn, rm);
+      if (stamp && pass == 1) p.stamps[231] = globaltimer();
+      ptx::fence_proxy_async_global();
+      cta_signal(p, EV_ANF, ob);
+      if (stamp && pass == 1) p.stamps[232] = globaltimer();
+      if (stamp && sbase + ST_RATT < 64) p.stamps[sbase + ST_RATT] = globaltimer();
+    }
     // ---- residual + norm (or step tail) after the down projection
     if (pass * NSTAGE + ST_RFFN >= p.max_stage) return;
     row_prefetch(p, ROW_FFN, step, layer, rm);
-    if (!cta_wait_event(p, c, EV_DOWN, p.n_units[G_DOWN] * (pass + 1), pass * NSTAGE + ST_RFFN)) return;
-    if (stamp && sbase + ST_DOWN < 64) p.stamps[sbase + ST_DOWN] = globaltimer();
-    row_op(p, smem, unit, ROW_FFN, step, layer, hn, rm);
-    ptx::fence_proxy_async_global();
-    cta_signal(p, EV_ANA);
-    if (stamp && sbase + ST_RFFN < 64) p.stamps[sbase + ST_RFFN] = globaltimer();
+    for (int ob = 0; ob < p.batch; ++ob) {
+      const ObsPtrs o = obs(p, ob);
+      const bool stamp = stamp0 && ob == 0;
+      if (!cta_wait_event(p, c, EVB(EV_DOWN, ob), p.n_units[G_DOWN] * (pass + 1), pass * NSTAGE + ST_RFFN)) return;
+      if (stamp && sbase + ST_DOWN < 64) p.stamps[sbase + ST_DOWN] = globaltimer();
+      row_op(p, o, smem, unit, ROW_FFN, step, layer, hn, rm);
+      ptx::fence_proxy_async_global();
+      cta_signal(p, EV_ANA, ob);
+      if (stamp && sbase + ST_RFFN < 64) p.stamps[sbase + ST_RFFN] = globaltimer();
+    }
   }
 }
 
@@ -1159,7 +1221,7 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
   const uint32_t tmem = s_tmem;
 
   // The first ring of weights does not depend on anything: start streaming before the prologue.
-  Producer prod{0, 0, 0, 0u, 0u, 0u, false};
+  Producer prod{0, 0, 0, 0, 0u, 0u, 0u, false};
   uint64_t policy = 0;
   if (is_gemm && warp == 0 && lane == 0) {
     policy = ptx::policy_evict_first();
@@ -1196,9 +1258,11 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
       const int unit = cta - p.n_gemm_ctas;
       float hn[8];
       RowMod none;
-      row_op(p, smem, unit, ROW_INIT, 0, 0, hn, none);
-      ptx::fence_proxy_async_global();
-      cta_signal(p, EV_ANA);
+      for (int ob = 0; ob < p.batch; ++ob) {
+        row_op(p, obs(p, ob), smem, unit, ROW_INIT, 0, 0, hn, none);
+        ptx::fence_proxy_async_global();
+        cta_signal(p, EV_ANA, ob);
+      }
       if (stamp) p.stamps[5] = globaltimer();
       row_cta(p, c, smem, unit, hn);
     }
@@ -1224,7 +1288,7 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
     const unsigned prev = atomicAdd(p.ctrl + EVW(EV_EXIT), 1u);
     if (prev == (unsigned)ncta - 1) {
       __threadfence();
-      for (int e = 0; e < NEVENTS; ++e) p.ctrl[EVW(e)] = 0u;
+      for (int e = 0; e < NEVENTS * MAXB; ++e) p.ctrl[32 * (1 + e)] = 0u;
       __threadfence();
     }
   }
@@ -1242,6 +1306,8 @@ struct pi05_engine {
   int n_gemm = 0;
   int max_prefix = 0;
   int prefix = 0;
+  int max_batch = 1;
+  int batch = 1;
   bool bound = false;
   const void* inputs[PI05_NUM_INPUTS] = {};
   void* actions = nullptr;
@@ -1302,24 +1368,25 @@ void build_layout(pi05_engine* h) {
     h->regions.push_back({name, off, bytes});
     off = align_up(off + bytes, 256);
   };
+  const size_t B = (size_t)h->max_batch;      // per-observation buffers: observation b at b * (size / B)
   add("ctrl", CTRL_BYTES);
   add("temb", (size_t)NS * W * 4);
   add("hid", (size_t)NS * W * 4);
   add("cond", (size_t)NS * W * 4);
   add("mod", (size_t)NS * NNORM * MODW * 4);
-  add("rope", (size_t)T * (HD / 2) * 4);
-  add("rope2", (size_t)T * (HD / 2) * 4);
-  add("x", (size_t)T * ADIM * 4);
-  add("h", (size_t)T * W * 2);
-  add("an_attn", (size_t)T * W * 2);
-  add("an_ffn", (size_t)T * W * 2);
-  add("qkv_acc", (size_t)T * QKVW * 4);
-  add("k", (size_t)T * HD * 2);
-  add("v", (size_t)T * HD * 2);
-  add("attn", (size_t)T * QD * 2);
-  add("o_acc", (size_t)T * W * 4);
-  add("d_acc", (size_t)T * W * 4);
-  add("act", (size_t)T * FF * 2);
+  add("rope", B * T * (HD / 2) * 4);
+  add("rope2", B * T * (HD / 2) * 4);
+  add("x", B * T * ADIM * 4);
+  add("h", B * T * W * 2);
+  add("an_attn", B * T * W * 2);
+  add("an_ffn", B * T * W * 2);
+  add("qkv_acc", B * T * QKVW * 4);
+  add("k", B * T * HD * 2);
+  add("v", B * T * HD * 2);
+  add("attn", B * T * QD * 2);
+  add("o_acc", B * T * W * 4);
+  add("d_acc", B * T * W * 4);
+  add("act", B * T * FF * 2);
   add("sched", (size_t)h->grid * MAX_UNITS * sizeof(Unit));
   add("sched_n", (size_t)h->grid * sizeof(int));
   h->ws_bytes = off;
@@ -1419,7 +1486,7 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   if (device < 0 || max_prefix < 1 || max_prefix > 4096 || max_batch < 1 || tp_size < 1 || tp_rank < 0 ||
       tp_rank >= tp_size)
     return PI05_ERR_ARGUMENT;
-  if (max_batch != 1 || tp_size != 1) return PI05_ERR_UNSUPPORTED;
+  if (max_batch > MAXB || tp_size != 1) return PI05_ERR_UNSUPPORTED;
   int ndev = 0;
   if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) { cudaGetLastError(); return PI05_ERR_NO_DEVICE; }
   if (device >= ndev) return PI05_ERR_ARGUMENT;
@@ -1433,6 +1500,7 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   h->grid = h->sms;
   h->n_gemm = h->grid - NROW_CTAS;
   h->max_prefix = max_prefix;
+  h->max_batch = max_batch;
   if (!build_schedule(h)) { delete h; return PI05_ERR_UNSUPPORTED; }
   build_layout(h);
   if (const char* e = getenv("PI05_POLL_NS")) h->poll_ns = atoi(e);   // tuning knob, not part of the interface
@@ -1466,7 +1534,8 @@ int pi05_workspace_bytes(pi05_handle_t h, size_t* bytes) {
 int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, int batch, void* actions,
               void* workspace, size_t workspace_bytes) {
   if (!valid_handle(h) || !inputs || !actions || !workspace) return PI05_ERR_ARGUMENT;
-  if (batch != 1) return PI05_ERR_UNSUPPORTED;
+  if (batch < 1) return PI05_ERR_ARGUMENT;
+  if (batch > h->max_batch) return PI05_ERR_UNSUPPORTED;
   if (prefix_len < 1 || prefix_len > h->max_prefix) return PI05_ERR_ARGUMENT;
   if (workspace_bytes < h->ws_bytes) { h->last_error = "workspace too small"; return PI05_ERR_ARGUMENT; }
   for (int i = 0; i < PI05_NUM_INPUTS; ++i) {
@@ -1487,6 +1556,7 @@ int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int pr
   h->actions = actions;
   h->ws = static_cast<uint8_t*>(workspace);
   h->prefix = prefix_len;
+  h->batch = batch;
   cudaError_t e = cudaMemset(workspace, 0, h->ws_bytes);
   if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(workspace)", e);
   e = cudaMemcpy(region_ptr<void>(h, "sched"), h->sched.data(), h->sched.size() * sizeof(Unit), cudaMemcpyHostToDevice);
@@ -1501,10 +1571,10 @@ int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int pr
   if ((rc = encode_2d(h, &h->maps.wg, inputs[12], W, (uint64_t)NL * FF))) return rc;
   if ((rc = encode_2d(h, &h->maps.wu, inputs[13], W, (uint64_t)NL * FF))) return rc;
   if ((rc = encode_2d(h, &h->maps.wd, inputs[14], FF, (uint64_t)NL * W))) return rc;
-  if ((rc = encode_2d(h, &h->maps.an_attn, region_ptr<void>(h, "an_attn"), W, T, A_BOX_ROWS))) return rc;
-  if ((rc = encode_2d(h, &h->maps.an_ffn, region_ptr<void>(h, "an_ffn"), W, T, A_BOX_ROWS))) return rc;
-  if ((rc = encode_2d(h, &h->maps.attn, region_ptr<void>(h, "attn"), QD, T, A_BOX_ROWS))) return rc;
-  if ((rc = encode_2d(h, &h->maps.act, region_ptr<void>(h, "act"), FF, T, A_BOX_ROWS))) return rc;
+  if ((rc = encode_2d(h, &h->maps.an_attn, region_ptr<void>(h, "an_attn"), W, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
+  if ((rc = encode_2d(h, &h->maps.an_ffn, region_ptr<void>(h, "an_ffn"), W, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
+  if ((rc = encode_2d(h, &h->maps.attn, region_ptr<void>(h, "attn"), QD, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
+  if ((rc = encode_2d(h, &h->maps.act, region_ptr<void>(h, "act"), FF, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
   e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceSynchronize", e);
   h->bound = true;
@@ -1541,25 +1611,29 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.attn_nw = (const float*)in[15]; p.attn_nb = (const float*)in[16];
   p.ffn_nw = (const float*)in[17]; p.ffn_nb = (const float*)in[18];
   p.fin_nw = (const float*)in[19]; p.fin_nb = (const float*)in[20];
-  p.noise = (const float*)in[21];
   p.wq = (const __nv_bfloat16*)in[8]; p.wk = (const __nv_bfloat16*)in[9]; p.wv = (const __nv_bfloat16*)in[10];
   p.wo = (const __nv_bfloat16*)in[11]; p.wg = (const __nv_bfloat16*)in[12]; p.wu = (const __nv_bfloat16*)in[13];
   p.wd = (const __nv_bfloat16*)in[14];
-  p.prefix_k = (const __nv_bfloat16*)in[22]; p.prefix_v = (const __nv_bfloat16*)in[23];
-  p.prefix_mask = (const uint8_t*)in[24];
-  p.actions = (float*)h->actions;
+  ObsPtrs& o = p.ob;
+  o.noise = (const float*)in[21];
+  o.prefix_k = (const __nv_bfloat16*)in[22]; o.prefix_v = (const __nv_bfloat16*)in[23];
+  o.prefix_mask = (const uint8_t*)in[24];
+  o.actions = (float*)h->actions;
+  o.x = region_ptr<float>(h, "x"); o.o_acc = region_ptr<float>(h, "o_acc"); o.d_acc = region_ptr<float>(h, "d_acc");
+  o.qkv_acc = region_ptr<float>(h, "qkv_acc");
+  o.rope = region_ptr<uint32_t>(h, "rope"); o.rope2 = region_ptr<uint32_t>(h, "rope2");
+  o.h = region_ptr<__nv_bfloat16>(h, "h"); o.an_attn = region_ptr<__nv_bfloat16>(h, "an_attn");
+  o.an_ffn = region_ptr<__nv_bfloat16>(h, "an_ffn");
+  o.k = region_ptr<__nv_bfloat16>(h, "k"); o.v = region_ptr<__nv_bfloat16>(h, "v");
+  o.attn = region_ptr<__nv_bfloat16>(h, "attn"); o.act = region_ptr<__nv_bfloat16>(h, "act");
+  o.b = 0;
   p.ctrl = region_ptr<unsigned int>(h, "ctrl");
   p.temb = region_ptr<float>(h, "temb"); p.hid = region_ptr<float>(h, "hid"); p.cond = region_ptr<float>(h, "cond");
-  p.mod = region_ptr<float>(h, "mod"); p.x = region_ptr<float>(h, "x");
-  p.o_acc = region_ptr<float>(h, "o_acc"); p.d_acc = region_ptr<float>(h, "d_acc");
-  p.rope = region_ptr<uint32_t>(h, "rope"); p.rope2 = region_ptr<uint32_t>(h, "rope2");
-  p.h = region_ptr<__nv_bfloat16>(h, "h"); p.an_attn = region_ptr<__nv_bfloat16>(h, "an_attn");
-  p.an_ffn = region_ptr<__nv_bfloat16>(h, "an_ffn"); p.qkv_acc = region_ptr<float>(h, "qkv_acc");
-  p.k = region_ptr<__nv_bfloat16>(h, "k"); p.v = region_ptr<__nv_bfloat16>(h, "v");
-  p.attn = region_ptr<__nv_bfloat16>(h, "attn"); p.act = region_ptr<__nv_bfloat16>(h, "act");
+  p.mod = region_ptr<float>(h, "mod");
   p.sched = region_ptr<Unit>(h, "sched"); p.sched_n = region_ptr<int>(h, "sched_n");
   p.stamps = stamps;
   p.wait_limit = h->wait_limit;
+  p.batch = h->batch;
   p.prefix = h->prefix; p.n_steps = n_steps; p.n_layers = n_layers; p.max_stage = h->max_stage;
   p.n_gemm_ctas = h->n_gemm;
   p.drop_event = h->drop_event;

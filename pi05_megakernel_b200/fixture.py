@@ -21,6 +21,7 @@ ORDER = ("action_in_weight", "action_in_bias", "time_in_weight", "time_in_bias",
          "wq", "wk", "wv", "wo", "wg", "wu", "wd",
          "attn_norm_weight", "attn_norm_bias", "ffn_norm_weight", "ffn_norm_bias",
          "final_norm_weight", "final_norm_bias", "noise", "prefix_k", "prefix_v", "prefix_mask")
+OBSERVATION = ("noise", "prefix_k", "prefix_v", "prefix_mask")   # per-observation tensors; the rest are weights
 SEEDS = (7301, 8917, 42811)          # reference bench.py:373
 WEIGHT_STD = 0.02
 
@@ -110,6 +111,20 @@ def make_inputs(geo: Geometry, seed: int, device: str = "cpu", mask: str = "full
     values = make_weights(geo, seed)
     values.update(make_observation(geo, seed, mask))
     return {k: values[k].to(device) for k in ORDER}
+
+
+def make_batch(geo: Geometry, seed: int, batch: int, device: str = "cpu", masks=None) -> tuple[dict, list[dict]]:
+    """Weights of `seed` plus `batch` independent observations (seed + 1, seed + 2, ...).
+
+    Returns the stacked inputs for the engine (observation tensors get a leading batch index) and the list of
+    per-observation input dicts for a reference that works one observation at a time."""
+    weights = make_weights(geo, seed)
+    masks = masks or ["full"] * batch
+    per = [{**weights, **make_observation(geo, seed + 1 + b, masks[b])} for b in range(batch)]
+    stacked = dict(weights)
+    for name in OBSERVATION:
+        stacked[name] = torch.stack([o[name] for o in per]).contiguous()
+    return {k: stacked[k].to(device) for k in ORDER}, [{k: o[k] for k in ORDER} for o in per]
 
 
 def sol(geo: Geometry, batch: int = 1) -> dict:

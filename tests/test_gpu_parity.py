@@ -297,3 +297,31 @@ def test_abi_state_errors(case128):
     cnt = ctypes.c_ulonglong()
     assert lib.pi05_launch_count(h, ctypes.byref(cnt)) == _lib.OK and cnt.value == 1
     assert lib.pi05_destroy(h) == _lib.OK
+
+
+@pytest.mark.parametrize("batch,variant", [(2, "b200-s2-l3"), (4, "b200"), (16, "b200-s1-l2")])
+def test_batched_observations(batch, variant):
+    """Several independent observations in one launch (shared weights, own prefix cache / mask / noise each):
+    every observation's result must sit in the band of its own oracle run, and must not depend on its
+    neighbours (the first observation equals a batch-of-one run up to split-K summation order)."""
+    geo, ogeo = FX.Geometry(prefix=128), O.Geo(prefix=128)
+    masks = ["full", "pad", "scatter", "full"] * 4
+    stacked, per = FX.make_batch(geo, FX.SEEDS[0], batch, "cpu", masks[:batch])
+    arm = _arm(geo, variant)
+    arm.close()
+    from pi05_megakernel_b200.arm import Pi05Arm
+    arm = Pi05Arm(geo, variant, "cuda", batch=batch)
+    arm.bind({k: v.cuda() for k, v in stacked.items()})
+    got = _run(arm)
+    assert tuple(got.shape) == (batch, 50, 32)
+    for b in range(batch):
+        want = O.chunk(per[b], ogeo, False, arm.steps, arm.layers)
+        exact = O.chunk(per[b], ogeo, True, arm.steps, arm.layers)
+        d = O.band(want, got[b], exact)
+        assert d["pass"], (b, d)
+    one = Pi05Arm(geo, variant, "cuda", batch=1)
+    one.bind({k: v.cuda() for k, v in per[0].items()})
+    alone = _run(one)
+    assert float((alone - got[0]).abs().max()) <= 2 * (O.ATOL + O.RTOL * float(alone.abs().max()))
+    one.close()
+    arm.close()

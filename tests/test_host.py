@@ -41,7 +41,7 @@ def test_argument_errors_never_touch_a_gpu(lib):
     assert lib.pi05_create(-1, 128, 1, 0, 1, ctypes.byref(h)) == _lib.ERR_ARGUMENT
     assert lib.pi05_create(0, 0, 1, 0, 1, ctypes.byref(h)) == _lib.ERR_ARGUMENT
     assert lib.pi05_create(0, 128, 1, 2, 2, ctypes.byref(h)) == _lib.ERR_ARGUMENT
-    assert lib.pi05_create(0, 128, 4, 0, 1, ctypes.byref(h)) == _lib.ERR_UNSUPPORTED
+    assert lib.pi05_create(0, 128, 17, 0, 1, ctypes.byref(h)) == _lib.ERR_UNSUPPORTED
     assert lib.pi05_create(0, 128, 1, 0, 2, ctypes.byref(h)) == _lib.ERR_UNSUPPORTED
     n = ctypes.c_size_t()
     assert lib.pi05_workspace_bytes(None, ctypes.byref(n)) == _lib.ERR_ARGUMENT
