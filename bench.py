@@ -174,6 +174,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--prefix", type=int, default=128)
+    ap.add_argument("--batch", type=int, default=1, help="independent observations per GPU per launch (1..16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--stage-times", action="store_true",
                     help="also print (stderr) the in-kernel stage timeline of one L2-flushed chunk")
@@ -195,11 +196,13 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=device)
 
     geo = FX.Geometry(prefix=args.prefix)
+    B = args.batch
     weights = FX.make_weights(geo, FX.SEEDS[0])
-    obs = FX.make_observation(geo, DP.observation_seed(FX.SEEDS[0], rank))   # every GPU: its own observation
-    cpu = {k: {**weights, **obs}[k] for k in FX.ORDER}
+    obs = [FX.make_observation(geo, DP.observation_seed(FX.SEEDS[0], rank, i)) for i in range(B)]  # own observations
+    cpu = {k: weights[k] if k in weights else (obs[0][k] if B == 1 else torch.stack([o[k] for o in obs]).contiguous())
+           for k in FX.ORDER}
     dev = {k: v.to(device) for k, v in cpu.items()}
-    arm = Pi05Arm(geo, "b200", str(device))
+    arm = Pi05Arm(geo, "b200", str(device), batch=B)
     arm.bind(dev)
     l2 = torch.cuda.get_device_properties(device).L2_cache_size
     flush = torch.empty(2 * l2, dtype=torch.uint8, device=device)
@@ -239,7 +242,7 @@ def main() -> int:
     # ---- end to end through the arm with host buffers: pinned observation -> device, chunk, actions -> host
     obs_names = ("noise", "prefix_k", "prefix_v", "prefix_mask")
     pinned = {k: cpu[k].pin_memory() for k in obs_names}
-    host_out = torch.empty((geo.horizon, geo.action_dim), dtype=torch.float32).pin_memory()
+    host_out = torch.empty(tuple(arm.actions.shape), dtype=torch.float32).pin_memory()
     h2d = sum(pinned[k].numel() * pinned[k].element_size() for k in obs_names)
     d2h = host_out.numel() * 4
 
@@ -266,33 +269,33 @@ def main() -> int:
 
     if rank == 0:
         peak_gbs, peak_kind = measured_peaks()
-        floor = FX.sol(geo)
+        floor = FX.sol(geo, B)
         alg_bytes = floor["bytes_restream"]
         achieved = alg_bytes / (ms_step * 1e-3) / 1e9
         line = {
-            "metric": METRIC, "value": DP.chunks_per_second(world, ms_step), "unit": UNIT, "n_gpus": world,
+            "metric": METRIC if B == 1 else METRIC.replace("B=1", f"B={B}"), "value": DP.chunks_per_second(world, ms_step, B), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": (1e3 / ms_step) / (1e3 / SOTA_GRAPH_MS) if world == 1 else None,
+            "scaling": "weak", "vs_baseline": (1e3 / ms_step) / (1e3 / SOTA_GRAPH_MS) if world == 1 and B == 1 else None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"pi0.5 action chunk, B=1 per GPU, prefix {geo.prefix}, 10 Euler steps x 18 "
+            "config": {"workload": f"pi0.5 action chunk, B={B} per GPU, prefix {geo.prefix}, 10 Euler steps x 18 "
                                    "Gemma-300M expert layers, BF16 weights and prefix K/V, FP32 time MLP / "
                                    "modulation; one persistent kernel launch per chunk",
                        "l2": "flushed before every timed chunk (2x L2 zero fill)",
                        "parallelism": f"dp{world} (independent observations, replicated weights, no collective)",
                        "engine": arm.config},
-            "ms_per_chunk": ms_step, "ms_per_chunk_median": statistics.median(samples),
+            "ms_per_chunk": ms_step / B, "ms_per_launch_median": statistics.median(samples), "batch_per_gpu": B,
             "x_hbm_floor_nominal": ms_step / (alg_bytes / HBM_NOMINAL * 1e3),
             "x_hbm_floor_measured": ms_step / (alg_bytes / (peak_gbs * 1e9) * 1e3),
             "vs_baseline_note": f"value / (1000 / {SOTA_GRAPH_MS} ms), the reference's published sota-graph arm on one B200",
             "clocks": clocks,
-            "e2e": {"value": DP.chunks_per_second(world, e2e_step_ms), "unit": UNIT, "ms_per_chunk": e2e_step_ms,
+            "e2e": {"value": DP.chunks_per_second(world, e2e_step_ms, B), "unit": UNIT, "ms_per_chunk": e2e_step_ms / B,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                          "frac": achieved / peak_gbs, "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": alg_bytes, "traffic": ncu_traffic()},
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and B == 1 and not args.no_cpu_baseline:
             cps, cores = cpu_chunks_per_sec(geo, cpu, 5)
             line["cpu_baseline"] = {"value": cps, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": "5 whole chunks of the same workload (eager BF16 schedule)"}
