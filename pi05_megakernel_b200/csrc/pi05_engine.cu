@@ -1007,6 +1007,13 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
       const int stage = stage_of(pass, un.gemm);
       if (stage >= p.max_stage) return;
       const uint32_t buf = uit & 1;
+      // k tiles: the RoPE table words of this thread's rotary index are fetched now, while the MMAs still run
+      uint2 cs[T / 2];
+      if (un.gemm == G_QKV && un.tile >= 16 && un.tile < 18) {
+        const uint2* __restrict__ rope = reinterpret_cast<const uint2*>(o.rope2) + (un.tile - 16) * 64 + (et & 63);
+#pragma unroll
+        for (int tp = 0; tp < T / 2; ++tp) cs[tp] = __ldcg(rope + tp * (HD / 2));
+      }
       const bool ok = wait_mbar(c, b.tfull + 8 * buf, (uit >> 1) & 1, WAIT_T_FULL, stage);
       {  // all 128 threads agree on whether to go on
         int any_fail;
@@ -1045,10 +1052,6 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
           const bool hi = et >= 64;
           const int j = (un.tile - 16) * 64 + (et & 63);
           __nv_bfloat16* dst = o.k + j + (hi ? 128 : 0);
-          const uint2* __restrict__ rope = reinterpret_cast<const uint2*>(o.rope2) + j;
-          uint2 cs[T / 2];
-#pragma unroll
-          for (int tp = 0; tp < T / 2; ++tp) cs[tp] = __ldcg(rope + tp * (HD / 2));   // all loads in flight first
 #pragma unroll
           for (int tp = 0; tp < T / 2; ++tp) {
             // packed BF16 arithmetic on a token pair; _rn keeps every product and the sum separately rounded
