@@ -142,6 +142,7 @@ struct Params {
   unsigned long long* stamps;
   long long wait_limit;
   int prefix, n_steps, n_layers, max_stage, n_gemm_ctas, batch;
+  int row_groups;          // groups of NROW_CTAS row CTAs; group g serves observations g, g + row_groups, ...
   int poll_ns;             // pause between two samples of a stage counter
   int drop_event;          // debug: this event is never signalled (exercises the bounded waits); -1 = none
   int n_units[4];          // units per GEMM kind (event targets)
@@ -1127,61 +1128,67 @@ __device__ void cta_signal(const Params& p, int ev, int b) {
   if (threadIdx.x == 0 && ev != p.drop_event) signal_event(p.ctrl + EVB(ev, b));
 }
 
-__device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, float (&hn)[8]) {
-  const int npass = p.n_steps * p.n_layers;
-  const int npc = (p.prefix + 63) / 64;
-  const bool stamp0 = p.stamps != nullptr && unit == 0 && threadIdx.x == 0;
+// One layer-pass step of a row CTA for one observation.  Each returns false when a wait gave up.
+__device__ __forceinline__ bool row_attention(const Params& p, const Ctx& c, uint8_t* smem, int unit, int pass, int ob,
+                                              bool stamp0) {
+  const int layer = pass % p.n_layers, npc = (p.prefix + 63) / 64, sbase = 6 + pass * NSTAGE;
+  const ObsPtrs o = obs(p, ob);
+  const bool stamp = stamp0 && ob == 0;
+  AttChunkIssue issue{p, o, c, smem, layer, npc, pass};
+  // prefix chunks do not depend on this layer's QKV: fetch them before waiting
+  const int nearly = min(npc, ATT_STAGES);
+  for (int j = 0; j < nearly; ++j) issue(j, j);
+  if (!cta_wait_event(p, c, EVB(EV_QKV, ob), (p.n_units[G_QKV] - NKVTILES) * (pass + 1), pass * NSTAGE + ST_ATT)) return false;
+  if (stamp && sbase + ST_QKV < 64) p.stamps[sbase + ST_QKV] = globaltimer();
+  build_q(o, smem, unit);                               // q straight from the FP32 sums
+  const bool tr = stamp && pass == 1;
+  if (!attention_unit(p, o, smem, unit, issue, nearly, tr)) return false;
+  if (tr) p.stamps[228] = globaltimer();
+  cta_signal(p, EV_ATT, ob);
+  if (tr) p.stamps[229] = globaltimer();
+  if (stamp && sbase + ST_ATT < 64) p.stamps[sbase + ST_ATT] = globaltimer();
+  return true;
+}
+
+__device__ __forceinline__ bool row_residual(const Params& p, const Ctx& c, uint8_t* smem, int unit, int pass, int ob,
+                                             int mode, float (&hn)[8], bool stamp0) {
+  const int layer = pass % p.n_layers, step = pass / p.n_layers, sbase = 6 + pass * NSTAGE;
+  const ObsPtrs o = obs(p, ob);
+  const bool stamp = stamp0 && ob == 0;
+  const bool first = mode == ROW_ATT;
+  RowMod rm;
+  row_prefetch(p, mode, step, layer, rm);
+  if (!cta_wait_event(p, c, EVB(first ? EV_O : EV_DOWN, ob), p.n_units[first ? G_O : G_DOWN] * (pass + 1),
+                      pass * NSTAGE + (first ? ST_RATT : ST_RFFN))) return false;
+  if (stamp && sbase + (first ? ST_O : ST_DOWN) < 64) p.stamps[sbase + (first ? ST_O : ST_DOWN)] = globaltimer();
+  row_op(p, o, smem, unit, mode, step, layer, hn, rm);
+  if (stamp && pass == 1 && first) p.stamps[231] = globaltimer();
+  ptx::fence_proxy_async_global();
+  cta_signal(p, first ? EV_ANF : EV_ANA, ob);
+  if (stamp && pass == 1 && first) p.stamps[232] = globaltimer();
+  if (stamp && sbase + (first ? ST_RATT : ST_RFFN) < 64) p.stamps[sbase + (first ? ST_RATT : ST_RFFN)] = globaltimer();
+  return true;
+}
+
+// Row CTA `unit` of group `group`: attention and the two residual operations of every layer pass for the
+// observations group, group + row_groups, ...  With several observations the residual after the O projection of
+// one observation is done right after the attention of the next one, so that the gate/up GEMM of the first can
+// start while the others are still in attention.  (The GEMM CTAs run a pass as q(all observations), O(all),
+// gate/up(all), down(all); every wait below is for something earlier in that order than anything still queued.)
+__device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, int group, float (&hn)[8]) {
+  const int npass = p.n_steps * p.n_layers, G = p.row_groups;
+  const bool stamp0 = p.stamps != nullptr && unit == 0 && group == 0 && threadIdx.x == 0;
+  const int nobs = (p.batch - group + G - 1) / G;       // observations of this group
   for (int pass = 0; pass < npass; ++pass) {
-    const int layer = pass % p.n_layers, step = pass / p.n_layers;
-    const int sbase = 6 + pass * NSTAGE;
-    // ---- attention, one observation after the other (each as soon as its own q is complete)
     if (pass * NSTAGE + ST_ATT >= p.max_stage) return;
-    for (int ob = 0; ob < p.batch; ++ob) {
-      const ObsPtrs o = obs(p, ob);
-      const bool stamp = stamp0 && ob == 0;
-      AttChunkIssue issue{p, o, c, smem, layer, npc, pass};
-      // prefix chunks do not depend on this layer's QKV: fetch them before waiting
-      const int nearly = min(npc, ATT_STAGES);
-      for (int j = 0; j < nearly; ++j) issue(j, j);
-      if (!cta_wait_event(p, c, EVB(EV_QKV, ob), (p.n_units[G_QKV] - NKVTILES) * (pass + 1), pass * NSTAGE + ST_ATT)) return;
-      if (stamp && sbase + ST_QKV < 64) p.stamps[sbase + ST_QKV] = globaltimer();
-      build_q(o, smem, unit);                               // q straight from the FP32 sums
-      const bool tr = stamp && pass == 1;
-      if (!attention_unit(p, o, smem, unit, issue, nearly, tr)) return;
-      if (tr) p.stamps[228] = globaltimer();
-      cta_signal(p, EV_ATT, ob);
-      if (tr) p.stamps[229] = globaltimer();
-      if (stamp && sbase + ST_ATT < 64) p.stamps[sbase + ST_ATT] = globaltimer();
+    const bool do_ratt = pass * NSTAGE + ST_RATT < p.max_stage;
+    for (int k = 0; k <= nobs; ++k) {                   // attention of observation k, residual of observation k - 1
+      if (k < nobs && !row_attention(p, c, smem, unit, pass, group + k * G, stamp0)) return;
+      if (k >= 1 && do_ratt && !row_residual(p, c, smem, unit, pass, group + (k - 1) * G, ROW_ATT, hn, stamp0)) return;
     }
-    // ---- residual + norm after the O projection
-    if (pass * NSTAGE + ST_RATT >= p.max_stage) return;
-    RowMod rm;
-    row_prefetch(p, ROW_ATT, step, layer, rm);
-    for (int ob = 0; ob < p.batch; ++ob) {
-      const ObsPtrs o = obs(p, ob);
-      const bool stamp = stamp0 && ob == 0;
-      if (!cta_wait_event(p, c, EVB(EV_O, ob), p.n_units[G_O] * (pass + 1), pass * NSTAGE + ST_RATT)) return;
-      if (stamp && sbase + ST_O < 64) p.stamps[sbase + ST_O] = globaltimer();
-      row_op(p, o, smem, unit, ROW_ATT, step, layer, hn, rm);
-      if (stamp && pass == 1) p.stamps[231] = globaltimer();
-      ptx::fence_proxy_async_global();
-      cta_signal(p, EV_ANF, ob);
-      if (stamp && pass == 1) p.stamps[232] = globaltimer();
-      if (stamp && sbase + ST_RATT < 64) p.stamps[sbase + ST_RATT] = globaltimer();
-    }
-    // ---- residual + norm (or step tail) after the down projection
     if (pass * NSTAGE + ST_RFFN >= p.max_stage) return;
-    row_prefetch(p, ROW_FFN, step, layer, rm);
-    for (int ob = 0; ob < p.batch; ++ob) {
-      const ObsPtrs o = obs(p, ob);
-      const bool stamp = stamp0 && ob == 0;
-      if (!cta_wait_event(p, c, EVB(EV_DOWN, ob), p.n_units[G_DOWN] * (pass + 1), pass * NSTAGE + ST_RFFN)) return;
-      if (stamp && sbase + ST_DOWN < 64) p.stamps[sbase + ST_DOWN] = globaltimer();
-      row_op(p, o, smem, unit, ROW_FFN, step, layer, hn, rm);
-      ptx::fence_proxy_async_global();
-      cta_signal(p, EV_ANA, ob);
-      if (stamp && sbase + ST_RFFN < 64) p.stamps[sbase + ST_RFFN] = globaltimer();
-    }
+    for (int k = 0; k < nobs; ++k)
+      if (!row_residual(p, c, smem, unit, pass, group + k * G, ROW_FFN, hn, stamp0)) return;
   }
 }
 
@@ -1258,16 +1265,16 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
         epilogue(p, c, units, nunits, smem, b, tmem);
       }
     } else {
-      const int unit = cta - p.n_gemm_ctas;
+      const int unit = (cta - p.n_gemm_ctas) % NROW_CTAS, group = (cta - p.n_gemm_ctas) / NROW_CTAS;
       float hn[8];
       RowMod none;
-      for (int ob = 0; ob < p.batch; ++ob) {
+      for (int ob = group; ob < p.batch; ob += p.row_groups) {
         row_op(p, obs(p, ob), smem, unit, ROW_INIT, 0, 0, hn, none);
         ptx::fence_proxy_async_global();
         cta_signal(p, EV_ANA, ob);
       }
       if (stamp) p.stamps[5] = globaltimer();
-      row_cta(p, c, smem, unit, hn);
+      row_cta(p, c, smem, unit, group, hn);
     }
   } else if (is_gemm && warp == 0 && lane == 0) {
     s_issued = prod.it;
@@ -1311,6 +1318,7 @@ struct pi05_engine {
   int prefix = 0;
   int max_batch = 1;
   int batch = 1;
+  int row_groups = 1;
   bool bound = false;
   const void* inputs[PI05_NUM_INPUTS] = {};
   void* actions = nullptr;
@@ -1501,6 +1509,7 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   h->device = device;
   h->sms = prop.multiProcessorCount;
   h->grid = h->sms;
+  h->row_groups = 1;
   h->n_gemm = h->grid - NROW_CTAS;
   h->max_prefix = max_prefix;
   h->max_batch = max_batch;
@@ -1560,6 +1569,15 @@ int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int pr
   h->ws = static_cast<uint8_t*>(workspace);
   h->prefix = prefix_len;
   h->batch = batch;
+  {
+    // More observations keep more row CTAs busy: one group of 25 per observation in flight, as long as the GEMM
+    // side keeps its 64 gate/up CTAs plus the 4 k / v CTAs.
+    int groups = batch >= 8 ? 3 : batch >= 2 ? 2 : 1;
+    while (groups > 1 && h->grid - groups * NROW_CTAS < 64 + NKVTILES) --groups;
+    h->row_groups = groups;
+    h->n_gemm = h->grid - groups * NROW_CTAS;
+    if (!build_schedule(h)) { h->last_error = "no schedule for this GPU"; return PI05_ERR_UNSUPPORTED; }
+  }
   cudaError_t e = cudaMemset(workspace, 0, h->ws_bytes);
   if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(workspace)", e);
   e = cudaMemcpy(region_ptr<void>(h, "sched"), h->sched.data(), h->sched.size() * sizeof(Unit), cudaMemcpyHostToDevice);
@@ -1639,6 +1657,7 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.batch = h->batch;
   p.prefix = h->prefix; p.n_steps = n_steps; p.n_layers = n_layers; p.max_stage = h->max_stage;
   p.n_gemm_ctas = h->n_gemm;
+  p.row_groups = h->row_groups;
   p.drop_event = h->drop_event;
   p.poll_ns = h->poll_ns;
   for (int g = 0; g < 4; ++g) p.n_units[g] = h->n_units[g];
