@@ -8,7 +8,8 @@ import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = [os.path.join(HERE, "csrc", "pi05_engine.cu")]
-HEADERS = [os.path.join(HERE, "csrc", "ptx_sm100.cuh"),
+HEADERS = [os.path.join(HERE, "csrc", "ptx_sm100.cuh"), os.path.join(HERE, "csrc", "pi05_common.cuh"),
+           os.path.join(HERE, "csrc", "pi05_chunk_kernel.cuh"),
            os.path.join(os.path.dirname(HERE), "include", "pi05_b200.h")]
 LIB = os.path.join(HERE, "libpi05_b200.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
