@@ -1,10 +1,17 @@
 // The chunk kernel and all of its device code.  This file has no include guard on purpose: the translation unit
 // includes it once per variant, inside a namespace of its own, with two macros set:
-//   PI05_TRACE    1: the kernel writes globaltimer stamps when given a stamp buffer (profiling builds of the same
-//                    code); 0: no trace code at all (the single-thread issue loops are sensitive to every
-//                    instruction: the production kernel is ~3 % faster without it)
+//   PI05_TRACE    1: the kernel writes globaltimer stamps when given a stamp buffer and honours the debug controls
+//                    (stage limit, withheld signal); 0: none of that code exists (the single-thread issue loops
+//                    are sensitive to every instruction: the production kernel is ~3 % faster without it)
 //   PI05_BATCHED  1: any number of observations per launch; 0: exactly one, and all per-observation pointer
 //                    arithmetic and loops fold away
+#if PI05_TRACE
+#define PI05_MAXSTAGE(p) ((p).max_stage)
+#define PI05_DROP(p) ((p).drop_event)
+#else
+#define PI05_MAXSTAGE(p) 0x7fffffff
+#define PI05_DROP(p) (-1)
+#endif
 #if PI05_BATCHED
 #define PI05_NB(p) ((p).batch)
 #define PI05_NG(p) ((p).row_groups)
@@ -741,7 +748,7 @@ __device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units
     if (st.pass >= npass) { st.done = true; break; }
     const Unit un = units[st.u];
     const int stage = stage_of(st.pass, un.gemm);
-    if (stage >= p.max_stage) { st.done = true; break; }
+    if (stage >= PI05_MAXSTAGE(p)) { st.done = true; break; }
     const CUtensorMap *ma, *mb;
     int ra, rbw;
     weight_rows(p, un, st.pass % p.n_layers, ma, mb, ra, rbw);
@@ -787,7 +794,7 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
     for (int ob = 0; ob < PI05_NB(p); ++ob) {
       const Unit un = units[u];
       const int stage = stage_of(pass, un.gemm);
-      if (stage >= p.max_stage) return;
+      if (stage >= PI05_MAXSTAGE(p)) return;
       const CUtensorMap* m;
       int ev;
       unsigned target;
@@ -827,7 +834,7 @@ __device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units,
     for (int ob = 0; ob < PI05_NB(p); ++ob, ++uit) {
       const Unit un = units[u];
       const int stage = stage_of(pass, un.gemm);
-      if (stage >= p.max_stage) return it;
+      if (stage >= PI05_MAXSTAGE(p)) return it;
       const uint32_t buf = uit & 1;
       if (!wait_mbar(c, b.tempty + 8 * buf, ((uit >> 1) & 1) ^ 1, WAIT_T_EMPTY, stage)) return it;
       ptx::tc_fence_after();
@@ -872,7 +879,7 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
       const Unit un = units[u];
       const ObsPtrs o = obs(p, ob);
       const int stage = stage_of(pass, un.gemm);
-      if (stage >= p.max_stage) return;
+      if (stage >= PI05_MAXSTAGE(p)) return;
       const uint32_t buf = uit & 1;
       // k tiles: the RoPE table words of this thread's rotary index are fetched now, while the MMAs still run
       uint2 cs[T / 2];
@@ -991,7 +998,7 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
 // ------------------------------------------------------------------------------------------- row CTA main loop
 __device__ void cta_signal(const Params& p, int ev, int b) {
   __syncthreads();
-  if (threadIdx.x == 0 && ev != p.drop_event) signal_event(p.ctrl + EVB(ev, b));
+  if (threadIdx.x == 0 && ev != PI05_DROP(p)) signal_event(p.ctrl + EVB(ev, b));
 }
 
 // One layer-pass step of a row CTA for one observation.  Each returns false when a wait gave up.
@@ -1046,13 +1053,13 @@ __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, 
   const bool stamp0 = PI05_TRACE && p.stamps != nullptr && unit == 0 && group == 0 && threadIdx.x == 0;
   const int nobs = (PI05_NB(p) - group + G - 1) / G;       // observations of this group
   for (int pass = 0; pass < npass; ++pass) {
-    if (pass * NSTAGE + ST_ATT >= p.max_stage) return;
-    const bool do_ratt = pass * NSTAGE + ST_RATT < p.max_stage;
+    if (pass * NSTAGE + ST_ATT >= PI05_MAXSTAGE(p)) return;
+    const bool do_ratt = pass * NSTAGE + ST_RATT < PI05_MAXSTAGE(p);
     for (int k = 0; k <= nobs; ++k) {                   // attention of observation k, residual of observation k - 1
       if (k < nobs && !row_attention(p, c, smem, unit, pass, group + k * G, stamp0)) return;
       if (k >= 1 && do_ratt && !row_residual(p, c, smem, unit, pass, group + (k - 1) * G, ROW_ATT, hn, stamp0)) return;
     }
-    if (pass * NSTAGE + ST_RFFN >= p.max_stage) return;
+    if (pass * NSTAGE + ST_RFFN >= PI05_MAXSTAGE(p)) return;
     for (int k = 0; k < nobs; ++k)
       if (!row_residual(p, c, smem, unit, pass, group + k * G, ROW_FFN, hn, stamp0)) return;
   }
@@ -1172,3 +1179,5 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
 
 #undef PI05_NB
 #undef PI05_NG
+#undef PI05_MAXSTAGE
+#undef PI05_DROP

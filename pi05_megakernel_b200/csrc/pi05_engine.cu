@@ -425,8 +425,10 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   for (int s = 0; s < NS; ++s) p.t_steps[s] = (float)(1.0 + s * dt);
   p.dt = (float)dt;
   void* args[] = {&p};
-  // stamps wanted: the traced build; otherwise the build without trace code, specialised for one observation
-  const void* kern = stamps ? (const void*)k_traced::pi05_chunk_kernel
+  // stamps or a debug control wanted: the traced build; otherwise the build without that code, specialised for
+  // one observation when there is only one
+  const bool debug = stamps != nullptr || h->max_stage != 0x7fffffff || h->drop_event >= 0;
+  const void* kern = debug ? (const void*)k_traced::pi05_chunk_kernel
                             : h->batch > 1 ? (const void*)k_batched::pi05_chunk_kernel
                                            : (const void*)k_plain::pi05_chunk_kernel;
   cudaError_t e = cudaLaunchCooperativeKernel(kern, dim3(h->grid), dim3(THREADS), args,
