@@ -136,7 +136,7 @@ int pi05_destroy(pi05_handle_t h);
  * The first call on a device does the set-up (host-side state, address of the array, shared-memory opt-in), and
  * the first call with a given set of pointers / prefix length encodes the TMA descriptors and clears the array;
  * both synchronise the device, so make that call once before any stream capture or latency-critical region.
- * Later calls with the same pointers only enqueue a 1 KB memset and the kernel on `stream`.  No cudaMalloc,
+ * Later calls with the same pointers only enqueue a memset of the control block (about 30 KB) and the kernel on `stream`.  No cudaMalloc,
  * cudaFree or allocating library routine is called on any of these paths.
  *
  * Limits: prefix_len <= PI05_STATIC_MAX_PREFIX and a GPU whose schedule fits the array (any B200), otherwise

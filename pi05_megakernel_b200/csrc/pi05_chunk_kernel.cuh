@@ -520,44 +520,73 @@ __device__ bool cta_wait_event(const Params& p, const Ctx& c, int word, unsigned
   return ok != 0;
 }
 
+// Parities of the attention barriers of a row CTA (bit j: keys of stage j, bit 8 + j: values of stage j) and which of
+// them have a copy in flight that nobody has waited for yet.
+struct AttBars {
+  uint32_t parity = 0, pending = 0;
+};
+
+__device__ __forceinline__ uint32_t att_bar(uint8_t* smem, int isv, int stage) {
+  return ptx::smem_u32(smem + OFF_ATTBARS) + 8 * (isv * ATT_STAGES + stage);
+}
+
+// All threads wait until the keys (isv = 0) or values (isv = 1) of `stage` have landed.
+__device__ __forceinline__ bool att_wait(const Ctx& c, uint8_t* smem, AttBars& bars, int isv, int stage, int st) {
+  const uint32_t bit = 1u << (8 * isv + stage);
+  const bool ok = wait_mbar(c, att_bar(smem, isv, stage), (bars.parity & bit) ? 1u : 0u, WAIT_A_FULL, st);
+  bars.parity ^= bit;
+  bars.pending &= ~bit;
+  return ok;
+}
+
+// Before a row CTA gives up: let its own copies in flight land (bounded like every wait).
+__device__ void att_drain(const Ctx& c, uint8_t* smem, AttBars& bars, int st) {
+  for (int isv = 0; isv < 2; ++isv)
+    for (int j = 0; j < ATT_STAGES; ++j)
+      if (bars.pending & (1u << (8 * isv + j))) att_wait(c, smem, bars, isv, j, st);
+}
+
 struct AttChunkIssue {
   const Params& p;
   const ObsPtrs& o;
   const Ctx& c;
   uint8_t* smem;
-  int layer, npc, pass;
-  // chunk < npc: prefix keys [64*chunk, ...); chunk == npc: the 50 suffix keys; chunk > npc: nothing (stage off)
+  AttBars& bars;
+  int layer, npc, pass, cend;
+  // chunk < npc: prefix keys [64*chunk, ...); chunk == npc: the 50 suffix keys; chunk >= cend (the end of this CTA's
+  // share of the keys) or > npc: nothing (stage off)
+  // `which`: 1 = keys only, 2 = values (and the validity bytes, which the previous occupant's softmax has read by
+  // then) only, 3 = both.  One thread issues four tiled copies (64 dims each) per chunk of keys or of values; they
+  // complete on the stage's barriers, and rows past the end of a short chunk arrive as zeros.
   // Collective over the CTA.  Returns false when the wait for the suffix keys gave up.
-  __device__ bool operator()(int chunk, int stage) const {
+  __device__ bool operator()(int chunk, int stage, int which = 3) const {
     const int tid = threadIdx.x;
-    if (chunk == npc &&
+    const bool live = chunk <= npc && chunk < cend;
+    if (chunk == npc && live && (which & 1) &&
         !cta_wait_event(p, c, EVB(EV_KV, o.b), NKVTILES * (pass + 1), pass * NSTAGE + ST_ATT)) return false;
-    uint8_t* ks = smem + OFF_KS + stage * KV_STAGE_BYTES;
-    uint8_t* vs = smem + OFF_VS + stage * KV_STAGE_BYTES;
-    uint8_t* kvalid = smem + OFF_KVALID + stage * 64;
     const bool is_prefix = chunk < npc;
-    const __nv_bfloat16* ksrc = is_prefix ? o.prefix_k + ((size_t)layer * p.prefix + (size_t)chunk * 64) * HD : o.k;
-    const __nv_bfloat16* vsrc = is_prefix ? o.prefix_v + ((size_t)layer * p.prefix + (size_t)chunk * 64) * HD : o.v;
-    const int nrows = chunk > npc ? 0 : (is_prefix ? min(64, p.prefix - chunk * 64) : T);
-    if (tid < 64) {
+    if (tid < 64 && (which & 2)) {
+      const int nrows = !live ? 0 : (is_prefix ? min(64, p.prefix - chunk * 64) : T);
       uint8_t ok = 0;
       if (tid < nrows) ok = is_prefix ? (o.prefix_mask[chunk * 64 + tid] ? 1 : 0) : 1;
-      kvalid[tid] = ok;
+      smem[OFF_KVALID + stage * 64 + tid] = ok;
     }
-    // 64 rows x 32 16-byte pieces for K, then the same for V; rows past the end are zero-filled.  The suffix chunk
-    // is the one attention waits for, so its keys and its values are separate groups: scoring starts on the keys.
+    if (!live) return true;
+#pragma unroll
     for (int isv = 0; isv < 2; ++isv) {
-      if (nrows > 0) {
-        for (int idx = tid; idx < 64 * 32; idx += THREADS) {
-          const int r = idx >> 5, cidx = idx & 31;
-          uint8_t* dst = (isv ? vs : ks) + r * (KV_STRIDE * 2) + cidx * 16;
-          if (r < nrows) ptx::cp_async_16(ptx::smem_u32(dst), (isv ? vsrc : ksrc) + (size_t)r * HD + cidx * 8);
-          else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-        }
+      if (!((which >> isv) & 1)) continue;
+      if (tid == 0) {
+        const uint32_t dst = ptx::smem_u32(smem + (isv ? OFF_VS : OFF_KS) + stage * KV_STAGE_BYTES);
+        const uint32_t bar = att_bar(smem, isv, stage);
+        const CUtensorMap* m = is_prefix ? (isv ? &p.maps.pv : &p.maps.pk) : (isv ? &p.maps.sv : &p.maps.sk);
+        const int row = is_prefix ? chunk * 64 : 0, plane = is_prefix ? o.b * NL + layer : o.b;
+        if (!is_prefix) ptx::fence_proxy_async_global();   // the suffix rows were written by GEMM epilogues
+        ptx::mbar_expect_tx(bar, KV_STAGE_BYTES);
+#pragma unroll
+        for (int sg = 0; sg < 4; ++sg) ptx::tma_load_3d(dst + sg * KV_SEG_BYTES, m, bar, sg * 64, row, plane);
       }
-      if (chunk == npc && isv == 0) ptx::cp_async_commit();
+      bars.pending |= 1u << (8 * isv + stage);
     }
-    ptx::cp_async_commit();
     return true;
   }
 };
@@ -566,13 +595,15 @@ struct AttChunkIssue {
 __device__ __forceinline__ void att_qk(uint32_t qs, uint32_t ks, int warp, int lane, float (&s4)[4]) {
   float e[4] = {0.f, 0.f, 0.f, 0.f}, o[4] = {0.f, 0.f, 0.f, 0.f};
   const uint32_t qaddr0 = qs + ((lane & 15) * KV_STRIDE + (lane >> 4) * 8) * 2;
-  const uint32_t kaddr0 = ks + ((warp * 8 + (lane & 7)) * KV_STRIDE + (lane >> 3) * 8) * 2;
+  // key row r = warp * 8 + (lane & 7); 16-byte piece c of the row sits at piece c ^ (r & 7) of its 128-byte line
+  const uint32_t krow = ks + (warp * 8 + (lane & 7)) * 128;
+  const uint32_t ksw = lane & 7, kc = lane >> 3;
 #pragma unroll
   for (int kk = 0; kk < HD / 16; kk += 2) {
     uint32_t a0, a1, a2, a3, a4, a5, a6, a7, b0, b1, b2, b3;
     ptx::ldmatrix_x4(qaddr0 + kk * 32, a0, a1, a2, a3);
     ptx::ldmatrix_x4(qaddr0 + kk * 32 + 32, a4, a5, a6, a7);
-    ptx::ldmatrix_x4(kaddr0 + kk * 32, b0, b1, b2, b3);
+    ptx::ldmatrix_x4(krow + (kk >> 2) * KV_SEG_BYTES + ((((kk & 3) * 2 + kc) ^ ksw) << 4), b0, b1, b2, b3);
     ptx::mma_16816(e, a0, a1, a2, a3, b0, b1);
     ptx::mma_16816(o, a4, a5, a6, a7, b2, b3);
   }
@@ -583,12 +614,15 @@ __device__ __forceinline__ void att_qk(uint32_t qs, uint32_t ks, int warp, int l
 // The first `nearly` stages (prefix chunks) were issued by the caller before q was ready.  Scores against them are
 // computed first; the suffix keys are waited for and copied only then, so the k / v tiles of the QKV GEMM may
 // finish later than the q tiles without holding attention up.  Returns false when a wait gave up.
+// With key groups (one observation, long prefix) the CTA covers only chunks [cbeg, cend) of the keys: groups >= 1 leave
+// their unnormalised accumulators, running maxima and sums in global memory (`kg` = their group), group 0 merges
+// them into its own (flash-decoding style) before it normalises.
 __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem, int unit, const AttChunkIssue& issue,
-                               int nearly, bool tr) {
-  const int npc = issue.npc;
+                               int cbeg, int nearly, int kg, bool tr) {
+  const int cend = issue.cend, wst = issue.pass * NSTAGE + ST_ATT;
+  AttBars& bars = issue.bars;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, qd = lane & 3;
-  const int nchunks = npc + 1;
   const uint32_t qs = ptx::smem_u32(smem + OFF_QS), ps = ptx::smem_u32(smem + OFF_PS);
   float* red = reinterpret_cast<float*>(smem + OFF_RED);
   const float NEG = -INFINITY;
@@ -600,26 +634,30 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
 #pragma unroll
     for (int b = 0; b < 4; ++b) oa[a][b] = 0.f;
 
-  for (int c0 = 0; c0 < nchunks; c0 += ATT_STAGES) {
-    const int nst = min(ATT_STAGES, nchunks - c0);
+  for (int c0 = cbeg; c0 < cend; c0 += ATT_STAGES) {
+    const int nst = min(ATT_STAGES, cend - c0);
     float sc[ATT_STAGES][4];
     // ---- scores; in the first pass the prefix stages are used while the suffix keys are still being produced
-    const int early = (c0 == 0) ? nearly : nst;
-    ptx::cp_async_wait<0>();
-    __syncthreads();
-    if (tr && c0 == 0) p.stamps[224] = globaltimer();
+    const int early = (c0 == cbeg) ? nearly : nst;
+    const bool more = c0 + ATT_STAGES < cend;
+    __syncthreads();                                   // q is in place (first round)
+    if (tr && c0 == cbeg) p.stamps[224] = globaltimer();
 #pragma unroll
     for (int j = 0; j < ATT_STAGES; ++j)
-      if (j < early) att_qk(qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
+      if (j < early) {
+        if (!att_wait(issue.c, smem, bars, 0, j, wst)) return false;
+        att_qk(qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
+      }
     if (early < nst) {
       if (!issue(c0 + early, early)) return false;     // waits for the k / v tiles, then copies the suffix chunk
-      ptx::cp_async_wait<1>();                         // its keys have landed; its values may still be in flight
-      __syncthreads();
 #pragma unroll
       for (int j = 0; j < ATT_STAGES; ++j)
-        if (j >= early && j < nst) att_qk(qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
+        if (j >= early && j < nst) {
+          if (!att_wait(issue.c, smem, bars, 0, j, wst)) return false;
+          att_qk(qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
+        }
     }
-    if (tr && c0 == 0) p.stamps[225] = globaltimer();
+    if (tr && c0 == cbeg) p.stamps[225] = globaltimer();
     // ---- mask, chunk max
     float cm_lo = NEG, cm_hi = NEG;
 #pragma unroll
@@ -645,10 +683,14 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
       mn_lo = fmaxf(mn_lo, red[w8 * 16 + g]);
       mn_hi = fmaxf(mn_hi, red[w8 * 16 + g + 8]);
     }
+    // every warp has scored these key stages: refill them for the next round while softmax and P V run
+    if (more) {
+      for (int j = 0; j < ATT_STAGES; ++j)
+        if (!issue(c0 + ATT_STAGES + j, j, 1)) return false;
+    }
     const float al_lo = __expf(m_lo - mn_lo), al_hi = __expf(m_hi - mn_hi);
     m_lo = mn_lo; m_hi = mn_hi;
     l_lo *= al_lo; l_hi *= al_hi;
-    ptx::cp_async_wait<0>();                           // suffix values (ordered for everyone by the barrier below)
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) { oa[nt][0] *= al_lo; oa[nt][1] *= al_lo; oa[nt][2] *= al_hi; oa[nt][3] *= al_hi; }
 #pragma unroll
@@ -664,20 +706,22 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
       }
     }
     __syncthreads();
-    if (tr && c0 == 0) p.stamps[226] = globaltimer();
+    if (tr && c0 == cbeg) p.stamps[226] = globaltimer();
     // ---- O += P V for this warp's 32 output dims
-    const int db = warp * 32;
 #pragma unroll
     for (int j = 0; j < ATT_STAGES; ++j) {
       if (j < nst) {
+        if (!att_wait(issue.c, smem, bars, 1, j, wst)) return false;
         const uint32_t vs = ptx::smem_u32(smem + OFF_VS + j * KV_STAGE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           uint32_t a0, a1, a2, a3, r0, r1, r2, r3, r4, r5, r6, r7;
           ptx::ldmatrix_x4(ps + ((lane & 15) * P_STRIDE + j * 64 + kk * 16 + (lane >> 4) * 8) * 2, a0, a1, a2, a3);
-          const uint32_t vaddr = vs + ((kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KV_STRIDE + db + (lane >> 4) * 8) * 2;
-          ptx::ldmatrix_x4_trans(vaddr, r0, r1, r2, r3);
-          ptx::ldmatrix_x4_trans(vaddr + 32, r4, r5, r6, r7);
+          // value row r, dims db + (lane >> 4) * 8 (+16): segment warp / 2, piece (warp & 1) * 4 + (lane >> 4) (+2)
+          const uint32_t vrow = vs + (warp >> 1) * KV_SEG_BYTES + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 128;
+          const uint32_t vc = (warp & 1) * 4 + (lane >> 4), vsw = lane & 7;
+          ptx::ldmatrix_x4_trans(vrow + ((vc ^ vsw) << 4), r0, r1, r2, r3);
+          ptx::ldmatrix_x4_trans(vrow + (((vc + 2) ^ vsw) << 4), r4, r5, r6, r7);
           ptx::mma_16816(oa[0], a0, a1, a2, a3, r0, r1);
           ptx::mma_16816(oa[1], a0, a1, a2, a3, r2, r3);
           ptx::mma_16816(oa[2], a0, a1, a2, a3, r4, r5);
@@ -685,11 +729,11 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
         }
       }
     }
-    if (tr && c0 == 0) p.stamps[227] = globaltimer();
-    if (c0 + ATT_STAGES < nchunks) {
-      __syncthreads();   // every warp is done with P and these K/V stages
+    if (tr && c0 == cbeg) p.stamps[227] = globaltimer();
+    if (more) {
+      __syncthreads();   // every warp is done with P and these value stages
       for (int j = 0; j < ATT_STAGES; ++j)
-        if (!issue(c0 + ATT_STAGES + j, j)) return false;
+        if (!issue(c0 + ATT_STAGES + j, j, 2)) return false;
     }
   }
   // ---- normalise and store
@@ -701,6 +745,40 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
   float tl_lo = 0.f, tl_hi = 0.f;
 #pragma unroll
   for (int w8 = 0; w8 < 8; ++w8) { tl_lo += red[w8 * 16 + g]; tl_hi += red[w8 * 16 + g + 8]; }
+  if (kg > 0) {
+    // partial result of key group kg: this thread's 16 accumulators, then (max, sum) of every row
+    float* part = p.att_part + ((size_t)(kg - 1) * NROW_CTAS + unit) * ATT_PART_FLOATS;
+    float4* po = reinterpret_cast<float4*>(part) + tid * 4;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) po[nt] = make_float4(oa[nt][0], oa[nt][1], oa[nt][2], oa[nt][3]);
+    if (warp == 0 && qd == 0) {
+      reinterpret_cast<float2*>(part + 256 * 16)[g] = make_float2(m_lo, tl_lo);
+      reinterpret_cast<float2*>(part + 256 * 16)[g + 8] = make_float2(m_hi, tl_hi);
+    }
+    return true;
+  }
+  if (p.key_groups > 1) {
+    // merge the other groups' partial results (they cover disjoint keys): rescale everything to the common maximum
+    if (!cta_wait_event(p, issue.c, EVB(EV_PART, o.b), NROW_CTAS * (p.key_groups - 1) * (issue.pass + 1),
+                        issue.pass * NSTAGE + ST_ATT)) return false;
+    for (int og = 1; og < p.key_groups; ++og) {
+      const float* part = p.att_part + ((size_t)(og - 1) * NROW_CTAS + unit) * ATT_PART_FLOATS;
+      const float2 ml_lo = __ldcg(reinterpret_cast<const float2*>(part + 256 * 16) + g);
+      const float2 ml_hi = __ldcg(reinterpret_cast<const float2*>(part + 256 * 16) + g + 8);
+      const float M_lo = fmaxf(m_lo, ml_lo.x), M_hi = fmaxf(m_hi, ml_hi.x);
+      const float a_lo = __expf(m_lo - M_lo), b_lo = __expf(ml_lo.x - M_lo);
+      const float a_hi = __expf(m_hi - M_hi), b_hi = __expf(ml_hi.x - M_hi);
+      const float4* po = reinterpret_cast<const float4*>(part) + tid * 4;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const float4 v = __ldcg(po + nt);
+        oa[nt][0] = oa[nt][0] * a_lo + v.x * b_lo; oa[nt][1] = oa[nt][1] * a_lo + v.y * b_lo;
+        oa[nt][2] = oa[nt][2] * a_hi + v.z * b_hi; oa[nt][3] = oa[nt][3] * a_hi + v.w * b_hi;
+      }
+      tl_lo = tl_lo * a_lo + ml_lo.y * b_lo; tl_hi = tl_hi * a_hi + ml_hi.y * b_hi;
+      m_lo = M_lo; m_hi = M_hi;
+    }
+  }
   const float il_lo = 1.0f / tl_lo, il_hi = 1.0f / tl_hi;
   __nv_bfloat16* out = o.attn + (size_t)unit * 2 * QD;   // rows m = token_local * 8 + head are contiguous
 #pragma unroll
@@ -948,6 +1026,7 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
             dst[(size_t)(2 * tp + 1) * HD] = __high2bfloat16(x);
           }
         }
+        ptx::fence_proxy_async_global();   // k and v are read by attention's bulk copies
       } else if (un.gemm != G_GU) {
         // split-K partial: FP32 reduction into an L2-resident accumulator ([T][W] for O / down, [T][2560] for QKV)
         float* acc;
@@ -1003,21 +1082,32 @@ __device__ void cta_signal(const Params& p, int ev, int b) {
 
 // One layer-pass step of a row CTA for one observation.  Each returns false when a wait gave up.
 __device__ __forceinline__ bool row_attention(const Params& p, const Ctx& c, uint8_t* smem, int unit, int pass, int ob,
-                                              bool stamp0) {
+                                              int kg, AttBars& bars, bool stamp0) {
   const int layer = pass % p.n_layers, npc = (p.prefix + 63) / 64, sbase = 6 + pass * NSTAGE;
   const ObsPtrs o = obs(p, ob);
   const bool stamp = stamp0 && ob == 0;
-  AttChunkIssue issue{p, o, c, smem, layer, npc, pass};
+  // chunks 0..npc-1 are prefix keys, chunk npc the suffix keys.  With key groups the chunks are cut into contiguous
+  // shares; group 0, which merges and goes on with the residual, takes the last one (it contains the suffix chunk,
+  // the one that arrives last), group g >= 1 takes share g - 1.
+  const int KG = p.key_groups, total = npc + 1, share = kg == 0 ? KG - 1 : kg - 1;
+  const int cbeg = total * share / KG, cend = total * (share + 1) / KG;
+  AttChunkIssue issue{p, o, c, smem, bars, layer, npc, pass, cend};
   // prefix chunks do not depend on this layer's QKV: fetch them before waiting
-  const int nearly = min(npc, ATT_STAGES);
-  for (int j = 0; j < nearly; ++j) issue(j, j);
-  if (!cta_wait_event(p, c, EVB(EV_QKV, ob), (p.n_units[G_QKV] - NKVTILES) * (pass + 1), pass * NSTAGE + ST_ATT)) return false;
+  const int nearly = max(0, min(min(cend, npc) - cbeg, ATT_STAGES));
+  for (int j = 0; j < nearly; ++j) issue(cbeg + j, j);
+  if (!cta_wait_event(p, c, EVB(EV_QKV, ob), (p.n_units[G_QKV] - NKVTILES) * (pass + 1), pass * NSTAGE + ST_ATT)) {
+    att_drain(c, smem, bars, pass * NSTAGE + ST_ATT);
+    return false;
+  }
   if (stamp && sbase + ST_QKV < 64) p.stamps[sbase + ST_QKV] = globaltimer();
   build_q(o, smem, unit);                               // q straight from the FP32 sums
   const bool tr = stamp && pass == 1;
-  if (!attention_unit(p, o, smem, unit, issue, nearly, tr)) return false;
+  if (!attention_unit(p, o, smem, unit, issue, cbeg, nearly, kg, tr)) {
+    att_drain(c, smem, bars, pass * NSTAGE + ST_ATT);
+    return false;
+  }
   if (tr) p.stamps[228] = globaltimer();
-  cta_signal(p, EV_ATT, ob);
+  cta_signal(p, kg > 0 ? EV_PART : EV_ATT, ob);
   if (tr) p.stamps[229] = globaltimer();
   if (stamp && sbase + ST_ATT < 64) p.stamps[sbase + ST_ATT] = globaltimer();
   return true;
@@ -1050,13 +1140,27 @@ __device__ __forceinline__ bool row_residual(const Params& p, const Ctx& c, uint
 // gate/up(all), down(all); every wait below is for something earlier in that order than anything still queued.)
 __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, int group, float (&hn)[8]) {
   const int npass = p.n_steps * p.n_layers, G = PI05_NG(p);
+  AttBars bars;
+  if (threadIdx.x == 0) {
+    for (int j = 0; j < 2 * ATT_STAGES; ++j) ptx::mbar_init(ptx::smem_u32(smem + OFF_ATTBARS) + 8 * j, 1);
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  if (p.key_groups > 1 && group > 0) {
+    // one observation, long prefix: this group only contributes its share of the keys to every attention
+    for (int pass = 0; pass < npass; ++pass) {
+      if (pass * NSTAGE + ST_ATT >= PI05_MAXSTAGE(p)) return;
+      if (!row_attention(p, c, smem, unit, pass, 0, group, bars, false)) return;
+    }
+    return;
+  }
   const bool stamp0 = PI05_TRACE && p.stamps != nullptr && unit == 0 && group == 0 && threadIdx.x == 0;
   const int nobs = (PI05_NB(p) - group + G - 1) / G;       // observations of this group
   for (int pass = 0; pass < npass; ++pass) {
     if (pass * NSTAGE + ST_ATT >= PI05_MAXSTAGE(p)) return;
     const bool do_ratt = pass * NSTAGE + ST_RATT < PI05_MAXSTAGE(p);
     for (int k = 0; k <= nobs; ++k) {                   // attention of observation k, residual of observation k - 1
-      if (k < nobs && !row_attention(p, c, smem, unit, pass, group + k * G, stamp0)) return;
+      if (k < nobs && !row_attention(p, c, smem, unit, pass, group + k * G, 0, bars, stamp0)) return;
       if (k >= 1 && do_ratt && !row_residual(p, c, smem, unit, pass, group + (k - 1) * G, ROW_ATT, hn, stamp0)) return;
     }
     if (pass * NSTAGE + ST_RFFN >= PI05_MAXSTAGE(p)) return;

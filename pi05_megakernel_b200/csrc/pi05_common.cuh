@@ -45,8 +45,9 @@ constexpr int OFF_BARS = OFF_STAGE + STAGE_BYTES;
 
 // shared-memory layout of the row CTAs (attention + row operations).  It may overlap the prologue's scratch
 // (OFF_STAGE): the prologue is over before a row CTA touches it.
-constexpr int KV_STRIDE = HD + 8;                   // BF16 elements per K/V/Q row (528 B: conflict-free ldmatrix)
-constexpr int KV_STAGE_BYTES = 64 * KV_STRIDE * 2;  // one 64-key chunk of K or of V
+constexpr int KV_STRIDE = HD + 8;                   // BF16 elements per Q row (528 B: conflict-free ldmatrix)
+constexpr int KV_SEG_BYTES = 64 * 128;              // 64 keys x 64 dims, rows of 128 B in the TMA's 128-byte swizzle
+constexpr int KV_STAGE_BYTES = 4 * KV_SEG_BYTES;    // one 64-key chunk of K or of V: four such segments
 constexpr int ATT_STAGES = 3;                       // 192 keys resident: all of prefix 128 + the 50 suffix keys
 constexpr int P_STRIDE = ATT_STAGES * 64 + 8;
 constexpr int OFF_KS = 0;
@@ -55,6 +56,8 @@ constexpr int OFF_QS = OFF_VS + ATT_STAGES * KV_STAGE_BYTES;
 constexpr int OFF_PS = OFF_QS + 16 * KV_STRIDE * 2;
 constexpr int OFF_RED = OFF_PS + 16 * P_STRIDE * 2;          // float [8][16]
 constexpr int OFF_KVALID = OFF_RED + 8 * 16 * 4;             // uint8 [ATT_STAGES][64]
+constexpr int OFF_ATTBARS = OFF_KVALID + ATT_STAGES * 64;   // mbarriers: keys landed [ATT_STAGES], values landed [ATT_STAGES]
+static_assert(ATT_STAGES * 64 + 2 * ATT_STAGES * 8 <= 256 && OFF_ATTBARS % 8 == 0, "attention barriers");
 constexpr int OFF_ROWBUF = OFF_KVALID + 256;                 // row-op scratch: float [2][1024 + 64]
 constexpr int ATT_SMEM_END = OFF_ROWBUF + 2 * (1024 + 64) * 4;
 constexpr int SMEM_BYTES = (ATT_SMEM_END > OFF_BARS + 512 ? ATT_SMEM_END : OFF_BARS + 512) + 1024;   // + alignment slack
@@ -65,12 +68,14 @@ enum { ST_QKV = 0, ST_ATT = 1, ST_O = 2, ST_RATT = 3, ST_GU = 4, ST_DOWN = 5, ST
 enum { G_QKV = 0, G_O = 1, G_GU = 2, G_DOWN = 3 };
 
 // event counters (uint32 each) in the control block
-enum { EV_P0 = 0, EV_P1, EV_P2, EV_P3, EV_ANA, EV_QKV, EV_KV, EV_ATT, EV_O, EV_ANF, EV_GU, EV_DOWN, EV_EXIT, NEVENTS };
+enum { EV_P0 = 0, EV_P1, EV_P2, EV_P3, EV_ANA, EV_QKV, EV_KV, EV_ATT, EV_O, EV_ANF, EV_GU, EV_DOWN, EV_EXIT, EV_PART, NEVENTS };
 // every counter sits on its own 128-byte line of the control block; words 0..3 are the status
 constexpr int MAXB = 16;            // observations per launch (weights are streamed from HBM once for all of them)
 #define EVB(e, b) (32 * (1 + (e) * MAXB + (b)))   // counter of event e for observation b
 #define EVW(e) EVB(e, 0)
 constexpr int NKVTILES = 4;         // k (2) and v (2) tiles of the QKV GEMM
+constexpr int MAX_KEY_GROUPS = 3;   // row-CTA groups that may share the keys of one attention
+constexpr int ATT_PART_FLOATS = 256 * 16 + 16 * 2;   // per (group, unit): every thread's 16 accumulators, then (max, sum) per row
 constexpr int CTRL_BYTES = 128 * (1 + NEVENTS * MAXB);
 
 // wait kinds reported in the status word
@@ -84,6 +89,8 @@ constexpr long long DRAIN_CYCLES = 400000;          // exit-time grace period fo
 struct alignas(64) TMaps {
   CUtensorMap wq, wk, wv, wo, wg, wu, wd;   // weights: {K, L*rows} BF16, box {64, 64}, 128-B swizzle
   CUtensorMap an_attn, an_ffn, attn, act;   // activations: {K, 50} BF16, box {64, 50}; slot rows 50..63 are never written
+  CUtensorMap pk, pv;                       // prefix keys / values: {256, P, L * batch} BF16, box {64, 64, 1}
+  CUtensorMap sk, sv;                       // this layer's suffix keys / values: {256, 50, batch}, box {64, 64, 1}
 };
 
 // Pointers that differ from one observation of the batch to the next (b = 0 in Params; obs() advances them).
@@ -116,6 +123,8 @@ struct Params {
   long long wait_limit;
   int prefix, n_steps, n_layers, max_stage, n_gemm_ctas, batch;
   int row_groups;          // groups of NROW_CTAS row CTAs; group g serves observations g, g + row_groups, ...
+  int key_groups;          // one observation, long prefix: the groups split the keys of every attention instead
+  float* att_part;         // [MAX_KEY_GROUPS - 1][NROW_CTAS][ATT_PART_FLOATS] partial attention results of groups >= 1
   int poll_ns;             // pause between two samples of a stage counter
   int drop_event;          // debug: this event is never signalled (exercises the bounded waits); -1 = none
   int n_units[4];          // units per GEMM kind (event targets)

@@ -75,6 +75,7 @@ struct pi05_engine {
   int max_batch = 1;
   int batch = 1;
   int row_groups = 1;
+  int key_groups = 1;
   bool bound = false;
   const void* inputs[PI05_NUM_INPUTS] = {};
   void* actions = nullptr;
@@ -154,6 +155,7 @@ void build_layout(pi05_engine* h) {
   add("o_acc", B * T * W * 4);
   add("d_acc", B * T * W * 4);
   add("act", B * T * FF * 2);
+  add("att_part", (size_t)(MAX_KEY_GROUPS - 1) * NROW_CTAS * ATT_PART_FLOATS * 4);
   add("sched", (size_t)h->grid * MAX_UNITS * sizeof(Unit));
   add("sched_n", (size_t)h->grid * sizeof(int));
   h->ws_bytes = off;
@@ -220,6 +222,24 @@ int encode_2d(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t inner, 
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     h->last_error = "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r);
+    return PI05_ERR_CUDA;
+  }
+  return PI05_OK;
+}
+
+// K / V of attention: {256, rows, planes} BF16, box {64, 64, 1}; rows past the end of a plane read as zeros.
+int encode_kv(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t rows, uint64_t planes) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) { h->last_error = "cuTensorMapEncodeTiled is not available from this driver"; return PI05_ERR_CUDA; }
+  cuuint64_t dims[3] = {(cuuint64_t)HD, rows, planes};
+  cuuint64_t strides[2] = {(cuuint64_t)HD * 2, rows * HD * 2};
+  cuuint32_t box[3] = {KATOM, 64, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    h->last_error = "cuTensorMapEncodeTiled (attention K/V) failed with code " + std::to_string((int)r);
     return PI05_ERR_CUDA;
   }
   return PI05_OK;
@@ -332,9 +352,13 @@ int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int pr
   {
     // More observations keep more row CTAs busy: one group of 25 per observation in flight, as long as the GEMM
     // side keeps its 64 gate/up CTAs plus the 4 k / v CTAs.
-    int groups = batch >= 8 ? 3 : batch >= 2 ? 2 : 1;
+    // One observation with a long prefix uses the extra groups differently: they split the keys of each attention.
+    const int chunks = (prefix_len + 63) / 64 + 1;
+    int groups = batch >= 8 ? 3 : batch >= 2 ? 2 : (chunks >= 7 ? 3 : chunks >= 5 ? 2 : 1);
+    if (const char* kg = getenv("PI05_KEY_GROUPS")) { if (batch == 1) groups = std::max(1, std::min(atoi(kg), (int)MAX_KEY_GROUPS)); }   // tuning knob
     while (groups > 1 && h->grid - groups * NROW_CTAS < 64 + NKVTILES) --groups;
-    h->row_groups = groups;
+    h->row_groups = batch > 1 ? groups : 1;
+    h->key_groups = batch > 1 ? 1 : groups;
     h->n_gemm = h->grid - groups * NROW_CTAS;
     if (!build_schedule(h)) { h->last_error = "no schedule for this GPU"; return PI05_ERR_UNSUPPORTED; }
   }
@@ -356,6 +380,10 @@ int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int pr
   if ((rc = encode_2d(h, &h->maps.an_ffn, region_ptr<void>(h, "an_ffn"), W, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
   if ((rc = encode_2d(h, &h->maps.attn, region_ptr<void>(h, "attn"), QD, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
   if ((rc = encode_2d(h, &h->maps.act, region_ptr<void>(h, "act"), FF, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
+  if ((rc = encode_kv(h, &h->maps.pk, inputs[22], (uint64_t)prefix_len, (uint64_t)NL * batch))) return rc;
+  if ((rc = encode_kv(h, &h->maps.pv, inputs[23], (uint64_t)prefix_len, (uint64_t)NL * batch))) return rc;
+  if ((rc = encode_kv(h, &h->maps.sk, region_ptr<void>(h, "k"), (uint64_t)T, (uint64_t)batch))) return rc;
+  if ((rc = encode_kv(h, &h->maps.sv, region_ptr<void>(h, "v"), (uint64_t)T, (uint64_t)batch))) return rc;
   e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceSynchronize", e);
   h->bound = true;
@@ -418,6 +446,8 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.prefix = h->prefix; p.n_steps = n_steps; p.n_layers = n_layers; p.max_stage = h->max_stage;
   p.n_gemm_ctas = h->n_gemm;
   p.row_groups = h->row_groups;
+  p.key_groups = h->key_groups;
+  p.att_part = region_ptr<float>(h, "att_part");
   p.drop_event = h->drop_event;
   p.poll_ns = h->poll_ns;
   for (int g = 0; g < 4; ++g) p.n_units[g] = h->n_units[g];
