@@ -592,20 +592,17 @@ struct AttChunkIssue {
 };
 
 // S = Q K^T for this warp's 8 keys of one stage (two interleaved accumulation chains).
-__device__ __forceinline__ void att_qk(uint32_t qs, uint32_t ks, int warp, int lane, float (&s4)[4]) {
+__device__ __forceinline__ void att_qk(const uint32_t (&qf)[HD / 16][4], uint32_t ks, int warp, int lane, float (&s4)[4]) {
   float e[4] = {0.f, 0.f, 0.f, 0.f}, o[4] = {0.f, 0.f, 0.f, 0.f};
-  const uint32_t qaddr0 = qs + ((lane & 15) * KV_STRIDE + (lane >> 4) * 8) * 2;
   // key row r = warp * 8 + (lane & 7); 16-byte piece c of the row sits at piece c ^ (r & 7) of its 128-byte line
   const uint32_t krow = ks + (warp * 8 + (lane & 7)) * 128;
   const uint32_t ksw = lane & 7, kc = lane >> 3;
 #pragma unroll
   for (int kk = 0; kk < HD / 16; kk += 2) {
-    uint32_t a0, a1, a2, a3, a4, a5, a6, a7, b0, b1, b2, b3;
-    ptx::ldmatrix_x4(qaddr0 + kk * 32, a0, a1, a2, a3);
-    ptx::ldmatrix_x4(qaddr0 + kk * 32 + 32, a4, a5, a6, a7);
+    uint32_t b0, b1, b2, b3;
     ptx::ldmatrix_x4(krow + (kk >> 2) * KV_SEG_BYTES + ((((kk & 3) * 2 + kc) ^ ksw) << 4), b0, b1, b2, b3);
-    ptx::mma_16816(e, a0, a1, a2, a3, b0, b1);
-    ptx::mma_16816(o, a4, a5, a6, a7, b2, b3);
+    ptx::mma_16816(e, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+    ptx::mma_16816(o, qf[kk + 1][0], qf[kk + 1][1], qf[kk + 1][2], qf[kk + 1][3], b2, b3);
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) s4[i] = e[i] + o[i];
@@ -628,6 +625,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
   const float NEG = -INFINITY;
 
   float m_lo = -1e30f, m_hi = -1e30f, l_lo = 0.f, l_hi = 0.f;
+  uint32_t qf[HD / 16][4];
   float oa[4][4];
 #pragma unroll
   for (int a = 0; a < 4; ++a)
@@ -641,12 +639,18 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
     const int early = (c0 == cbeg) ? nearly : nst;
     const bool more = c0 + ATT_STAGES < cend;
     __syncthreads();                                   // q is in place (first round)
+    if (c0 == cbeg) {
+      // the whole 16 x 256 q tile as A fragments, kept in registers for every stage of every round
+      const uint32_t qaddr0 = qs + ((lane & 15) * KV_STRIDE + (lane >> 4) * 8) * 2;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) ptx::ldmatrix_x4(qaddr0 + kk * 32, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+    }
     if (tr && c0 == cbeg) p.stamps[224] = globaltimer();
 #pragma unroll
     for (int j = 0; j < ATT_STAGES; ++j)
       if (j < early) {
         if (!att_wait(issue.c, smem, bars, 0, j, wst)) return false;
-        att_qk(qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
+        att_qk(qf, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
       }
     if (early < nst) {
       if (!issue(c0 + early, early)) return false;     // waits for the k / v tiles, then copies the suffix chunk
@@ -654,7 +658,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
       for (int j = 0; j < ATT_STAGES; ++j)
         if (j >= early && j < nst) {
           if (!att_wait(issue.c, smem, bars, 0, j, wst)) return false;
-          att_qk(qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
+          att_qk(qf, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
         }
     }
     if (tr && c0 == cbeg) p.stamps[225] = globaltimer();
