@@ -556,8 +556,8 @@ struct AttChunkIssue {
   // chunk < npc: prefix keys [64*chunk, ...); chunk == npc: the 50 suffix keys; chunk >= cend (the end of this CTA's
   // share of the keys) or > npc: nothing (stage off)
   // `which`: 1 = keys only, 2 = values (and the validity bytes, which the previous occupant's softmax has read by
-  // then) only, 3 = both.  One thread issues four tiled copies (64 dims each) per chunk of keys or of values; they
-  // complete on the stage's barriers, and rows past the end of a short chunk arrive as zeros.
+  // then) only, 3 = both.  One thread issues one tiled copy per chunk of keys or of values (four 64-dim segments); it
+  // completes on the stage's barrier, and rows past the end of a short chunk arrive as zeros.
   // Collective over the CTA.  Returns false when the wait for the suffix keys gave up.
   __device__ bool operator()(int chunk, int stage, int which = 3) const {
     const int tid = threadIdx.x;
@@ -582,8 +582,7 @@ struct AttChunkIssue {
         const int row = is_prefix ? chunk * 64 : 0, plane = is_prefix ? o.b * NL + layer : o.b;
         if (!is_prefix) ptx::fence_proxy_async_global();   // the suffix rows were written by GEMM epilogues
         ptx::mbar_expect_tx(bar, KV_STAGE_BYTES);
-#pragma unroll
-        for (int sg = 0; sg < 4; ++sg) ptx::tma_load_3d(dst + sg * KV_SEG_BYTES, m, bar, sg * 64, row, plane);
+        ptx::tma_load_4d(dst, m, bar, 0, row, 0, plane);
       }
       bars.pending |= 1u << (8 * isv + stage);
     }
@@ -646,6 +645,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
       for (int kk = 0; kk < HD / 16; ++kk) ptx::ldmatrix_x4(qaddr0 + kk * 32, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
     }
     if (tr && c0 == cbeg) p.stamps[224] = globaltimer();
+    if (tr && c0 != cbeg && !more) p.stamps[232] = globaltimer();
 #pragma unroll
     for (int j = 0; j < ATT_STAGES; ++j)
       if (j < early) {
@@ -662,6 +662,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
         }
     }
     if (tr && c0 == cbeg) p.stamps[225] = globaltimer();
+    if (tr && c0 != cbeg && !more) p.stamps[233] = globaltimer();
     // ---- mask, chunk max
     float cm_lo = NEG, cm_hi = NEG;
 #pragma unroll
@@ -711,6 +712,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
     }
     __syncthreads();
     if (tr && c0 == cbeg) p.stamps[226] = globaltimer();
+    if (tr && c0 != cbeg && !more) p.stamps[234] = globaltimer();
     // ---- O += P V for this warp's 32 output dims
 #pragma unroll
     for (int j = 0; j < ATT_STAGES; ++j) {
@@ -734,6 +736,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
       }
     }
     if (tr && c0 == cbeg) p.stamps[227] = globaltimer();
+    if (tr && c0 != cbeg && !more) p.stamps[235] = globaltimer();
     if (more) {
       __syncthreads();   // every warp is done with P and these value stages
       for (int j = 0; j < ATT_STAGES; ++j)
@@ -749,6 +752,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
   float tl_lo = 0.f, tl_hi = 0.f;
 #pragma unroll
   for (int w8 = 0; w8 < 8; ++w8) { tl_lo += red[w8 * 16 + g]; tl_hi += red[w8 * 16 + g + 8]; }
+  if (tr) p.stamps[236] = globaltimer();
   if (kg > 0) {
     // partial result of key group kg: this thread's 16 accumulators, then (max, sum) of every row
     float* part = p.att_part + ((size_t)(kg - 1) * NROW_CTAS + unit) * ATT_PART_FLOATS;
@@ -763,26 +767,41 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
   }
   if (p.key_groups > 1) {
     // merge the other groups' partial results (they cover disjoint keys): rescale everything to the common maximum
-    if (!cta_wait_event(p, issue.c, EVB(EV_PART, o.b), NROW_CTAS * (p.key_groups - 1) * (issue.pass + 1),
+    if (!cta_wait_event(p, issue.c, EVB(EV_PART + (unit >> 4), unit & 15), (p.key_groups - 1) * (issue.pass + 1),
                         issue.pass * NSTAGE + ST_ATT)) return false;
-    for (int og = 1; og < p.key_groups; ++og) {
-      const float* part = p.att_part + ((size_t)(og - 1) * NROW_CTAS + unit) * ATT_PART_FLOATS;
-      const float2 ml_lo = __ldcg(reinterpret_cast<const float2*>(part + 256 * 16) + g);
-      const float2 ml_hi = __ldcg(reinterpret_cast<const float2*>(part + 256 * 16) + g + 8);
-      const float M_lo = fmaxf(m_lo, ml_lo.x), M_hi = fmaxf(m_hi, ml_hi.x);
-      const float a_lo = __expf(m_lo - M_lo), b_lo = __expf(ml_lo.x - M_lo);
-      const float a_hi = __expf(m_hi - M_hi), b_hi = __expf(ml_hi.x - M_hi);
-      const float4* po = reinterpret_cast<const float4*>(part) + tid * 4;
+    if (tr) p.stamps[237] = globaltimer();
+    // all loads first, then the arithmetic
+    float2 ml[MAX_KEY_GROUPS - 1][2];
+    float4 pv[MAX_KEY_GROUPS - 1][4];
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const float4 v = __ldcg(po + nt);
-        oa[nt][0] = oa[nt][0] * a_lo + v.x * b_lo; oa[nt][1] = oa[nt][1] * a_lo + v.y * b_lo;
-        oa[nt][2] = oa[nt][2] * a_hi + v.z * b_hi; oa[nt][3] = oa[nt][3] * a_hi + v.w * b_hi;
+    for (int og = 1; og < MAX_KEY_GROUPS; ++og) {
+      if (og < p.key_groups) {
+        const float* part = p.att_part + ((size_t)(og - 1) * NROW_CTAS + unit) * ATT_PART_FLOATS;
+        ml[og - 1][0] = __ldcg(reinterpret_cast<const float2*>(part + 256 * 16) + g);
+        ml[og - 1][1] = __ldcg(reinterpret_cast<const float2*>(part + 256 * 16) + g + 8);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) pv[og - 1][nt] = __ldcg(reinterpret_cast<const float4*>(part) + tid * 4 + nt);
       }
-      tl_lo = tl_lo * a_lo + ml_lo.y * b_lo; tl_hi = tl_hi * a_hi + ml_hi.y * b_hi;
-      m_lo = M_lo; m_hi = M_hi;
+    }
+#pragma unroll
+    for (int og = 1; og < MAX_KEY_GROUPS; ++og) {
+      if (og < p.key_groups) {
+        const float2 ml_lo = ml[og - 1][0], ml_hi = ml[og - 1][1];
+        const float M_lo = fmaxf(m_lo, ml_lo.x), M_hi = fmaxf(m_hi, ml_hi.x);
+        const float a_lo = __expf(m_lo - M_lo), b_lo = __expf(ml_lo.x - M_lo);
+        const float a_hi = __expf(m_hi - M_hi), b_hi = __expf(ml_hi.x - M_hi);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const float4 v = pv[og - 1][nt];
+          oa[nt][0] = oa[nt][0] * a_lo + v.x * b_lo; oa[nt][1] = oa[nt][1] * a_lo + v.y * b_lo;
+          oa[nt][2] = oa[nt][2] * a_hi + v.z * b_hi; oa[nt][3] = oa[nt][3] * a_hi + v.w * b_hi;
+        }
+        tl_lo = tl_lo * a_lo + ml_lo.y * b_lo; tl_hi = tl_hi * a_hi + ml_hi.y * b_hi;
+        m_lo = M_lo; m_hi = M_hi;
+      }
     }
   }
+  if (tr) p.stamps[238] = globaltimer();
   const float il_lo = 1.0f / tl_lo, il_hi = 1.0f / tl_hi;
   __nv_bfloat16* out = o.attn + (size_t)unit * 2 * QD;   // rows m = token_local * 8 + head are contiguous
 #pragma unroll
@@ -1111,7 +1130,12 @@ __device__ __forceinline__ bool row_attention(const Params& p, const Ctx& c, uin
     return false;
   }
   if (tr) p.stamps[228] = globaltimer();
-  cta_signal(p, kg > 0 ? EV_PART : EV_ATT, ob);
+  if (kg > 0) {
+    __syncthreads();
+    if (threadIdx.x == 0) signal_event(p.ctrl + EVB(EV_PART + (unit >> 4), unit & 15));
+  } else {
+    cta_signal(p, EV_ATT, ob);
+  }
   if (tr) p.stamps[229] = globaltimer();
   if (stamp && sbase + ST_ATT < 64) p.stamps[sbase + ST_ATT] = globaltimer();
   return true;

@@ -68,12 +68,14 @@ enum { ST_QKV = 0, ST_ATT = 1, ST_O = 2, ST_RATT = 3, ST_GU = 4, ST_DOWN = 5, ST
 enum { G_QKV = 0, G_O = 1, G_GU = 2, G_DOWN = 3 };
 
 // event counters (uint32 each) in the control block
-enum { EV_P0 = 0, EV_P1, EV_P2, EV_P3, EV_ANA, EV_QKV, EV_KV, EV_ATT, EV_O, EV_ANF, EV_GU, EV_DOWN, EV_EXIT, EV_PART, NEVENTS };
+enum { EV_P0 = 0, EV_P1, EV_P2, EV_P3, EV_ANA, EV_QKV, EV_KV, EV_ATT, EV_O, EV_ANF, EV_GU, EV_DOWN, EV_EXIT, EV_PART, EV_PART2, NEVENTS };
+// EV_PART / EV_PART2 (key groups, one observation): slot u of the 2 * MAXB slots counts the partial results of row unit u
 // every counter sits on its own 128-byte line of the control block; words 0..3 are the status
 constexpr int MAXB = 16;            // observations per launch (weights are streamed from HBM once for all of them)
 #define EVB(e, b) (32 * (1 + (e) * MAXB + (b)))   // counter of event e for observation b
 #define EVW(e) EVB(e, 0)
 constexpr int NKVTILES = 4;         // k (2) and v (2) tiles of the QKV GEMM
+static_assert(NROW_CTAS <= 2 * MAXB, "EV_PART / EV_PART2 slots");
 constexpr int MAX_KEY_GROUPS = 3;   // row-CTA groups that may share the keys of one attention
 constexpr int ATT_PART_FLOATS = 256 * 16 + 16 * 2;   // per (group, unit): every thread's 16 accumulators, then (max, sum) per row
 constexpr int CTRL_BYTES = 128 * (1 + NEVENTS * MAXB);
@@ -89,8 +91,8 @@ constexpr long long DRAIN_CYCLES = 400000;          // exit-time grace period fo
 struct alignas(64) TMaps {
   CUtensorMap wq, wk, wv, wo, wg, wu, wd;   // weights: {K, L*rows} BF16, box {64, 64}, 128-B swizzle
   CUtensorMap an_attn, an_ffn, attn, act;   // activations: {K, 50} BF16, box {64, 50}; slot rows 50..63 are never written
-  CUtensorMap pk, pv;                       // prefix keys / values: {256, P, L * batch} BF16, box {64, 64, 1}
-  CUtensorMap sk, sv;                       // this layer's suffix keys / values: {256, 50, batch}, box {64, 64, 1}
+  CUtensorMap pk, pv;                       // prefix keys / values: {64, P, 4, L * batch} BF16, box {64, 64, 4, 1}
+  CUtensorMap sk, sv;                       // this layer's suffix keys / values: {64, 50, 4, batch}, same box
 };
 
 // Pointers that differ from one observation of the batch to the next (b = 0 in Params; obs() advances them).

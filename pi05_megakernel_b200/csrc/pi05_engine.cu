@@ -227,15 +227,17 @@ int encode_2d(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t inner, 
   return PI05_OK;
 }
 
-// K / V of attention: {256, rows, planes} BF16, box {64, 64, 1}; rows past the end of a plane read as zeros.
+// K / V of attention, [planes][rows][256] BF16 in memory, described as {64, rows, 4, planes}: the 256 dims of a row are
+// four 64-dim segments, and the segment index is an outer dimension, so that one copy of a box {64, 64, 4, 1} lands
+// as four segment blocks of 64 rows x 128 B (128-byte swizzle each).  Rows past the end of a plane read as zeros.
 int encode_kv(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t rows, uint64_t planes) {
   EncodeTiledFn enc = get_encode();
   if (!enc) { h->last_error = "cuTensorMapEncodeTiled is not available from this driver"; return PI05_ERR_CUDA; }
-  cuuint64_t dims[3] = {(cuuint64_t)HD, rows, planes};
-  cuuint64_t strides[2] = {(cuuint64_t)HD * 2, rows * HD * 2};
-  cuuint32_t box[3] = {KATOM, 64, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+  cuuint64_t dims[4] = {(cuuint64_t)KATOM, rows, (cuuint64_t)(HD / KATOM), planes};
+  cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)KATOM * 2, rows * HD * 2};
+  cuuint32_t box[4] = {KATOM, 64, HD / KATOM, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -354,7 +356,7 @@ int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int pr
     // side keeps its 64 gate/up CTAs plus the 4 k / v CTAs.
     // One observation with a long prefix uses the extra groups differently: they split the keys of each attention.
     const int chunks = (prefix_len + 63) / 64 + 1;
-    int groups = batch >= 8 ? 3 : batch >= 2 ? 2 : (chunks >= 7 ? 3 : chunks >= 5 ? 2 : 1);
+    int groups = batch >= 8 ? 3 : batch >= 2 ? 2 : (chunks >= 8 ? 3 : chunks >= 6 ? 2 : 1);
     if (const char* kg = getenv("PI05_KEY_GROUPS")) { if (batch == 1) groups = std::max(1, std::min(atoi(kg), (int)MAX_KEY_GROUPS)); }   // tuning knob
     while (groups > 1 && h->grid - groups * NROW_CTAS < 64 + NKVTILES) --groups;
     h->row_groups = batch > 1 ? groups : 1;
