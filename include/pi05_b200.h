@@ -67,6 +67,34 @@ int pi05_workspace_bytes(pi05_handle_t h, size_t* bytes);
 int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, int batch,
               void* actions, void* workspace, size_t workspace_bytes);
 
+/* The prefix cache where its producer left it (the hand-off after `prefill`, reference/pi05.py:167-195, whose keys
+ * and values the reference passes on as dense [18,P,1,256] tensors): a pool of pages with arbitrary strides, and per
+ * observation a list of the pages that hold its tokens in order.  Nothing is copied or repacked; the attention's
+ * tiled copies read the pool through these strides.
+ *   token t of observation b, layer l, lives at
+ *     k + (page_table[b * pages_per_obs + t / page_tokens] * page_stride + l * layer_stride
+ *          + (t % page_tokens) * token_stride) elements, 256 contiguous BF16 from there (v likewise).
+ * Requirements: k and v 16-byte aligned; the three strides multiples of 8 elements; page_tokens a multiple of 64
+ * unless pages_per_obs is 1 (one page per observation: any length >= prefix_len, e.g. a cache allocated for the
+ * longest prompt and filled up to prefix_len); prefix_len <= pages_per_obs * page_tokens; every page_table entry in
+ * [0, num_pages).  page_table is a host array and is copied at bind time.  Tokens at and beyond prefix_len are never
+ * read as values: whatever the cache holds there cannot reach the result. */
+typedef struct pi05_kv_view {
+  const void* k;
+  const void* v;
+  long long token_stride, layer_stride, page_stride;   /* in BF16 elements */
+  int page_tokens;
+  int num_pages;
+  int pages_per_obs;
+  const int* page_table;
+} pi05_kv_view;
+
+/* pi05_bind with the prefix cache given as a view: inputs[22] and inputs[23] are ignored (may be NULL), everything
+ * else is as in pi05_bind (inputs[24], the validity mask, stays [batch][prefix_len]).  pi05_bind itself is this call
+ * with the dense view (one page per observation, token stride 256, layer stride prefix_len * 256). */
+int pi05_bind_view(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], const pi05_kv_view* kv, int prefix_len,
+                   int batch, void* actions, void* workspace, size_t workspace_bytes);
+
 /* Counterpart of the harness's optional refresh_weights() (bench.py:209-216).  The engine reads the caller's
  * tensors in place and keeps no repacked copies, so this only re-validates the binding. */
 int pi05_refresh(pi05_handle_t h);

@@ -9,7 +9,7 @@ from .fixture import ORDER, SEEDS, Geometry, make_batch, make_inputs, sol  # noq
 
 
 def __getattr__(name):
-    if name == "Pi05Arm":
-        from .arm import Pi05Arm
-        return Pi05Arm
+    if name in ("Pi05Arm", "PagedPrefix"):
+        from . import arm
+        return getattr(arm, name)
     raise AttributeError(name)

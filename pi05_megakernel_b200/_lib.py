@@ -21,11 +21,23 @@ WAIT_EVENT = 7
 OK, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_NOT_BOUND, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE = range(7)
 
 _c = ctypes
+
+
+class KvView(ctypes.Structure):
+    """``pi05_kv_view`` of the header: the prefix cache as a pool of pages with strides (in BF16 elements)."""
+    _fields_ = [("k", _c.c_void_p), ("v", _c.c_void_p),
+                ("token_stride", _c.c_longlong), ("layer_stride", _c.c_longlong), ("page_stride", _c.c_longlong),
+                ("page_tokens", _c.c_int), ("num_pages", _c.c_int), ("pages_per_obs", _c.c_int),
+                ("page_table", _c.POINTER(_c.c_int))]
+
+
 SIGNATURES = {
     "pi05_create": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_void_p)]),
     "pi05_workspace_bytes": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_size_t)]),
     "pi05_bind": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_void_p), _c.c_int, _c.c_int, _c.c_void_p,
                              _c.c_void_p, _c.c_size_t]),
+    "pi05_bind_view": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_void_p), _c.POINTER(KvView), _c.c_int, _c.c_int,
+                                  _c.c_void_p, _c.c_void_p, _c.c_size_t]),
     "pi05_refresh": (_c.c_int, [_c.c_void_p]),
     "pi05_launch": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
     "pi05_status": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),

@@ -38,6 +38,39 @@ def parse_variant(variant: str) -> dict:
     return out
 
 
+class PagedPrefix:
+    """The prefix cache in the layout of whoever produced it.
+
+    ``k`` and ``v`` are BF16 CUDA tensors ``[pages, layers, page_tokens, kv_heads(1), 256]`` with any strides whose
+    last dimension is contiguous (a slice of a larger cache, a pool with padding between tokens, ...); ``table`` is an
+    integer array ``[batch][pages_per_observation]`` (list or CPU tensor) naming, in order, the pages that hold each
+    observation's tokens.  With more than one page per observation ``page_tokens`` must be a multiple of 64.
+    """
+
+    def __init__(self, k: torch.Tensor, v: torch.Tensor, table) -> None:
+        if k.dim() != 5 or k.shape != v.shape or k.shape[3] != 1 or k.shape[4] != 256:
+            raise ValueError("k and v must be [pages, layers, page_tokens, 1, 256]")
+        if k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+            raise ValueError("k and v must be bfloat16")
+        if k.stride() != v.stride() or k.stride(4) != 1:
+            raise ValueError("k and v must share their strides and have a contiguous last dimension")
+        self.k, self.v = k, v
+        self.table = [[int(x) for x in row] for row in (table.tolist() if hasattr(table, "tolist") else table)]
+
+    def as_view(self, arm: "Pi05Arm"):
+        if self.k.device != arm.device or self.v.device != arm.device:
+            raise ValueError(f"the prefix cache must live on {arm.device}")
+        if len(self.table) != arm.batch or len({len(r) for r in self.table}) != 1:
+            raise ValueError("the page table needs one row of equal length per observation")
+        if self.k.shape[1] != arm.geo.layers:
+            raise ValueError("wrong number of layers in the prefix cache")
+        flat = [x for row in self.table for x in row]
+        table = (ctypes.c_int * len(flat))(*flat)
+        view = _lib.KvView(self.k.data_ptr(), self.v.data_ptr(), self.k.stride(2), self.k.stride(1), self.k.stride(0),
+                           self.k.shape[2], self.k.shape[0], len(self.table[0]), table)
+        return view, table
+
+
 class Pi05Arm:
     name = "b200-megakernel"
 
@@ -74,10 +107,16 @@ class Pi05Arm:
         self.config.update(prefix=geo.prefix, steps=self.steps, layers=self.layers, batch=batch)
 
     # ------------------------------------------------------------------ arm protocol
-    def bind(self, inputs: dict) -> None:
+    def bind(self, inputs: dict, kv_pages: "PagedPrefix | None" = None) -> None:
+        """Record the 25 tensors (kept by pointer, read in place).  With ``kv_pages`` the prefix keys / values are read
+        where their producer left them (a strided or paged pool, see ``PagedPrefix``) and ``inputs["prefix_k"]`` /
+        ``inputs["prefix_v"]`` are not needed."""
         want = shapes(self.geo)
         tensors = []
         for name in ORDER:
+            if kv_pages is not None and name in ("prefix_k", "prefix_v"):
+                tensors.append(None)
+                continue
             value = inputs[name]
             shape, dtype = want[name]
             if self.batch > 1 and name in OBSERVATION:
@@ -89,10 +128,18 @@ class Pi05Arm:
             if value.device != self.device:
                 raise ValueError(f"{name} must live on {self.device}")
             tensors.append(value)
-        ptrs = (ctypes.c_void_p * _lib.NUM_INPUTS)(*[t.data_ptr() for t in tensors])
-        _lib.check(self.lib, self.handle, self.lib.pi05_bind(
-            self.handle, ptrs, self.geo.prefix, self.batch, self.actions.data_ptr(), self.ws.data_ptr(),
-            self.ws.numel()))
+        ptrs = (ctypes.c_void_p * _lib.NUM_INPUTS)(*[None if t is None else t.data_ptr() for t in tensors])
+        if kv_pages is None:
+            _lib.check(self.lib, self.handle, self.lib.pi05_bind(
+                self.handle, ptrs, self.geo.prefix, self.batch, self.actions.data_ptr(), self.ws.data_ptr(),
+                self.ws.numel()))
+        else:
+            view, keep = kv_pages.as_view(self)
+            _lib.check(self.lib, self.handle, self.lib.pi05_bind_view(
+                self.handle, ptrs, ctypes.byref(view), self.geo.prefix, self.batch, self.actions.data_ptr(),
+                self.ws.data_ptr(), self.ws.numel()))
+            tensors += [kv_pages.k, kv_pages.v]
+            del keep
         self.tensors = tensors
 
     def refresh_weights(self) -> None:

@@ -25,9 +25,8 @@ __device__ __constant__ int kGemmStage[4] = {ST_QKV, ST_O, ST_GU, ST_DOWN};
 __device__ __forceinline__ ObsPtrs obs(const Params& p, int b) {
   ObsPtrs o = p.ob;
   if (!PI05_BATCHED) return o;
-  const size_t kv = (size_t)NL * p.prefix * HD;
   o.noise += (size_t)b * T * ADIM; o.actions += (size_t)b * T * ADIM; o.x += (size_t)b * T * ADIM;
-  o.prefix_k += b * kv; o.prefix_v += b * kv; o.prefix_mask += (size_t)b * p.prefix;
+  o.prefix_mask += (size_t)b * p.prefix;
   o.o_acc += (size_t)b * T * W; o.d_acc += (size_t)b * T * W; o.qkv_acc += (size_t)b * T * QKVW;
   o.rope += (size_t)b * T * (HD / 2); o.rope2 += (size_t)b * T * (HD / 2);
   o.h += (size_t)b * T * W; o.an_attn += (size_t)b * T * W; o.an_ffn += (size_t)b * T * W;
@@ -578,11 +577,19 @@ struct AttChunkIssue {
       if (tid == 0) {
         const uint32_t dst = ptx::smem_u32(smem + (isv ? OFF_VS : OFF_KS) + stage * KV_STAGE_BYTES);
         const uint32_t bar = att_bar(smem, isv, stage);
-        const CUtensorMap* m = is_prefix ? (isv ? &p.maps.pv : &p.maps.pk) : (isv ? &p.maps.sv : &p.maps.sk);
-        const int row = is_prefix ? chunk * 64 : 0, plane = is_prefix ? o.b * NL + layer : o.b;
-        if (!is_prefix) ptx::fence_proxy_async_global();   // the suffix rows were written by GEMM epilogues
         ptx::mbar_expect_tx(bar, KV_STAGE_BYTES);
-        ptx::tma_load_4d(dst, m, bar, 0, row, 0, plane);
+        if (is_prefix) {
+          // logical page of the chunk -> physical page of the pool; the last page goes through the map whose rows
+          // end at the last valid token, so that whatever lies behind it in the cache arrives as zeros
+          const int lp = p.pages_per_obs == 1 ? 0 : chunk * 64 / p.page_tokens, row = chunk * 64 - lp * p.page_tokens;
+          const int phys = reinterpret_cast<const int*>(smem + OFF_PAGETAB)[o.b * p.pages_per_obs + lp];
+          const bool tail = lp == (p.prefix - 1) / p.page_tokens;
+          const CUtensorMap* m = tail ? (isv ? &p.maps.pv_tail : &p.maps.pk_tail) : (isv ? &p.maps.pv : &p.maps.pk);
+          ptx::tma_load_5d(dst, m, bar, 0, row, 0, layer, phys);
+        } else {
+          ptx::fence_proxy_async_global();   // the suffix rows were written by GEMM epilogues
+          ptx::tma_load_4d(dst, isv ? &p.maps.sv : &p.maps.sk, bar, 0, 0, 0, o.b);
+        }
       }
       bars.pending |= 1u << (8 * isv + stage);
     }
@@ -1169,6 +1176,8 @@ __device__ __forceinline__ bool row_residual(const Params& p, const Ctx& c, uint
 __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, int group, float (&hn)[8]) {
   const int npass = p.n_steps * p.n_layers, G = PI05_NG(p);
   AttBars bars;
+  for (int i = threadIdx.x; i < PI05_NB(p) * p.pages_per_obs; i += THREADS)   // the page table, kept in shared memory
+    reinterpret_cast<int*>(smem + OFF_PAGETAB)[i] = p.page_table[i];
   if (threadIdx.x == 0) {
     for (int j = 0; j < 2 * ATT_STAGES; ++j) ptx::mbar_init(ptx::smem_u32(smem + OFF_ATTBARS) + 8 * j, 1);
     ptx::fence_mbar_init();

@@ -59,7 +59,9 @@ constexpr int OFF_KVALID = OFF_RED + 8 * 16 * 4;             // uint8 [ATT_STAGE
 constexpr int OFF_ATTBARS = OFF_KVALID + ATT_STAGES * 64;   // mbarriers: keys landed [ATT_STAGES], values landed [ATT_STAGES]
 static_assert(ATT_STAGES * 64 + 2 * ATT_STAGES * 8 <= 256 && OFF_ATTBARS % 8 == 0, "attention barriers");
 constexpr int OFF_ROWBUF = OFF_KVALID + 256;                 // row-op scratch: float [2][1024 + 64]
-constexpr int ATT_SMEM_END = OFF_ROWBUF + 2 * (1024 + 64) * 4;
+constexpr int OFF_PAGETAB = OFF_ROWBUF + 2 * (1024 + 64) * 4;   // int [MAX_PAGE_ENTRIES]: the page table of the prefix cache
+constexpr int MAX_PAGE_ENTRIES = 1024;                        // batch x pages per observation
+constexpr int ATT_SMEM_END = OFF_PAGETAB + MAX_PAGE_ENTRIES * 4;
 constexpr int SMEM_BYTES = (ATT_SMEM_END > OFF_BARS + 512 ? ATT_SMEM_END : OFF_BARS + 512) + 1024;   // + alignment slack
 static_assert(SMEM_BYTES <= 232448 - 256, "over the 227 KB per-CTA limit");
 
@@ -91,14 +93,14 @@ constexpr long long DRAIN_CYCLES = 400000;          // exit-time grace period fo
 struct alignas(64) TMaps {
   CUtensorMap wq, wk, wv, wo, wg, wu, wd;   // weights: {K, L*rows} BF16, box {64, 64}, 128-B swizzle
   CUtensorMap an_attn, an_ffn, attn, act;   // activations: {K, 50} BF16, box {64, 50}; slot rows 50..63 are never written
-  CUtensorMap pk, pv;                       // prefix keys / values: {64, P, 4, L * batch} BF16, box {64, 64, 4, 1}
+  CUtensorMap pk, pv;                       // prefix keys / values, full pages: {64, page tokens, 4, L, pages} BF16, box {64, 64, 4, 1, 1}
+  CUtensorMap pk_tail, pv_tail;             // the same pool, rows limited to the valid tokens of an observation's last page
   CUtensorMap sk, sv;                       // this layer's suffix keys / values: {64, 50, 4, batch}, same box
 };
 
 // Pointers that differ from one observation of the batch to the next (b = 0 in Params; obs() advances them).
 struct ObsPtrs {
   const float* noise;                       // [T][32]
-  const __nv_bfloat16 *prefix_k, *prefix_v; // [L][P][256]
   const uint8_t* prefix_mask;               // [P]
   float* actions;                           // [T][32]
   float *x, *o_acc, *d_acc;                 // [T][32], [T][W], [T][W]
@@ -126,6 +128,8 @@ struct Params {
   int prefix, n_steps, n_layers, max_stage, n_gemm_ctas, batch;
   int row_groups;          // groups of NROW_CTAS row CTAs; group g serves observations g, g + row_groups, ...
   int key_groups;          // one observation, long prefix: the groups split the keys of every attention instead
+  const int* page_table;   // [batch][pages_per_obs] physical page of every logical page of the prefix cache
+  int pages_per_obs, page_tokens;
   float* att_part;         // [MAX_KEY_GROUPS - 1][NROW_CTAS][ATT_PART_FLOATS] partial attention results of groups >= 1
   int poll_ns;             // pause between two samples of a stage counter
   int drop_event;          // debug: this event is never signalled (exercises the bounded waits); -1 = none

@@ -76,6 +76,7 @@ struct pi05_engine {
   int batch = 1;
   int row_groups = 1;
   int key_groups = 1;
+  int pages_per_obs = 1, page_tokens = 1;
   bool bound = false;
   const void* inputs[PI05_NUM_INPUTS] = {};
   void* actions = nullptr;
@@ -156,6 +157,7 @@ void build_layout(pi05_engine* h) {
   add("d_acc", B * T * W * 4);
   add("act", B * T * FF * 2);
   add("att_part", (size_t)(MAX_KEY_GROUPS - 1) * NROW_CTAS * ATT_PART_FLOATS * 4);
+  add("page_table", (size_t)h->max_batch * ((h->max_prefix + 63) / 64) * sizeof(int));
   add("sched", (size_t)h->grid * MAX_UNITS * sizeof(Unit));
   add("sched_n", (size_t)h->grid * sizeof(int));
   h->ws_bytes = off;
@@ -227,21 +229,41 @@ int encode_2d(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t inner, 
   return PI05_OK;
 }
 
-// K / V of attention, [planes][rows][256] BF16 in memory, described as {64, rows, 4, planes}: the 256 dims of a row are
-// four 64-dim segments, and the segment index is an outer dimension, so that one copy of a box {64, 64, 4, 1} lands
-// as four segment blocks of 64 rows x 128 B (128-byte swizzle each).  Rows past the end of a plane read as zeros.
-int encode_kv(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t rows, uint64_t planes) {
+// K / V of attention.  The 256 dims of a token are four 64-dim segments, and the segment index is an outer dimension
+// of the map, so that one copy of a box {64 dims, 64 tokens, 4 segments, 1, 1} lands as four segment blocks of
+// 64 rows x 128 B (128-byte swizzle each).  `rows` tokens per page are visible (the rest read as zeros), pages are
+// addressed by (layer, page); strides in BF16 elements.
+int encode_kv(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t rows, uint64_t layers, uint64_t pages,
+              uint64_t token_stride, uint64_t layer_stride, uint64_t page_stride) {
   EncodeTiledFn enc = get_encode();
   if (!enc) { h->last_error = "cuTensorMapEncodeTiled is not available from this driver"; return PI05_ERR_CUDA; }
-  cuuint64_t dims[4] = {(cuuint64_t)KATOM, rows, (cuuint64_t)(HD / KATOM), planes};
-  cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)KATOM * 2, rows * HD * 2};
+  cuuint64_t dims[5] = {(cuuint64_t)KATOM, rows, (cuuint64_t)(HD / KATOM), layers, pages};
+  cuuint64_t strides[4] = {token_stride * 2, (cuuint64_t)KATOM * 2, layer_stride * 2, page_stride * 2};
+  cuuint32_t box[5] = {KATOM, 64, HD / KATOM, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    h->last_error = "cuTensorMapEncodeTiled (attention K/V) failed with code " + std::to_string((int)r);
+    return PI05_ERR_CUDA;
+  }
+  return PI05_OK;
+}
+
+// This layer's suffix keys / values in the workspace: [batch][50][256], described as {64, 50, 4, batch}.
+int encode_suffix_kv(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t planes) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) { h->last_error = "cuTensorMapEncodeTiled is not available from this driver"; return PI05_ERR_CUDA; }
+  cuuint64_t dims[4] = {(cuuint64_t)KATOM, (cuuint64_t)T, (cuuint64_t)(HD / KATOM), planes};
+  cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)KATOM * 2, (cuuint64_t)T * HD * 2};
   cuuint32_t box[4] = {KATOM, 64, HD / KATOM, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    h->last_error = "cuTensorMapEncodeTiled (attention K/V) failed with code " + std::to_string((int)r);
+    h->last_error = "cuTensorMapEncodeTiled (suffix K/V) failed with code " + std::to_string((int)r);
     return PI05_ERR_CUDA;
   }
   return PI05_OK;
@@ -327,12 +349,57 @@ int pi05_workspace_bytes(pi05_handle_t h, size_t* bytes) {
 
 int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, int batch, void* actions,
               void* workspace, size_t workspace_bytes) {
-  if (!valid_handle(h) || !inputs || !actions || !workspace) return PI05_ERR_ARGUMENT;
+  if (!valid_handle(h) || !inputs) return PI05_ERR_ARGUMENT;
+  if (batch < 1 || batch > MAXB || prefix_len < 1) return PI05_ERR_ARGUMENT;
+  if (!inputs[22] || !inputs[23]) { h->last_error = "null input pointer"; return PI05_ERR_ARGUMENT; }
+  // dense [batch][18][P][1][256]: one page per observation
+  int table[MAXB];
+  for (int b = 0; b < batch; ++b) table[b] = b;
+  pi05_kv_view kv;
+  kv.k = inputs[22]; kv.v = inputs[23];
+  kv.token_stride = HD; kv.layer_stride = (long long)prefix_len * HD; kv.page_stride = (long long)NL * prefix_len * HD;
+  kv.page_tokens = prefix_len; kv.num_pages = batch; kv.pages_per_obs = 1; kv.page_table = table;
+  return pi05_bind_view(h, inputs, &kv, prefix_len, batch, actions, workspace, workspace_bytes);
+}
+
+int pi05_bind_view(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], const pi05_kv_view* kv, int prefix_len,
+                   int batch, void* actions, void* workspace, size_t workspace_bytes) {
+  if (!valid_handle(h) || !inputs || !kv || !actions || !workspace) return PI05_ERR_ARGUMENT;
   if (batch < 1) return PI05_ERR_ARGUMENT;
   if (batch > h->max_batch) return PI05_ERR_UNSUPPORTED;
   if (prefix_len < 1 || prefix_len > h->max_prefix) return PI05_ERR_ARGUMENT;
   if (workspace_bytes < h->ws_bytes) { h->last_error = "workspace too small"; return PI05_ERR_ARGUMENT; }
+  {
+    // the view of the prefix cache
+    const int max_pages = (h->max_prefix + 63) / 64;
+    if (!kv->k || !kv->v || !kv->page_table) { h->last_error = "null pointer in the prefix cache view"; return PI05_ERR_ARGUMENT; }
+    if ((reinterpret_cast<uintptr_t>(kv->k) & 15) || (reinterpret_cast<uintptr_t>(kv->v) & 15)) {
+      h->last_error = "prefix cache pools must be 16-byte aligned";
+      return PI05_ERR_ARGUMENT;
+    }
+    if (kv->token_stride < HD || kv->layer_stride < 0 || kv->page_stride < 0 || (kv->token_stride & 7) ||
+        (kv->layer_stride & 7) || (kv->page_stride & 7)) {
+      h->last_error = "prefix cache strides must be multiples of 8 elements (token stride >= 256)";
+      return PI05_ERR_ARGUMENT;
+    }
+    if (kv->page_tokens < 1 || kv->num_pages < 1 || kv->pages_per_obs < 1 || kv->pages_per_obs > max_pages ||
+        (kv->pages_per_obs > 1 && kv->page_tokens % 64 != 0) ||
+        (long long)kv->pages_per_obs * kv->page_tokens < prefix_len) {
+      h->last_error = "prefix cache pages do not cover the prefix (page_tokens must be a multiple of 64 with several pages)";
+      return PI05_ERR_ARGUMENT;
+    }
+    if ((long long)batch * kv->pages_per_obs > MAX_PAGE_ENTRIES) {
+      h->last_error = "page table too large (batch x pages per observation > 1024)";
+      return PI05_ERR_UNSUPPORTED;
+    }
+    for (int i = 0; i < batch * kv->pages_per_obs; ++i)
+      if (kv->page_table[i] < 0 || kv->page_table[i] >= kv->num_pages) {
+        h->last_error = "page table entry " + std::to_string(i) + " is outside the pool";
+        return PI05_ERR_ARGUMENT;
+      }
+  }
   for (int i = 0; i < PI05_NUM_INPUTS; ++i) {
+    if (i == 22 || i == 23) continue;   // superseded by the view
     if (!inputs[i]) { h->last_error = "null input pointer"; return PI05_ERR_ARGUMENT; }
     if (i != 24 && (reinterpret_cast<uintptr_t>(inputs[i]) & 15)) {
       h->last_error = "input " + std::to_string(i) + " is not 16-byte aligned";
@@ -347,6 +414,9 @@ int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int pr
   if (!guard.ok) return PI05_ERR_CUDA;
   h->bound = false;
   for (int i = 0; i < PI05_NUM_INPUTS; ++i) h->inputs[i] = inputs[i];
+  h->inputs[22] = kv->k; h->inputs[23] = kv->v;
+  h->pages_per_obs = kv->pages_per_obs;
+  h->page_tokens = kv->page_tokens;
   h->actions = actions;
   h->ws = static_cast<uint8_t*>(workspace);
   h->prefix = prefix_len;
@@ -382,10 +452,25 @@ int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int pr
   if ((rc = encode_2d(h, &h->maps.an_ffn, region_ptr<void>(h, "an_ffn"), W, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
   if ((rc = encode_2d(h, &h->maps.attn, region_ptr<void>(h, "attn"), QD, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
   if ((rc = encode_2d(h, &h->maps.act, region_ptr<void>(h, "act"), FF, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
-  if ((rc = encode_kv(h, &h->maps.pk, inputs[22], (uint64_t)prefix_len, (uint64_t)NL * batch))) return rc;
-  if ((rc = encode_kv(h, &h->maps.pv, inputs[23], (uint64_t)prefix_len, (uint64_t)NL * batch))) return rc;
-  if ((rc = encode_kv(h, &h->maps.sk, region_ptr<void>(h, "k"), (uint64_t)T, (uint64_t)batch))) return rc;
-  if ((rc = encode_kv(h, &h->maps.sv, region_ptr<void>(h, "v"), (uint64_t)T, (uint64_t)batch))) return rc;
+  {
+    // full pages, and the last page of an observation cut at its last valid token
+    const uint64_t full_rows = (uint64_t)kv->page_tokens;
+    const uint64_t tail_rows = (uint64_t)(prefix_len - (prefix_len - 1) / kv->page_tokens * kv->page_tokens);
+    const void* pools[2] = {kv->k, kv->v};
+    CUtensorMap* full[2] = {&h->maps.pk, &h->maps.pv};
+    CUtensorMap* tail[2] = {&h->maps.pk_tail, &h->maps.pv_tail};
+    for (int i = 0; i < 2; ++i) {
+      if ((rc = encode_kv(h, full[i], pools[i], full_rows, NL, (uint64_t)kv->num_pages, (uint64_t)kv->token_stride,
+                          (uint64_t)kv->layer_stride, (uint64_t)kv->page_stride))) return rc;
+      if ((rc = encode_kv(h, tail[i], pools[i], tail_rows, NL, (uint64_t)kv->num_pages, (uint64_t)kv->token_stride,
+                          (uint64_t)kv->layer_stride, (uint64_t)kv->page_stride))) return rc;
+    }
+  }
+  if ((rc = encode_suffix_kv(h, &h->maps.sk, region_ptr<void>(h, "k"), (uint64_t)batch))) return rc;
+  if ((rc = encode_suffix_kv(h, &h->maps.sv, region_ptr<void>(h, "v"), (uint64_t)batch))) return rc;
+  e = cudaMemcpy(region_ptr<void>(h, "page_table"), kv->page_table, (size_t)batch * kv->pages_per_obs * sizeof(int),
+                 cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return fail_cuda(h, "cudaMemcpy(page table)", e);
   e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceSynchronize", e);
   h->bound = true;
@@ -427,7 +512,7 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.wd = (const __nv_bfloat16*)in[14];
   ObsPtrs& o = p.ob;
   o.noise = (const float*)in[21];
-  o.prefix_k = (const __nv_bfloat16*)in[22]; o.prefix_v = (const __nv_bfloat16*)in[23];
+
   o.prefix_mask = (const uint8_t*)in[24];
   o.actions = (float*)h->actions;
   o.x = region_ptr<float>(h, "x"); o.o_acc = region_ptr<float>(h, "o_acc"); o.d_acc = region_ptr<float>(h, "d_acc");
@@ -450,6 +535,8 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.row_groups = h->row_groups;
   p.key_groups = h->key_groups;
   p.att_part = region_ptr<float>(h, "att_part");
+  p.page_table = region_ptr<int>(h, "page_table");
+  p.pages_per_obs = h->pages_per_obs; p.page_tokens = h->page_tokens;
   p.drop_event = h->drop_event;
   p.poll_ns = h->poll_ns;
   for (int g = 0; g < 4; ++g) p.n_units[g] = h->n_units[g];

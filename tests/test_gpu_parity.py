@@ -325,3 +325,79 @@ def test_batched_observations(batch, variant):
     assert float((alone - got[0]).abs().max()) <= 2 * (O.ATOL + O.RTOL * float(alone.abs().max()))
     one.close()
     arm.close()
+
+
+def _pool_from_dense(dense, page_tokens, num_pages, order, token_pad, fill):
+    """Scatter a dense cache [B][L][P][1][256] into a pool [pages][L][page_tokens][1][256 + token_pad] (the returned
+    view drops the padding) whose unused pages, padding and rows behind the prefix hold `fill`."""
+    B, L, P = dense.shape[0], dense.shape[1], dense.shape[2]
+    per = (P + page_tokens - 1) // page_tokens
+    pool = torch.full((num_pages, L, page_tokens, 1, 256 + token_pad), fill, dtype=torch.bfloat16)
+    table = []
+    for b in range(B):
+        row = []
+        for lp in range(per):
+            phys = order[b * per + lp]
+            n = min(page_tokens, P - lp * page_tokens)
+            pool[phys, :, :n, :, :256] = dense[b, :, lp * page_tokens:lp * page_tokens + n]
+            row.append(phys)
+        table.append(row)
+    return pool, table
+
+
+@pytest.mark.parametrize("prefix,page_tokens,batch,variant", [(300, 1024, 1, "b200-s2-l3"), (512, 128, 2, "b200-s2-l2"),
+                                                              (968, 64, 1, "b200-s1-l2")])
+def test_prefix_cache_view(prefix, page_tokens, batch, variant):
+    """The prefix cache read where a producer left it: pages in shuffled order inside a larger pool, padding between
+    tokens, one over-long page per observation or many 64-token pages.  Unused pages, the padding and the rows
+    behind the prefix hold NaN, so any read of them would poison the result; the result must match the dense bind."""
+    from pi05_megakernel_b200.arm import PagedPrefix, Pi05Arm
+    geo, ogeo = FX.Geometry(prefix=prefix), O.Geo(prefix=prefix)
+    masks = ["scatter", "pad"][:batch]
+    stacked, per = FX.make_batch(geo, FX.SEEDS[1], batch, "cpu", masks)
+    dense_k = stacked["prefix_k"].reshape(batch, geo.layers, prefix, 1, 256)
+    dense_v = stacked["prefix_v"].reshape(batch, geo.layers, prefix, 1, 256)
+    pages_per = (prefix + page_tokens - 1) // page_tokens
+    num_pages = batch * pages_per + 3
+    order = torch.randperm(num_pages, generator=torch.Generator().manual_seed(5)).tolist()
+    pool_k, table = _pool_from_dense(dense_k, page_tokens, num_pages, order, 64, float("nan"))
+    pool_v, _ = _pool_from_dense(dense_v, page_tokens, num_pages, order, 64, float("nan"))
+    dev = {k: v.cuda() for k, v in stacked.items()}
+    if batch == 1:
+        dev = {k: (v[0] if k in FX.OBSERVATION else v) for k, v in dev.items()}
+    arm = Pi05Arm(geo, variant, "cuda", batch=batch)
+    arm.bind(dev)
+    dense = _run(arm).reshape(batch, 50, 32)
+    gk, gv = pool_k.cuda(), pool_v.cuda()
+    view = PagedPrefix(gk[..., :256], gv[..., :256], table)
+    rest = {k: v for k, v in dev.items() if k not in ("prefix_k", "prefix_v")}
+    arm.bind(rest, kv_pages=view)
+    paged = _run(arm).reshape(batch, 50, 32)
+    assert torch.isfinite(paged).all()
+    assert float((paged - dense).abs().max()) <= 2 * (O.ATOL + O.RTOL * float(dense.abs().max()))
+    for b in range(batch):
+        want = O.chunk(per[b], ogeo, False, arm.steps, arm.layers)
+        exact = O.chunk(per[b], ogeo, True, arm.steps, arm.layers)
+        assert O.band(want, paged[b], exact)["pass"], b
+    arm.close()
+
+
+def test_prefix_cache_view_rejects_bad_views():
+    from pi05_megakernel_b200 import _lib
+    from pi05_megakernel_b200.arm import PagedPrefix, Pi05Arm
+    geo = FX.Geometry(prefix=200)
+    dev = {k: v.cuda() for k, v in FX.make_inputs(geo, FX.SEEDS[0], "cpu").items()}
+    rest = {k: v for k, v in dev.items() if k not in ("prefix_k", "prefix_v")}
+    arm = Pi05Arm(geo, "b200-s1-l1", "cuda")
+    pool = torch.zeros((4, geo.layers, 100, 1, 256), dtype=torch.bfloat16, device="cuda")
+    for table, why in (([[0, 1]], "page_tokens not a multiple of 64"), ([[0]], "pages do not cover the prefix"),
+                       ([[0, 9]], "entry outside the pool")):
+        with pytest.raises(_lib.EngineError) as err:
+            arm.bind(rest, kv_pages=PagedPrefix(pool, pool, table))
+        assert err.value.code == _lib.ERR_ARGUMENT, why
+    odd = torch.zeros((1, geo.layers, 256, 1, 260), dtype=torch.bfloat16, device="cuda")[..., :256]
+    with pytest.raises(_lib.EngineError):
+        arm.bind(rest, kv_pages=PagedPrefix(odd, odd, [[0]]))      # token stride 260 is not a multiple of 8 elements
+    with pytest.raises(_lib.EngineError):
+        arm.launch()                                                # nothing is bound after a failed bind
+    arm.close()
