@@ -175,6 +175,9 @@ def main() -> int:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--prefix", type=int, default=128)
     ap.add_argument("--batch", type=int, default=1, help="independent observations per GPU per launch (1..16)")
+    ap.add_argument("--mask", default="full", choices=["full", "pad", "scatter"],
+                    help="prefix validity: every token valid, a right-padded prefix, or the same count of valid tokens at "
+                         "random places (count uniform in [prefix/2, prefix], from the seed)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--stage-times", action="store_true",
                     help="also print (stderr) the in-kernel stage timeline of one L2-flushed chunk")
@@ -198,7 +201,7 @@ def main() -> int:
     geo = FX.Geometry(prefix=args.prefix)
     B = args.batch
     weights = FX.make_weights(geo, FX.SEEDS[0])
-    obs = [FX.make_observation(geo, DP.observation_seed(FX.SEEDS[0], rank, i)) for i in range(B)]  # own observations
+    obs = [FX.make_observation(geo, DP.observation_seed(FX.SEEDS[0], rank, i), args.mask) for i in range(B)]  # own observations
     cpu = {k: weights[k] if k in weights else (obs[0][k] if B == 1 else torch.stack([o[k] for o in obs]).contiguous())
            for k in FX.ORDER}
     dev = {k: v.to(device) for k, v in cpu.items()}
@@ -277,7 +280,7 @@ def main() -> int:
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": (1e3 / ms_step) / (1e3 / SOTA_GRAPH_MS) if world == 1 and B == 1 else None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"pi0.5 action chunk, B={B} per GPU, prefix {geo.prefix}, 10 Euler steps x 18 "
+            "config": {"workload": f"pi0.5 action chunk, B={B} per GPU, prefix {geo.prefix} ({args.mask} mask), 10 Euler steps x 18 "
                                    "Gemma-300M expert layers, BF16 weights and prefix K/V, FP32 time MLP / "
                                    "modulation; one persistent kernel launch per chunk",
                        "l2": "flushed before every timed chunk (2x L2 zero fill)",
