@@ -169,7 +169,7 @@ int pi05_destroy(pi05_handle_t h);
  *
  * Limits: prefix_len <= PI05_STATIC_MAX_PREFIX and a GPU whose schedule fits the array (any B200), otherwise
  * PI05_ERR_UNSUPPORTED; batch 1 only.  Returns a PI05_* code; the call is asynchronous like pi05_launch. */
-#define PI05_STATIC_SCRATCH_BYTES (8u << 20)
+#define PI05_STATIC_SCRATCH_BYTES (12u << 20)
 #define PI05_STATIC_MAX_PREFIX 1024
 int pi05_chunk_static(int device, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, void* actions,
                       int n_steps, int n_layers, void* stream);

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("PI05_B200_LIB") or os.path.join(HERE, "libpi05_b200.so")   # the variable: another build of the same library
 NUM_INPUTS = 25
 NUM_STAMPS = 256
-STATIC_SCRATCH_BYTES = 8 << 20
+STATIC_SCRATCH_BYTES = 12 << 20
 STATIC_MAX_PREFIX = 1024
 
 EVENT_ATTENTION_DONE, EVENT_FFN_NORM_READY = 7, 9

@@ -29,7 +29,7 @@ __device__ __forceinline__ ObsPtrs obs(const Params& p, int b) {
   o.prefix_mask += (size_t)b * p.prefix;
   o.o_acc += (size_t)b * T * W; o.d_acc += (size_t)b * T * W; o.qkv_acc += (size_t)b * T * QKVW;
   o.rope += (size_t)b * T * (HD / 2); o.rope2 += (size_t)b * T * (HD / 2);
-  o.h += (size_t)b * T * W; o.an_attn += (size_t)b * T * W; o.an_ffn += (size_t)b * T * W;
+  o.h += (size_t)b * T * W; o.an_attn += (size_t)b * AN_COPIES * T * W; o.an_ffn += (size_t)b * AN_COPIES * T * W;
   o.k += (size_t)b * T * HD; o.v += (size_t)b * T * HD; o.attn += (size_t)b * T * QD; o.act += (size_t)b * T * FF;
   o.b = b;
   return o;
@@ -375,7 +375,9 @@ __device__ void row_op(const Params& p, const ObsPtrs& o, uint8_t* smem, int uni
       const float b = __fadd_rn(__fmul_rn(__fmul_rn(v[e + 1], rs), __fadd_rn(1.0f, scale[e + 1])), shift[e + 1]);
       ow[e >> 1] = pack_bf16(a, b);
     }
-    *reinterpret_cast<uint4*>(dst + (size_t)t * W + c0) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+#pragma unroll
+    for (int r = 0; r < AN_COPIES; ++r)   // one copy per group of reader CTAs
+      *reinterpret_cast<uint4*>(dst + ((size_t)r * T + t) * W + c0) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
   };
   auto store_h = [&](const float (&v)[8]) {   // the kernel itself never reads h back; kept for stage-level checks
     const uint4 packed = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
@@ -597,8 +599,11 @@ struct AttChunkIssue {
   }
 };
 
+constexpr int QF_KEPT = PI05_QF_KEPT;   // 16-dim blocks of q (of 16) whose A fragments stay in registers (even)
 // S = Q K^T for this warp's 8 keys of one stage (two interleaved accumulation chains).
-__device__ __forceinline__ void att_qk(const uint32_t (&qf)[HD / 16][4], uint32_t ks, int warp, int lane, float (&s4)[4]) {
+__device__ __forceinline__ void att_qk(const uint32_t (&qf)[QF_KEPT][4], uint32_t qs, uint32_t ks, int warp, int lane,
+                                       float (&s4)[4]) {
+  const uint32_t qaddr0 = qs + ((lane & 15) * KV_STRIDE + (lane >> 4) * 8) * 2;
   float e[4] = {0.f, 0.f, 0.f, 0.f}, o[4] = {0.f, 0.f, 0.f, 0.f};
   // key row r = warp * 8 + (lane & 7); 16-byte piece c of the row sits at piece c ^ (r & 7) of its 128-byte line
   const uint32_t krow = ks + (warp * 8 + (lane & 7)) * 128;
@@ -607,8 +612,16 @@ __device__ __forceinline__ void att_qk(const uint32_t (&qf)[HD / 16][4], uint32_
   for (int kk = 0; kk < HD / 16; kk += 2) {
     uint32_t b0, b1, b2, b3;
     ptx::ldmatrix_x4(krow + (kk >> 2) * KV_SEG_BYTES + ((((kk & 3) * 2 + kc) ^ ksw) << 4), b0, b1, b2, b3);
-    ptx::mma_16816(e, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
-    ptx::mma_16816(o, qf[kk + 1][0], qf[kk + 1][1], qf[kk + 1][2], qf[kk + 1][3], b2, b3);
+    if (kk < QF_KEPT) {      // the first blocks of q stay in registers, the rest is fetched again for every stage
+      ptx::mma_16816(e, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+      ptx::mma_16816(o, qf[kk + 1][0], qf[kk + 1][1], qf[kk + 1][2], qf[kk + 1][3], b2, b3);
+    } else {
+      uint32_t a0, a1, a2, a3, a4, a5, a6, a7;
+      ptx::ldmatrix_x4(qaddr0 + kk * 32, a0, a1, a2, a3);
+      ptx::ldmatrix_x4(qaddr0 + kk * 32 + 32, a4, a5, a6, a7);
+      ptx::mma_16816(e, a0, a1, a2, a3, b0, b1);
+      ptx::mma_16816(o, a4, a5, a6, a7, b2, b3);
+    }
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) s4[i] = e[i] + o[i];
@@ -631,7 +644,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
   const float NEG = -INFINITY;
 
   float m_lo = -1e30f, m_hi = -1e30f, l_lo = 0.f, l_hi = 0.f;
-  uint32_t qf[HD / 16][4];
+  uint32_t qf[QF_KEPT][4];
   float oa[4][4];
 #pragma unroll
   for (int a = 0; a < 4; ++a)
@@ -649,7 +662,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
       // the whole 16 x 256 q tile as A fragments, kept in registers for every stage of every round
       const uint32_t qaddr0 = qs + ((lane & 15) * KV_STRIDE + (lane >> 4) * 8) * 2;
 #pragma unroll
-      for (int kk = 0; kk < HD / 16; ++kk) ptx::ldmatrix_x4(qaddr0 + kk * 32, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+      for (int kk = 0; kk < QF_KEPT; ++kk) ptx::ldmatrix_x4(qaddr0 + kk * 32, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
     }
     if (tr && c0 == cbeg) p.stamps[224] = globaltimer();
     if (tr && c0 != cbeg && !more) p.stamps[232] = globaltimer();
@@ -657,7 +670,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
     for (int j = 0; j < ATT_STAGES; ++j)
       if (j < early) {
         if (!att_wait(issue.c, smem, bars, 0, j, wst)) return false;
-        att_qk(qf, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
+        att_qk(qf, qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
       }
     if (early < nst) {
       if (!issue(c0 + early, early)) return false;     // waits for the k / v tiles, then copies the suffix chunk
@@ -665,7 +678,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
       for (int j = 0; j < ATT_STAGES; ++j)
         if (j >= early && j < nst) {
           if (!att_wait(issue.c, smem, bars, 0, j, wst)) return false;
-          att_qk(qf, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
+          att_qk(qf, qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
         }
     }
     if (tr && c0 == cbeg) p.stamps[225] = globaltimer();
@@ -848,7 +861,7 @@ __device__ __forceinline__ void weight_rows(const Params& p, const Unit& un, int
 // in its warp, so every instruction costs its full latency: everything that does not change within a unit is
 // computed once per unit.
 __device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t ring,
-                                const Bars& b, Producer& st, uint32_t until, uint64_t policy) {
+                                const Bars& b, Producer& st, uint32_t until, uint64_t policy, bool leader) {
   const int npass = p.n_steps * p.n_layers;
   if (nunits == 0) { st.done = true; return; }
   const bool once = PI05_NB(p) == 1;     // one observation: every weight byte is used once, mark it evict-first in L2
@@ -867,13 +880,15 @@ __device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units
       if (!wait_mbar(c, b.empty + 8 * slot, par ^ 1, WAIT_W_EMPTY, stage)) { st.done = true; break; }
       const uint32_t full = b.full + 8 * slot;
       const uint32_t dst = ring + slot * STAGE_BYTES_ALL;
-      ptx::mbar_expect_tx(full, W_STAGE_BYTES);
-      if (once) {
+      if (!leader) {
+      } else if (once) {
+        ptx::mbar_expect_tx(full, W_STAGE_BYTES);
         ptx::tma_load_2d_hint(dst, ma, full, kc, ra, policy);
         ptx::tma_load_2d_hint(dst + W_ATOM_BYTES / 2, mb, full, kc, rbw, policy);
         ptx::tma_load_2d_hint(dst + W_ATOM_BYTES, ma, full, kc + KATOM, ra, policy);
         ptx::tma_load_2d_hint(dst + W_ATOM_BYTES + W_ATOM_BYTES / 2, mb, full, kc + KATOM, rbw, policy);
       } else {                        // the unit's weights come again for the next observation: keep them in L2
+        ptx::mbar_expect_tx(full, W_STAGE_BYTES);
         ptx::tma_load_2d(dst, ma, full, kc, ra);
         ptx::tma_load_2d(dst + W_ATOM_BYTES / 2, mb, full, kc, rbw);
         ptx::tma_load_2d(dst + W_ATOM_BYTES, ma, full, kc + KATOM, ra);
@@ -894,7 +909,8 @@ __device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units
 
 // Activation half of every stage: waits for the stage that produces the operand, then follows the same stage
 // order as the weight producer.
-__device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t ring, const Bars& b) {
+__device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t ring, const Bars& b,
+                             bool leader) {
   const int npass = p.n_steps * p.n_layers;
   uint32_t slot = 0, par = 0;
   for (int pass = 0; pass < npass; ++pass) {
@@ -911,19 +927,24 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
       else if (un.gemm == G_GU) { m = &p.maps.an_ffn; ev = EV_ANF; target = NROW_CTAS * (pass + 1); }
       else { m = &p.maps.act; ev = EV_GU; target = p.n_units[G_GU] * (pass + 1); }
       if (!wait_event(c, p.ctrl + EVB(ev, ob), target, stage)) return;
-      if (ob == 0) trace(p, c.cta, pass, un.gemm, 0);
+      if (ob == 0 && leader) trace(p, c.cta, pass, un.gemm, 0);
       ptx::fence_proxy_async_global();
+      // first row of this observation's tile: the normalised activations exist in AN_COPIES copies
+      const int row0 = (un.gemm == G_QKV || un.gemm == G_GU) ? (ob * AN_COPIES + c.cta % AN_COPIES) * T : ob * T;
       int kc = un.k0 * KSTAGE;
       for (int a = 0; a < un.nk; ++a, kc += KSTAGE) {
         if (!wait_mbar(c, b.empty + 8 * slot, par ^ 1, WAIT_A_EMPTY, stage)) return;
         const uint32_t full = b.full + 8 * slot;
         const uint32_t dst = ring + slot * STAGE_BYTES_ALL + W_STAGE_BYTES;
-        ptx::mbar_expect_tx(full, A_STAGE_TX);
-        ptx::tma_load_2d(dst, m, full, kc, ob * T);          // rows of observation ob
-        ptx::tma_load_2d(dst + A_ATOM_BYTES, m, full, kc + KATOM, ob * T);
+        if (leader) {
+          ptx::mbar_expect_tx(full, A_STAGE_TX);
+          ptx::tma_load_2d(dst, m, full, kc, row0);
+          ptx::tma_load_2d(dst + A_ATOM_BYTES, m, full, kc + KATOM, row0);
+          if (PI05_TRACE && p.stamps != nullptr && pass == 1 && c.cta == 0 && un.gemm == G_GU && a < 8) p.stamps[241 + 2 * a] = globaltimer();
+        }
         if (++slot == NSTG) { slot = 0; par ^= 1; }
       }
-      if (ob == 0) trace(p, c.cta, pass, un.gemm, 1);
+      if (ob == 0 && leader) trace(p, c.cta, pass, un.gemm, 1);
     }
   }
 }
@@ -932,7 +953,7 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
 // tcgen05 instruction costs it about 50 cycles, so the loop does one wait and one commit per eight MMAs and
 // advances the shared-memory descriptors by adding constants to their low words.
 __device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t ring,
-                               const Bars& b, uint32_t tmem) {
+                               const Bars& b, uint32_t tmem, bool leader) {
   const int npass = p.n_steps * p.n_layers;
   const uint32_t idesc = ptx::umma_idesc_bf16(128, 64);
   const uint64_t adesc0 = ptx::umma_smem_desc(ring), bdesc0 = ptx::umma_smem_desc(ring + W_STAGE_BYTES);
@@ -950,24 +971,17 @@ __device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units,
       uint32_t accumulate = 0;
       for (int a = 0; a < un.nk; ++a, ++it) {
         if (!wait_mbar(c, b.full + 8 * slot, par, WAIT_W_FULL, stage)) return it;
-        if (a == 0 && ob == 0) trace(p, c.cta, pass, un.gemm, 2);
-        ptx::tc_fence_after();
+        if (a == 0 && ob == 0 && leader) trace(p, c.cta, pass, un.gemm, 2);
+        if (PI05_TRACE && leader && p.stamps != nullptr && pass == 1 && c.cta == 0 && un.gemm == G_GU && a < 8) p.stamps[240 + 2 * a] = globaltimer();
         const uint64_t ad = adesc0 + (uint64_t)(slot * (STAGE_BYTES_ALL >> 4));
         const uint64_t bd = bdesc0 + (uint64_t)(slot * (STAGE_BYTES_ALL >> 4));
-        ptx::umma_bf16(d, ad, bd, idesc, accumulate);
-        ptx::umma_bf16(d, ad + 2, bd + 2, idesc, 1u);
-        ptx::umma_bf16(d, ad + 4, bd + 4, idesc, 1u);
-        ptx::umma_bf16(d, ad + 6, bd + 6, idesc, 1u);
-        ptx::umma_bf16(d, ad + (W_ATOM_BYTES >> 4), bd + (A_ATOM_BYTES >> 4), idesc, 1u);
-        ptx::umma_bf16(d, ad + (W_ATOM_BYTES >> 4) + 2, bd + (A_ATOM_BYTES >> 4) + 2, idesc, 1u);
-        ptx::umma_bf16(d, ad + (W_ATOM_BYTES >> 4) + 4, bd + (A_ATOM_BYTES >> 4) + 4, idesc, 1u);
-        ptx::umma_bf16(d, ad + (W_ATOM_BYTES >> 4) + 6, bd + (A_ATOM_BYTES >> 4) + 6, idesc, 1u);
+        if (leader)
+          ptx::umma_bf16_stage8<(W_ATOM_BYTES >> 4), (A_ATOM_BYTES >> 4)>(d, ad, bd, idesc, accumulate, b.empty + 8 * slot);
         accumulate = 1u;
-        ptx::umma_commit(b.empty + 8 * slot);
         if (++slot == NSTG) { slot = 0; par ^= 1; }
       }
-      ptx::umma_commit(b.tfull + 8 * buf);
-      if (ob == 0) trace(p, c.cta, pass, un.gemm, 3);
+      if (leader) ptx::umma_commit(b.tfull + 8 * buf);
+      if (ob == 0 && leader) trace(p, c.cta, pass, un.gemm, 3);
     }
   }
   return it;
@@ -1210,7 +1224,10 @@ __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, 
 __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_constant__ Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int cta = blockIdx.x, ncta = gridDim.x;
+  const int ncta = gridDim.x;
+  // which CTA of the schedule this block plays: by default its own index; permuted, the two blocks of a cluster
+  // (a TPC) are CTA i and CTA grid / 2 + i, e.g. a gate/up CTA next to a light one
+  const int cta = p.cta_perm ? (int)(blockIdx.x >> 1) + (int)(blockIdx.x & 1) * (ncta >> 1) : (int)blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool is_gemm = cta < p.n_gemm_ctas;
   const Ctx c{p.ctrl, p.wait_limit, cta, (unsigned)p.poll_ns};
@@ -1247,9 +1264,10 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
   // The first ring of weights does not depend on anything: start streaming before the prologue.
   Producer prod{0, 0, 0, 0, 0u, 0u, 0u, false};
   uint64_t policy = 0;
-  if (is_gemm && warp == 0 && lane == 0) {
+  const bool leader = ptx::elect_one();     // every warp is converged here
+  if (is_gemm && warp == 0) {
     policy = ptx::policy_evict_first();
-    weight_producer(p, c, units, nunits, ring, b, prod, NSTG, policy);
+    weight_producer(p, c, units, nunits, ring, b, prod, NSTG, policy, leader);
   }
 
   // ---------------- prologue: tables, time MLP, all modulation rows (FP32 weights streamed once)
@@ -1266,15 +1284,17 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
 
   if (ok) {
     if (is_gemm) {
+      // Warps 0-2 run their loops as whole (converged) warps and one elected lane issues the TMA / tcgen05
+      // instructions: with warp-uniform control flow the compiler keeps descriptors and coordinates in uniform
+      // registers, which those instructions read; the same loops run by a single lane issued ~35 % slower.
       if (warp == 0) {
-        if (lane == 0) {
-          weight_producer(p, c, units, nunits, ring, b, prod, 0xffffffffu, policy);
-          s_issued = prod.it;
-        }
+        weight_producer(p, c, units, nunits, ring, b, prod, 0xffffffffu, policy, leader);
+        if (leader) s_issued = prod.it;
       } else if (warp == 1) {
-        if (lane == 0) s_consumed = mma_issuer(p, c, units, nunits, ring, b, tmem);
+        const uint32_t consumed = mma_issuer(p, c, units, nunits, ring, b, tmem, leader);
+        if (leader) s_consumed = consumed;
       } else if (warp == 2) {
-        if (lane == 0) act_producer(p, c, units, nunits, ring, b);
+        act_producer(p, c, units, nunits, ring, b, leader);
       } else if (warp >= 4) {
         epilogue(p, c, units, nunits, smem, b, tmem);
       }
@@ -1290,7 +1310,7 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
       if (stamp) p.stamps[5] = globaltimer();
       row_cta(p, c, smem, unit, group, hn);
     }
-  } else if (is_gemm && warp == 0 && lane == 0) {
+  } else if (is_gemm && warp == 0 && leader) {
     s_issued = prod.it;
   }
 

@@ -78,6 +78,10 @@ constexpr int MAXB = 16;            // observations per launch (weights are stre
 #define EVW(e) EVB(e, 0)
 constexpr int NKVTILES = 4;         // k (2) and v (2) tiles of the QKV GEMM
 static_assert(NROW_CTAS <= 2 * MAXB, "EV_PART / EV_PART2 slots");
+// Copies of the normalised activations (inputs of the QKV and gate/up GEMMs, read by up to 64 CTAs at the same
+// moment): GEMM CTA c reads copy c % AN_COPIES.  Eight copies were measured and changed nothing in the arrival rate
+// of the activation stages (the readers are not limited by contention on the same L2 lines), so one copy is kept.
+constexpr int AN_COPIES = 1;
 constexpr int MAX_KEY_GROUPS = 3;   // row-CTA groups that may share the keys of one attention
 constexpr int ATT_PART_FLOATS = 256 * 16 + 16 * 2;   // per (group, unit): every thread's 16 accumulators, then (max, sum) per row
 constexpr int CTRL_BYTES = 128 * (1 + NEVENTS * MAXB);
@@ -92,7 +96,7 @@ constexpr long long DRAIN_CYCLES = 400000;          // exit-time grace period fo
 
 struct alignas(64) TMaps {
   CUtensorMap wq, wk, wv, wo, wg, wu, wd;   // weights: {K, L*rows} BF16, box {64, 64}, 128-B swizzle
-  CUtensorMap an_attn, an_ffn, attn, act;   // activations: {K, 50} BF16, box {64, 50}; slot rows 50..63 are never written
+  CUtensorMap an_attn, an_ffn, attn, act;   // activations: {K, 50} BF16 (an_*: AN_COPIES copies per observation), box {64, 50}; slot rows 50..63 are never written
   CUtensorMap pk, pv;                       // prefix keys / values, full pages: {64, page tokens, 4, L, pages} BF16, box {64, 64, 4, 1, 1}
   CUtensorMap pk_tail, pv_tail;             // the same pool, rows limited to the valid tokens of an observation's last page
   CUtensorMap sk, sv;                       // this layer's suffix keys / values: {64, 50, 4, batch}, same box
@@ -133,6 +137,7 @@ struct Params {
   float* att_part;         // [MAX_KEY_GROUPS - 1][NROW_CTAS][ATT_PART_FLOATS] partial attention results of groups >= 1
   int poll_ns;             // pause between two samples of a stage counter
   int drop_event;          // debug: this event is never signalled (exercises the bounded waits); -1 = none
+  int cta_perm;            // role permutation over the blocks of the grid (see the kernel's first lines)
   int n_units[4];          // units per GEMM kind (event targets)
   float t_steps[NS];
   float dt;

@@ -149,6 +149,37 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// One pipeline stage of the GEMM CTAs in one piece: eight K = 16 MMAs over a 128-k stage (four 32-byte steps in each
+// of the two 64-k operand atoms, which lie a_atom / b_atom descriptor units apart) and the commit that frees the stage.
+template <uint32_t A_ATOM, uint32_t B_ATOM>
+__device__ __forceinline__ void umma_bf16_stage8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate, uint32_t commit_bar) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 a1, a2, a3, a4, a5, a6, a7, b1, b2, b3, b4, b5, b6, b7;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "add.u64 a1, %1, 2;\n add.u64 a2, %1, 4;\n add.u64 a3, %1, 6;\n add.u64 a4, %1, %6;\n"
+      "add.u64 a5, a4, 2;\n add.u64 a6, a4, 4;\n add.u64 a7, a4, 6;\n"
+      "add.u64 b1, %2, 2;\n add.u64 b2, %2, 4;\n add.u64 b3, %2, 6;\n add.u64 b4, %2, %7;\n"
+      "add.u64 b5, b4, 2;\n add.u64 b6, b4, 4;\n add.u64 b7, b4, 6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, 1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, 1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, 1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a4, b4, %3, 1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a5, b5, %3, 1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a6, b6, %3, 1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a7, b7, %3, 1;\n"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(commit_bar),
+        "n"((unsigned long long)A_ATOM), "n"((unsigned long long)B_ATOM) : "memory");
+}
+// One lane of a converged warp (always the same one), for instructions that a single thread must issue while the
+// loop around them stays warp-uniform.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t leader;
+  asm volatile("{\n.reg .pred P;\n.reg .b32 r;\nelect.sync r|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}" : "=r"(leader));
+  return leader != 0;
+}
 // Arrive once on an mbarrier of this CTA when every tcgen05 op issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
