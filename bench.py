@@ -178,6 +178,9 @@ def main() -> int:
     ap.add_argument("--mask", default="full", choices=["full", "pad", "scatter"],
                     help="prefix validity: every token valid, a right-padded prefix, or the same count of valid tokens at "
                          "random places (count uniform in [prefix/2, prefix], from the seed)")
+    ap.add_argument("--kv-pages", type=int, default=0, metavar="TOKENS",
+                    help="hand the prefix cache over as a pool of shuffled pages of this many tokens (a multiple of 64) "
+                         "through the strided / paged view instead of dense tensors")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--stage-times", action="store_true",
                     help="also print (stderr) the in-kernel stage timeline of one L2-flushed chunk")
@@ -206,7 +209,27 @@ def main() -> int:
            for k in FX.ORDER}
     dev = {k: v.to(device) for k, v in cpu.items()}
     arm = Pi05Arm(geo, "b200", str(device), batch=B)
-    arm.bind(dev)
+    pool = None
+    if args.kv_pages:
+        # the same keys / values scattered over a pool of pages (two spare pages, shuffled order)
+        from pi05_megakernel_b200.arm import PagedPrefix
+        T_ = args.kv_pages
+        per = (geo.prefix + T_ - 1) // T_
+        order = torch.randperm(B * per + 2, generator=torch.Generator().manual_seed(11)).tolist()
+        pool = {n: torch.zeros((B * per + 2, geo.layers, T_, 1, 256), dtype=torch.bfloat16) for n in ("prefix_k", "prefix_v")}
+        table = [[order[b * per + lp] for lp in range(per)] for b in range(B)]
+        for n in pool:
+            dense = cpu[n].reshape(B, geo.layers, geo.prefix, 1, 256)
+            for b in range(B):
+                for lp in range(per):
+                    cnt = min(T_, geo.prefix - lp * T_)
+                    pool[n][table[b][lp], :, :cnt] = dense[b, :, lp * T_:lp * T_ + cnt]
+        cpu.update(pool)
+        dev = {k: v.to(device) for k, v in cpu.items()}
+        arm.bind({k: v for k, v in dev.items() if k not in pool},
+                 kv_pages=PagedPrefix(dev["prefix_k"], dev["prefix_v"], table))
+    else:
+        arm.bind(dev)
     l2 = torch.cuda.get_device_properties(device).L2_cache_size
     flush = torch.empty(2 * l2, dtype=torch.uint8, device=device)
     stream = torch.cuda.current_stream(device)
@@ -284,6 +307,7 @@ def main() -> int:
                                    "Gemma-300M expert layers, BF16 weights and prefix K/V, FP32 time MLP / "
                                    "modulation; one persistent kernel launch per chunk",
                        "l2": "flushed before every timed chunk (2x L2 zero fill)",
+                       "prefix_cache": f"pool of shuffled {args.kv_pages}-token pages read in place" if args.kv_pages else "dense",
                        "parallelism": f"dp{world} (independent observations, replicated weights, no collective)",
                        "engine": arm.config},
             "ms_per_chunk": ms_step / B, "ms_per_launch_median": statistics.median(samples), "batch_per_gpu": B,

@@ -9,6 +9,8 @@ atomics, so two launches may differ in the last bit of an accumulator; values de
 earlier launch are therefore compared to one BF16 ulp, not bit for bit.
 """
 import ctypes
+import json
+import os
 
 import pytest
 import torch
@@ -401,3 +403,30 @@ def test_prefix_cache_view_rejects_bad_views():
     with pytest.raises(_lib.EngineError):
         arm.launch()                                                # nothing is bound after a failed bind
     arm.close()
+
+
+def test_plain_cooperative_launch_without_clusters():
+    """The engine launches the grid as clusters of two CTAs when the device takes it that way; the plain cooperative
+    launch (selected here through the tuning variable) must give a result in the band as well."""
+    import subprocess
+    import sys
+    code = (
+        "import json, torch\n"
+        "from oracle import pi05_oracle as O\n"
+        "from pi05_megakernel_b200 import fixture as FX\n"
+        "from pi05_megakernel_b200.arm import Pi05Arm\n"
+        "geo = FX.Geometry(prefix=128)\n"
+        "cpu = FX.make_inputs(geo, FX.SEEDS[2], 'cpu')\n"
+        "arm = Pi05Arm(geo, 'b200-s2-l3', 'cuda')\n"
+        "arm.bind({k: v.cuda() for k, v in cpu.items()})\n"
+        "arm.launch(); arm.status()\n"
+        "got = arm.outputs()['actions'].cpu()\n"
+        "g = O.Geo(prefix=128)\n"
+        "d = O.band(O.chunk(cpu, g, False, arm.steps, arm.layers), got, O.chunk(cpu, g, True, arm.steps, arm.layers))\n"
+        "print(json.dumps({'pass': bool(d['pass']), 'clusters': arm.config.get('clusters_of_2')}))\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PI05_NO_CLUSTER="1", PYTHONPATH=root)
+    out = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    result = json.loads(out.stdout.strip().splitlines()[-1])
+    assert result == {"pass": True, "clusters": False}

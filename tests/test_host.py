@@ -81,3 +81,10 @@ def test_fixture_shapes_and_determinism():
     assert geo.prefix // 2 <= n <= geo.prefix and bool(pad[:n].all()) and not bool(pad[n:].any())
     sc = FX.make_observation(geo, 5, "scatter")["prefix_mask"]
     assert geo.prefix // 2 <= int(sc.sum()) <= geo.prefix
+
+
+def test_bind_view_argument_errors(lib):
+    view = _lib.KvView()
+    ptrs = (ctypes.c_void_p * _lib.NUM_INPUTS)()
+    assert lib.pi05_bind_view(None, ptrs, ctypes.byref(view), 128, 1, None, None, 0) == _lib.ERR_ARGUMENT
+    assert lib.pi05_bind(None, ptrs, 128, 1, None, None, 0) == _lib.ERR_ARGUMENT
