@@ -5,6 +5,10 @@
 //                    are sensitive to every instruction: the production kernel is ~3 % faster without it)
 //   PI05_BATCHED  1: any number of observations per launch; 0: exactly one, and all per-observation pointer
 //                    arithmetic and loops fold away
+//   PI05_GN       observations per MMA (1, 2 or 4): the GEMM CTAs put the activations of GN observations side by
+//                    side on the N side of one MMA (N = 64 * GN), so a weight stage in shared memory is fetched
+//                    once for all of them.  The activation half of a stage grows to GN x 16 KB and the ring keeps
+//                    192 KB: 4 / 3 / 2 stages.  Row CTAs and counters stay per observation.
 #if PI05_TRACE
 #define PI05_MAXSTAGE(p) ((p).max_stage)
 #define PI05_DROP(p) ((p).drop_event)
@@ -20,7 +24,26 @@
 #define PI05_NG(p) 1
 #endif
 
+constexpr int GN = PI05_GN;
+static_assert(GN == 1 || GN == 2 || GN == 4, "observations per MMA");
+static_assert(GN == 1 || PI05_BATCHED, "several observations per MMA only in a batched build");
+constexpr int V_A_ATOM = GN * A_ATOM_BYTES;            // 64 * GN token rows x 64 k: observation g's box at g * A_ATOM_BYTES
+constexpr int V_STAGE_ALL = W_STAGE_BYTES + 2 * V_A_ATOM;
+constexpr int V_NSTG = GN == 1 ? 4 : GN == 2 ? 3 : 2;
+constexpr int V_TMEM_COLS = 2 * 64 * GN;               // two accumulators of 64 * GN columns
+static_assert(V_NSTG * V_STAGE_ALL <= OFF_STAGE && V_NSTG <= NSTG && V_TMEM_COLS <= 512, "ring / TMEM budget");
+#define PI05_NGRP(p) ((PI05_NB(p) + GN - 1) / GN)      // groups of observations that share MMAs
+
 __device__ __constant__ int kGemmStage[4] = {ST_QKV, ST_O, ST_GU, ST_DOWN};
+
+// A schedule entry of a batched build may name the one group of observations it serves: bits 8.. of `gemm` hold
+// group + 1, or 0 for "every group in turn".  Returns the range of groups and strips the field.
+__device__ __forceinline__ void unit_groups(const Params& p, Unit& un, int& g0, int& g1) {
+  if (!PI05_BATCHED) { g0 = 0; g1 = 1; return; }
+  const int g = un.gemm >> 8;
+  un.gemm &= 0xff;
+  if (g == 0) { g0 = 0; g1 = PI05_NGRP(p); } else { g0 = g - 1; g1 = g; }
+}
 
 __device__ __forceinline__ ObsPtrs obs(const Params& p, int b) {
   ObsPtrs o = p.ob;
@@ -864,10 +887,12 @@ __device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units
                                 const Bars& b, Producer& st, uint32_t until, uint64_t policy, bool leader) {
   const int npass = p.n_steps * p.n_layers;
   if (nunits == 0) { st.done = true; return; }
-  const bool once = PI05_NB(p) == 1;     // one observation: every weight byte is used once, mark it evict-first in L2
+  const bool once = PI05_NGRP(p) == 1;   // one group of observations: every weight byte is used once, mark it evict-first in L2
   while (!st.done && st.it < until) {
     if (st.pass >= npass) { st.done = true; break; }
-    const Unit un = units[st.u];
+    Unit un = units[st.u];
+    int ug0, ug1;
+    unit_groups(p, un, ug0, ug1);
     const int stage = stage_of(st.pass, un.gemm);
     if (stage >= PI05_MAXSTAGE(p)) { st.done = true; break; }
     const CUtensorMap *ma, *mb;
@@ -879,7 +904,7 @@ __device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units
     for (; a < un.nk && it < until; ++a, ++it, kc += KSTAGE) {
       if (!wait_mbar(c, b.empty + 8 * slot, par ^ 1, WAIT_W_EMPTY, stage)) { st.done = true; break; }
       const uint32_t full = b.full + 8 * slot;
-      const uint32_t dst = ring + slot * STAGE_BYTES_ALL;
+      const uint32_t dst = ring + slot * V_STAGE_ALL;
       if (!leader) {
       } else if (once) {
         ptx::mbar_expect_tx(full, W_STAGE_BYTES);
@@ -894,12 +919,12 @@ __device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units
         ptx::tma_load_2d(dst + W_ATOM_BYTES, ma, full, kc + KATOM, ra);
         ptx::tma_load_2d(dst + W_ATOM_BYTES + W_ATOM_BYTES / 2, mb, full, kc + KATOM, rbw);
       }
-      if (++slot == NSTG) { slot = 0; par ^= 1; }
+      if (++slot == V_NSTG) { slot = 0; par ^= 1; }
     }
     st.slot = slot; st.par = par; st.it = it; st.a = a;
     if (a >= un.nk) {
       st.a = 0;
-      if (++st.b >= PI05_NB(p)) {        // same unit again for the next observation, then the next unit
+      if (++st.b >= ug1 - ug0) {         // same unit again for the next group of observations, then the next unit
         st.b = 0;
         if (++st.u >= nunits) { st.u = 0; ++st.pass; }
       }
@@ -915,8 +940,10 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
   uint32_t slot = 0, par = 0;
   for (int pass = 0; pass < npass; ++pass) {
     for (int u = 0; u < nunits; ++u)
-    for (int ob = 0; ob < PI05_NB(p); ++ob) {
-      const Unit un = units[u];
+    for (int gi = 0, ug0 = 0, ug1 = 1; gi < ug1 - ug0; ++gi) {   // one group of up to GN observations per round of MMAs
+      Unit un = units[u];
+      unit_groups(p, un, ug0, ug1);
+      const int ob0 = (ug0 + gi) * GN;
       const int stage = stage_of(pass, un.gemm);
       if (stage >= PI05_MAXSTAGE(p)) return;
       const CUtensorMap* m;
@@ -926,25 +953,35 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
       else if (un.gemm == G_O) { m = &p.maps.attn; ev = EV_ATT; target = NROW_CTAS * (pass + 1); }
       else if (un.gemm == G_GU) { m = &p.maps.an_ffn; ev = EV_ANF; target = NROW_CTAS * (pass + 1); }
       else { m = &p.maps.act; ev = EV_GU; target = p.n_units[G_GU] * (pass + 1); }
-      if (!wait_event(c, p.ctrl + EVB(ev, ob), target, stage)) return;
-      if (ob == 0 && leader) trace(p, c.cta, pass, un.gemm, 0);
+      const int nob = GN == 1 ? 1 : min(GN, PI05_NB(p) - ob0);
+      for (int g = 0; g < nob; ++g)
+        if (!wait_event(c, p.ctrl + EVB(ev, ob0 + g), target, stage)) return;
+      if (ob0 == 0 && leader) trace(p, c.cta, pass, un.gemm, 0);
       ptx::fence_proxy_async_global();
-      // first row of this observation's tile: the normalised activations exist in AN_COPIES copies
-      const int row0 = (un.gemm == G_QKV || un.gemm == G_GU) ? (ob * AN_COPIES + c.cta % AN_COPIES) * T : ob * T;
+      // first row of the first observation's tile: the normalised activations exist in AN_COPIES copies
+      const bool copies = un.gemm == G_QKV || un.gemm == G_GU;
+      const int row0 = copies ? (ob0 * AN_COPIES + c.cta % AN_COPIES) * T : ob0 * T;
+      const int rstep = copies ? AN_COPIES * T : T;
       int kc = un.k0 * KSTAGE;
       for (int a = 0; a < un.nk; ++a, kc += KSTAGE) {
         if (!wait_mbar(c, b.empty + 8 * slot, par ^ 1, WAIT_A_EMPTY, stage)) return;
         const uint32_t full = b.full + 8 * slot;
-        const uint32_t dst = ring + slot * STAGE_BYTES_ALL + W_STAGE_BYTES;
+        const uint32_t dst = ring + slot * V_STAGE_ALL + W_STAGE_BYTES;
         if (leader) {
-          ptx::mbar_expect_tx(full, A_STAGE_TX);
-          ptx::tma_load_2d(dst, m, full, kc, row0);
-          ptx::tma_load_2d(dst + A_ATOM_BYTES, m, full, kc + KATOM, row0);
+          // observation g's 50 token rows land in rows 64 g .. of both 64-k atoms; the slots of observations
+          // that a short last group lacks keep stale bytes, which only reach accumulator columns nobody reads
+          ptx::mbar_expect_tx(full, nob * A_STAGE_TX);
+#pragma unroll
+          for (int g = 0; g < GN; ++g)
+            if (g < nob) {
+              ptx::tma_load_2d(dst + g * A_ATOM_BYTES, m, full, kc, row0 + g * rstep);
+              ptx::tma_load_2d(dst + V_A_ATOM + g * A_ATOM_BYTES, m, full, kc + KATOM, row0 + g * rstep);
+            }
           if (PI05_TRACE && p.stamps != nullptr && pass == 1 && c.cta == 0 && un.gemm == G_GU && a < 8) p.stamps[241 + 2 * a] = globaltimer();
         }
-        if (++slot == NSTG) { slot = 0; par ^= 1; }
+        if (++slot == V_NSTG) { slot = 0; par ^= 1; }
       }
-      if (ob == 0 && leader) trace(p, c.cta, pass, un.gemm, 1);
+      if (ob0 == 0 && leader) trace(p, c.cta, pass, un.gemm, 1);
     }
   }
 }
@@ -955,33 +992,34 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
 __device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units, int nunits, uint32_t ring,
                                const Bars& b, uint32_t tmem, bool leader) {
   const int npass = p.n_steps * p.n_layers;
-  const uint32_t idesc = ptx::umma_idesc_bf16(128, 64);
+  const uint32_t idesc = ptx::umma_idesc_bf16(128, 64 * GN);
   const uint64_t adesc0 = ptx::umma_smem_desc(ring), bdesc0 = ptx::umma_smem_desc(ring + W_STAGE_BYTES);
   uint32_t it = 0, uit = 0, slot = 0, par = 0;
   for (int pass = 0; pass < npass; ++pass) {
     for (int u = 0; u < nunits; ++u)
-    for (int ob = 0; ob < PI05_NB(p); ++ob, ++uit) {
-      const Unit un = units[u];
+    for (int gi = 0, ug0 = 0, ug1 = 1; gi < ug1 - ug0; ++gi, ++uit) {
+      Unit un = units[u];
+      unit_groups(p, un, ug0, ug1);
       const int stage = stage_of(pass, un.gemm);
       if (stage >= PI05_MAXSTAGE(p)) return it;
       const uint32_t buf = uit & 1;
       if (!wait_mbar(c, b.tempty + 8 * buf, ((uit >> 1) & 1) ^ 1, WAIT_T_EMPTY, stage)) return it;
       ptx::tc_fence_after();
-      const uint32_t d = tmem + buf * 64;
+      const uint32_t d = tmem + buf * (64 * GN);
       uint32_t accumulate = 0;
       for (int a = 0; a < un.nk; ++a, ++it) {
         if (!wait_mbar(c, b.full + 8 * slot, par, WAIT_W_FULL, stage)) return it;
-        if (a == 0 && ob == 0 && leader) trace(p, c.cta, pass, un.gemm, 2);
+        if (a == 0 && gi == 0 && leader) trace(p, c.cta, pass, un.gemm, 2);
         if (PI05_TRACE && leader && p.stamps != nullptr && pass == 1 && c.cta == 0 && un.gemm == G_GU && a < 8) p.stamps[240 + 2 * a] = globaltimer();
-        const uint64_t ad = adesc0 + (uint64_t)(slot * (STAGE_BYTES_ALL >> 4));
-        const uint64_t bd = bdesc0 + (uint64_t)(slot * (STAGE_BYTES_ALL >> 4));
+        const uint64_t ad = adesc0 + (uint64_t)(slot * (V_STAGE_ALL >> 4));
+        const uint64_t bd = bdesc0 + (uint64_t)(slot * (V_STAGE_ALL >> 4));
         if (leader)
-          ptx::umma_bf16_stage8<(W_ATOM_BYTES >> 4), (A_ATOM_BYTES >> 4)>(d, ad, bd, idesc, accumulate, b.empty + 8 * slot);
+          ptx::umma_bf16_stage8<(W_ATOM_BYTES >> 4), (V_A_ATOM >> 4)>(d, ad, bd, idesc, accumulate, b.empty + 8 * slot);
         accumulate = 1u;
-        if (++slot == NSTG) { slot = 0; par ^= 1; }
+        if (++slot == V_NSTG) { slot = 0; par ^= 1; }
       }
       if (leader) ptx::umma_commit(b.tfull + 8 * buf);
-      if (ob == 0 && leader) trace(p, c.cta, pass, un.gemm, 3);
+      if (gi == 0 && leader) trace(p, c.cta, pass, un.gemm, 3);
     }
   }
   return it;
@@ -997,16 +1035,20 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
   uint32_t uit = 0;
   for (int pass = 0; pass < npass; ++pass) {
     for (int u = 0; u < nunits; ++u)
-    for (int ob = 0; ob < PI05_NB(p); ++ob, ++uit) {
-      const Unit un = units[u];
-      const ObsPtrs o = obs(p, ob);
+    for (int gi = 0, ug0 = 0, ug1 = 1; gi < ug1 - ug0; ++gi, ++uit) {   // one accumulator holds a group of up to GN observations
+      Unit un = units[u];
+      unit_groups(p, un, ug0, ug1);
+      const int ob0 = (ug0 + gi) * GN;
       const int stage = stage_of(pass, un.gemm);
       if (stage >= PI05_MAXSTAGE(p)) return;
       const uint32_t buf = uit & 1;
+      const int nob = GN == 1 ? 1 : min(GN, PI05_NB(p) - ob0);
+      const bool ktile = un.gemm == G_QKV && un.tile >= 16 && un.tile < 18;
       // k tiles: the RoPE table words of this thread's rotary index are fetched now, while the MMAs still run
+      // (with several observations per accumulator: per observation, below)
       uint2 cs[T / 2];
-      if (un.gemm == G_QKV && un.tile >= 16 && un.tile < 18) {
-        const uint2* __restrict__ rope = reinterpret_cast<const uint2*>(o.rope2) + (un.tile - 16) * 64 + (et & 63);
+      if (GN == 1 && ktile) {
+        const uint2* __restrict__ rope = reinterpret_cast<const uint2*>(obs(p, ob0).rope2) + (un.tile - 16) * 64 + (et & 63);
 #pragma unroll
         for (int tp = 0; tp < T / 2; ++tp) cs[tp] = __ldcg(rope + tp * (HD / 2));
       }
@@ -1017,20 +1059,31 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
                      : "=r"(any_fail) : "r"(ok ? 0 : 1) : "memory");
         if (any_fail) return;
       }
-      if (et == 0 && ob == 0) trace(p, c.cta, pass, un.gemm, 4);
+      if (et == 0 && ob0 == 0) trace(p, c.cta, pass, un.gemm, 4);
       ptx::tc_fence_after();
+#pragma unroll 1
+      for (int g = 0; g < nob; ++g) {
+      const int ob = ob0 + g;
+      const ObsPtrs o = obs(p, ob);
+      if (GN > 1 && ktile) {
+        const uint2* __restrict__ rope = reinterpret_cast<const uint2*>(o.rope2) + (un.tile - 16) * 64 + (et & 63);
+#pragma unroll
+        for (int tp = 0; tp < T / 2; ++tp) cs[tp] = __ldcg(rope + tp * (HD / 2));
+      }
       uint32_t r[64];
       {
         uint32_t lo[32], hi[32];
-        const uint32_t taddr = tmem + buf * 64 + ((uint32_t)(ew * 32) << 16);
+        const uint32_t taddr = tmem + buf * (64 * GN) + g * 64 + ((uint32_t)(ew * 32) << 16);
         ptx::tmem_ld_32x32(taddr, lo);
         ptx::tmem_ld_32x32(taddr + 32, hi);
         ptx::tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) { r[i] = lo[i]; r[32 + i] = hi[i]; }
       }
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(b.tempty + 8 * buf);
+      if (g == nob - 1) {      // the accumulator is in registers for every observation of the group
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(b.tempty + 8 * buf);
+      }
       if (et == 0 && ob == 0) trace(p, c.cta, pass, un.gemm, 5);
 
       if (un.gemm == G_QKV && un.tile >= 16) {
@@ -1110,10 +1163,13 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
       if (et == 0 && ob == 0) trace(p, c.cta, pass, un.gemm, 6);
       ptx::named_bar_sync(1, 128);
       if (et == 0) {
+        // one signal per observation as soon as its results are stored (signalling a whole group at once was
+        // measured slower: the first observation's consumers then start later)
         const int ev = un.gemm == G_QKV ? (un.tile >= 16 ? EV_KV : EV_QKV) : un.gemm == G_O ? EV_O : un.gemm == G_GU ? EV_GU : EV_DOWN;
         signal_event(p.ctrl + EVB(ev, ob));
         if (ob == 0) trace(p, c.cta, pass, un.gemm, 7);
       }
+      }   // observations of the group
     }
   }
 }
@@ -1210,6 +1266,12 @@ __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, 
   for (int pass = 0; pass < npass; ++pass) {
     if (pass * NSTAGE + ST_ATT >= PI05_MAXSTAGE(p)) return;
     const bool do_ratt = pass * NSTAGE + ST_RATT < PI05_MAXSTAGE(p);
+    if (PI05_BATCHED && p.row_order == 1) {
+      for (int k = 0; k < nobs; ++k)
+        if (!row_attention(p, c, smem, unit, pass, group + k * G, 0, bars, stamp0)) return;
+      for (int k = 0; k < nobs && do_ratt; ++k)
+        if (!row_residual(p, c, smem, unit, pass, group + k * G, ROW_ATT, hn, stamp0)) return;
+    } else
     for (int k = 0; k <= nobs; ++k) {                   // attention of observation k, residual of observation k - 1
       if (k < nobs && !row_attention(p, c, smem, unit, pass, group + k * G, 0, bars, stamp0)) return;
       if (k >= 1 && do_ratt && !row_residual(p, c, smem, unit, pass, group + (k - 1) * G, ROW_ATT, hn, stamp0)) return;
@@ -1247,13 +1309,13 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
 
   if (tid == 0) {
     s_issued = 0; s_consumed = 0;
-    for (int i = 0; i < NSTG; ++i) { ptx::mbar_init(b.full + 8 * i, 2); ptx::mbar_init(b.empty + 8 * i, 1); }
+    for (int i = 0; i < V_NSTG; ++i) { ptx::mbar_init(b.full + 8 * i, 2); ptx::mbar_init(b.empty + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) { ptx::mbar_init(b.tfull + 8 * i, 1); ptx::mbar_init(b.tempty + 8 * i, 128); }
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_shared();
   }
   if (is_gemm && warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(&s_tmem), TMEM_COLS);
+    ptx::tmem_alloc(ptx::smem_u32(&s_tmem), V_TMEM_COLS);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
@@ -1267,7 +1329,7 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
   const bool leader = ptx::elect_one();     // every warp is converged here
   if (is_gemm && warp == 0) {
     policy = ptx::policy_evict_first();
-    weight_producer(p, c, units, nunits, ring, b, prod, NSTG, policy, leader);
+    weight_producer(p, c, units, nunits, ring, b, prod, V_NSTG, policy, leader);
   }
 
   // ---------------- prologue: tables, time MLP, all modulation rows (FP32 weights streamed once)
@@ -1325,7 +1387,7 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
   __syncthreads();
   if (is_gemm && warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem, TMEM_COLS);
+    ptx::tmem_dealloc(tmem, V_TMEM_COLS);
   }
   if (tid == 0) {
     __threadfence();
@@ -1339,6 +1401,7 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
 }
 
 #undef PI05_NB
+#undef PI05_NGRP
 #undef PI05_NG
 #undef PI05_MAXSTAGE
 #undef PI05_DROP

@@ -35,32 +35,69 @@
 #include "pi05_common.cuh"
 using namespace pi05;
 
-// Three builds of the same device code (see pi05_chunk_kernel.cuh): the production kernel for one observation,
-// the batched kernel, and the traced kernel that serves any batch when the caller asks for stamps.
-namespace k_plain {
+// Five builds of the same device code (see pi05_chunk_kernel.cuh): the production kernel for one observation, the
+// batched kernels with one, two or four observations per MMA, and the traced kernel that serves any batch when the
+// caller asks for stamps or debug controls.
 #ifndef PI05_QF_KEPT
 #define PI05_QF_KEPT 8
 #endif
+namespace k_plain {
 #define PI05_TRACE 0
 #define PI05_BATCHED 0
+#define PI05_GN 1
 #include "pi05_chunk_kernel.cuh"
 #undef PI05_TRACE
 #undef PI05_BATCHED
+#undef PI05_GN
 }  // namespace k_plain
 namespace k_batched {
 #define PI05_TRACE 0
 #define PI05_BATCHED 1
+#define PI05_GN 1
 #include "pi05_chunk_kernel.cuh"
 #undef PI05_TRACE
 #undef PI05_BATCHED
+#undef PI05_GN
 }  // namespace k_batched
+namespace k_pairs {
+#define PI05_TRACE 0
+#define PI05_BATCHED 1
+#define PI05_GN 2
+#include "pi05_chunk_kernel.cuh"
+#undef PI05_TRACE
+#undef PI05_BATCHED
+#undef PI05_GN
+}  // namespace k_pairs
+namespace k_quads {
+#define PI05_TRACE 0
+#define PI05_BATCHED 1
+#define PI05_GN 4
+#include "pi05_chunk_kernel.cuh"
+#undef PI05_TRACE
+#undef PI05_BATCHED
+#undef PI05_GN
+}  // namespace k_quads
 namespace k_traced {
 #define PI05_TRACE 1
 #define PI05_BATCHED 1
+#define PI05_GN 1
 #include "pi05_chunk_kernel.cuh"
 #undef PI05_TRACE
 #undef PI05_BATCHED
+#undef PI05_GN
 }  // namespace k_traced
+
+#ifndef PI05_PAIRS_FROM
+#define PI05_PAIRS_FROM 8       // batch sizes from this one on run two observations per MMA
+#endif
+#ifndef PI05_QUADS_FROM
+#define PI05_QUADS_FROM 1000    // ... and from this one on four
+#endif
+namespace {
+const void* const kAllKernels[] = {(const void*)k_plain::pi05_chunk_kernel, (const void*)k_batched::pi05_chunk_kernel,
+                                   (const void*)k_pairs::pi05_chunk_kernel, (const void*)k_quads::pi05_chunk_kernel,
+                                   (const void*)k_traced::pi05_chunk_kernel};
+}  // namespace
 
 // =========================================================================================== host side
 namespace {
@@ -92,6 +129,9 @@ struct pi05_engine {
   std::vector<int> sched_n;
   int n_units[4] = {0, 0, 0, 0};
   TMaps maps;
+  int obs_per_mma = 0;           // 0: chosen from the batch size at bind; 1 / 2 / 4: forced (tuning knob)
+  int gn = 1;                    // observations per MMA of the bound batch
+  bool balanced = true;          // several observations: the throughput schedule (tuning knob PI05_LATENCY_SCHEDULE: off)
   int max_stage = 0x7fffffff;
   int drop_event = -1;
   int poll_ns = 20;
@@ -180,15 +220,12 @@ Tp* region_ptr(const pi05_engine* h, const char* name) {
 }
 
 // Static work schedule: which CTA runs which 128-row weight tile over which range of 128-wide K stages.
+// One observation (the latency schedule, every entry serves "all groups" = the one there is):
 //   gate/up: 64 tiles (64 gate rows + the matching 64 up rows), full K, one per CTA 0..63
 //   QKV:     16 q tiles x 4 K parts on the gate/up CTAs, 4 k / v tiles x full K on CTAs 64..67
 //   O, down: 8 row tiles each, K split in contiguous runs over all GEMM CTAs (partial sums meet in L2)
-bool build_schedule(pi05_engine* h) {
+bool schedule_one(pi05_engine* h, std::vector<std::vector<Unit>>& per) {
   const int ng = h->n_gemm;
-  if (ng < 64 + 8) return false;
-  h->sched.assign((size_t)h->grid * MAX_UNITS, Unit{0, 0, 0, 0});
-  h->sched_n.assign(h->grid, 0);
-  std::vector<std::vector<Unit>> per(h->grid);
   // QKV: the 4 k / v tiles over the full K on CTAs 64..67 (BF16 keys / values with RoPE straight from the epilogue);
   // the 16 q tiles in 4 two-stage K parts, one on each gate/up CTA (FP32 sums, finished by attention)
   for (int u = 0; u < NKVTILES; ++u) per[64 + u].push_back(Unit{G_QKV, 16 + u, 0, W / KSTAGE});
@@ -205,13 +242,67 @@ bool build_schedule(pi05_engine* h) {
   split(G_O, W / 128, QD / KSTAGE);
   for (int u = 0; u < 64; ++u) per[u].push_back(Unit{G_GU, u, 0, W / KSTAGE});
   split(G_DOWN, W / 128, FF / KSTAGE);
+  return true;
+}
+
+// Several observations (the throughput schedule): every entry names the group of observations it serves, and the
+// entries of each phase (k / v and q, O, gate/up, down) are dealt over ALL GEMM CTAs by load, so that no phase is
+// left to a few CTAs while the others wait (with the latency schedule the k / v tiles of every group would queue on
+// four CTAs and the gate/up tiles on 64).  Every CTA's list is in (phase, group) order, the same global order for
+// all, so whatever an entry waits for is produced by entries that come earlier in that order, or by row CTAs.
+// The K splits get coarser as the number of groups grows (about two entries per CTA and phase): fewer, longer
+// units mean fewer epilogues and atomics.
+bool schedule_groups(pi05_engine* h, std::vector<std::vector<Unit>>& per, int ngroups) {
+  const int ng = h->n_gemm;
+  std::vector<int> total(ng, 0);
+  auto deal = [&](int gemm, int ntiles, int tile0, int stages, int parts, std::vector<int>& load, int grp) {
+    for (int t = 0; t < ntiles; ++t)
+      for (int j = 0; j < parts; ++j) {
+        const int a0 = stages * j / parts, a1 = stages * (j + 1) / parts;
+        if (a1 <= a0) continue;
+        int best = 0;
+        for (int cta = 1; cta < ng; ++cta)
+          if (load[cta] < load[best] || (load[cta] == load[best] && total[cta] < total[best])) best = cta;
+        per[best].push_back(Unit{gemm | ((grp + 1) << 8), tile0 + t, a0, a1 - a0});
+        load[best] += a1 - a0;
+        total[best] += a1 - a0;
+      }
+  };
+  auto parts_for = [&](int ntiles, int stages) {
+    const int want = (2 * ng + ntiles * ngroups / 2) / (ntiles * ngroups);
+    return std::max(1, std::min(stages, want));
+  };
+  const int pq = std::min(4, parts_for(16, W / KSTAGE)), po = parts_for(W / 128, QD / KSTAGE),
+            pd = parts_for(W / 128, FF / KSTAGE);
+  {
+    std::vector<int> load(ng, 0);
+    for (int g = 0; g < ngroups; ++g) {
+      deal(G_QKV, NKVTILES, 16, W / KSTAGE, 1, load, g);    // k / v first: attention waits for them last
+      deal(G_QKV, 16, 0, W / KSTAGE, pq, load, g);
+    }
+  }
+  { std::vector<int> load(ng, 0); for (int g = 0; g < ngroups; ++g) deal(G_O, W / 128, 0, QD / KSTAGE, po, load, g); }
+  { std::vector<int> load(ng, 0); for (int g = 0; g < ngroups; ++g) deal(G_GU, 64, 0, W / KSTAGE, 1, load, g); }
+  { std::vector<int> load(ng, 0); for (int g = 0; g < ngroups; ++g) deal(G_DOWN, W / 128, 0, FF / KSTAGE, pd, load, g); }
+  return true;
+}
+
+bool build_schedule(pi05_engine* h, int ngroups = 1) {
+  const int ng = h->n_gemm;
+  const bool grouped = h->batch > 2 && h->balanced;   // two observations still do best on the latency schedule
+  if (ng < (grouped ? 32 : 64 + 8)) return false;
+  h->sched.assign((size_t)h->grid * MAX_UNITS, Unit{0, 0, 0, 0});
+  h->sched_n.assign(h->grid, 0);
+  std::vector<std::vector<Unit>> per(h->grid);
+  if (!(grouped ? schedule_groups(h, per, ngroups) : schedule_one(h, per))) return false;
   for (int g = 0; g < 4; ++g) h->n_units[g] = 0;
   for (int ctaid = 0; ctaid < h->grid; ++ctaid) {
     if ((int)per[ctaid].size() > MAX_UNITS) return false;
     h->sched_n[ctaid] = (int)per[ctaid].size();
     for (size_t i = 0; i < per[ctaid].size(); ++i) {
-      h->sched[(size_t)ctaid * MAX_UNITS + i] = per[ctaid][i];
-      h->n_units[per[ctaid][i].gemm]++;
+      const Unit& un = per[ctaid][i];
+      h->sched[(size_t)ctaid * MAX_UNITS + i] = un;
+      if ((un.gemm >> 8) <= 1) h->n_units[un.gemm & 0xff]++;   // units per observation: count one group's entries
     }
   }
   return true;
@@ -321,11 +412,15 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   if (!build_schedule(h)) { delete h; return PI05_ERR_UNSUPPORTED; }
   build_layout(h);
   if (const char* e = getenv("PI05_POLL_NS")) h->poll_ns = atoi(e);   // tuning knob, not part of the interface
+  if (const char* e = getenv("PI05_OBS_PER_MMA")) {                   // tuning knob: 1, 2 or 4 observations per MMA
+    const int v = atoi(e);
+    if (v == 1 || v == 2 || v == 4) h->obs_per_mma = v;
+  }
+  if (getenv("PI05_LATENCY_SCHEDULE")) h->balanced = false;          // tuning knob: the one-observation schedule for batches too
   DeviceGuard guard(device);
   if (!guard.ok) { delete h; return PI05_ERR_CUDA; }
   cudaError_t e = cudaSuccess;
-  for (const void* kern : {(const void*)k_plain::pi05_chunk_kernel, (const void*)k_batched::pi05_chunk_kernel,
-                           (const void*)k_traced::pi05_chunk_kernel}) {
+  for (const void* kern : kAllKernels) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) { cudaGetLastError(); delete h; return PI05_ERR_CUDA; }
   }
@@ -338,8 +433,7 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
     // places consecutive blocks on the two SMs of a TPC, which measured ~1 % faster than the plain cooperative
     // launch's placement.  PI05_NO_CLUSTER (a tuning knob) selects the plain launch.
     bool want = (h->grid % 2 == 0) && getenv("PI05_NO_CLUSTER") == nullptr;
-    for (const void* kern : {(const void*)k_plain::pi05_chunk_kernel, (const void*)k_batched::pi05_chunk_kernel,
-                             (const void*)k_traced::pi05_chunk_kernel}) {
+    for (const void* kern : kAllKernels) {
       if (!want) break;
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
@@ -457,11 +551,13 @@ int pi05_bind_view(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], c
     const int chunks = (prefix_len + 63) / 64 + 1;
     int groups = batch >= 8 ? 3 : batch >= 2 ? 2 : (chunks >= 8 ? 3 : chunks >= 6 ? 2 : 1);
     if (const char* kg = getenv("PI05_KEY_GROUPS")) { if (batch == 1) groups = std::max(1, std::min(atoi(kg), (int)MAX_KEY_GROUPS)); }   // tuning knob
-    while (groups > 1 && h->grid - groups * NROW_CTAS < 64 + NKVTILES) --groups;
+    if (const char* rg = getenv("PI05_ROW_GROUPS")) { if (batch > 1) groups = std::max(1, std::min(atoi(rg), 4)); }   // tuning knob
+    while (groups > 1 && h->grid - groups * NROW_CTAS < (batch > 2 && h->balanced ? 32 : 64 + NKVTILES)) --groups;
     h->row_groups = batch > 1 ? groups : 1;
     h->key_groups = batch > 1 ? 1 : groups;
     h->n_gemm = h->grid - groups * NROW_CTAS;
-    if (!build_schedule(h)) { h->last_error = "no schedule for this GPU"; return PI05_ERR_UNSUPPORTED; }
+    h->gn = batch == 1 ? 1 : h->obs_per_mma ? h->obs_per_mma : batch >= PI05_QUADS_FROM ? 4 : batch >= PI05_PAIRS_FROM ? 2 : 1;
+    if (!build_schedule(h, (batch + h->gn - 1) / h->gn)) { h->last_error = "no schedule for this GPU"; return PI05_ERR_UNSUPPORTED; }
   }
   cudaError_t e = cudaMemset(workspace, 0, h->ws_bytes);
   if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(workspace)", e);
@@ -570,16 +666,26 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.poll_ns = h->poll_ns;
   for (int g = 0; g < 4; ++g) p.n_units[g] = h->n_units[g];
   p.cta_perm = h->cta_perm;
+  p.row_order = getenv("PI05_ROW_ORDER") ? atoi(getenv("PI05_ROW_ORDER")) : 0;
   const double dt = -1.0 / NS;
   for (int s = 0; s < NS; ++s) p.t_steps[s] = (float)(1.0 + s * dt);
   p.dt = (float)dt;
   void* args[] = {&p};
   // stamps or a debug control wanted: the traced build; otherwise the build without that code, specialised for
-  // one observation when there is only one
+  // one observation when there is only one, and with two or four observations side by side in every MMA when
+  // there are several (a weight stage in shared memory then serves all of them)
   const bool debug = stamps != nullptr || h->max_stage != 0x7fffffff || h->drop_event >= 0;
+  const int gn = h->gn;
+  if (debug && gn != 1) {   // the traced build runs one observation per MMA; the bound schedule is for groups of gn
+    h->last_error = "stamps and debug controls need one observation per MMA: batch < " + std::to_string(PI05_PAIRS_FROM) +
+                    ", or PI05_OBS_PER_MMA=1 when the engine is created";
+    return PI05_ERR_UNSUPPORTED;
+  }
   const void* kern = debug ? (const void*)k_traced::pi05_chunk_kernel
-                            : h->batch > 1 ? (const void*)k_batched::pi05_chunk_kernel
-                                           : (const void*)k_plain::pi05_chunk_kernel;
+                     : h->batch == 1 ? (const void*)k_plain::pi05_chunk_kernel
+                     : gn == 4 ? (const void*)k_quads::pi05_chunk_kernel
+                     : gn == 2 ? (const void*)k_pairs::pi05_chunk_kernel
+                               : (const void*)k_batched::pi05_chunk_kernel;
   cudaError_t e;
   if (h->clustered) {
     cudaLaunchAttribute attrs[2];

@@ -329,6 +329,30 @@ def test_batched_observations(batch, variant):
     arm.close()
 
 
+@pytest.mark.parametrize("per_mma,batch", [(1, 3), (2, 3), (2, 4), (4, 3), (4, 5), (4, 8)])
+def test_observations_per_mma(per_mma, batch, monkeypatch):
+    """The batched kernels put one, two or four observations side by side in every MMA of the GEMM CTAs (the engine
+    picks two below a batch of four and four from there on; the tuning variable forces a width).  Every width must
+    give every observation a result in the band of its own oracle run, also when the batch does not fill the last
+    group (3 of 4, 5 of 8) and the spare accumulator columns hold whatever the ring held before."""
+    from pi05_megakernel_b200.arm import Pi05Arm
+    monkeypatch.setenv("PI05_OBS_PER_MMA", str(per_mma))
+    geo, ogeo = FX.Geometry(prefix=128), O.Geo(prefix=128)
+    masks = ["scatter", "full", "pad", "full"] * 2
+    stacked, per = FX.make_batch(geo, FX.SEEDS[1], batch, "cpu", masks[:batch])
+    arm = Pi05Arm(geo, "b200-s1-l2", "cuda", batch=batch)
+    arm.bind({k: v.cuda() for k, v in stacked.items()})
+    got = _run(arm)
+    again = _run(arm)
+    arm.close()
+    for b in range(batch):
+        want = O.chunk(per[b], ogeo, False, 1, 2)
+        exact = O.chunk(per[b], ogeo, True, 1, 2)
+        d = O.band(want, got[b], exact)
+        assert d["pass"], (per_mma, b, d)
+    assert float((again - got).abs().max()) <= 2 * (O.ATOL + O.RTOL * float(got.abs().max()))
+
+
 def _pool_from_dense(dense, page_tokens, num_pages, order, token_pad, fill):
     """Scatter a dense cache [B][L][P][1][256] into a pool [pages][L][page_tokens][1][256 + token_pad] (the returned
     view drops the padding) whose unused pages, padding and rows behind the prefix hold `fill`."""
