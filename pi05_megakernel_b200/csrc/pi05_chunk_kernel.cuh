@@ -5,10 +5,11 @@
 //                    are sensitive to every instruction: the production kernel is ~3 % faster without it)
 //   PI05_BATCHED  1: any number of observations per launch; 0: exactly one, and all per-observation pointer
 //                    arithmetic and loops fold away
-//   PI05_GN       observations per MMA (1, 2 or 4): the GEMM CTAs put the activations of GN observations side by
+//   PI05_GN       observations per MMA (1 or 2): the GEMM CTAs put the activations of GN observations side by
 //                    side on the N side of one MMA (N = 64 * GN), so a weight stage in shared memory is fetched
 //                    once for all of them.  The activation half of a stage grows to GN x 16 KB and the ring keeps
-//                    192 KB: 4 / 3 / 2 stages.  Row CTAs and counters stay per observation.
+//                    192 KB: 4 or 3 stages.  Row CTAs and counters stay per observation.  (Four observations per
+//                    MMA leave a ring of two stages and measured slower than two at every batch size.)
 #if PI05_TRACE
 #define PI05_MAXSTAGE(p) ((p).max_stage)
 #define PI05_DROP(p) ((p).drop_event)
@@ -25,11 +26,11 @@
 #endif
 
 constexpr int GN = PI05_GN;
-static_assert(GN == 1 || GN == 2 || GN == 4, "observations per MMA");
+static_assert(GN == 1 || GN == 2, "observations per MMA");
 static_assert(GN == 1 || PI05_BATCHED, "several observations per MMA only in a batched build");
 constexpr int V_A_ATOM = GN * A_ATOM_BYTES;            // 64 * GN token rows x 64 k: observation g's box at g * A_ATOM_BYTES
 constexpr int V_STAGE_ALL = W_STAGE_BYTES + 2 * V_A_ATOM;
-constexpr int V_NSTG = GN == 1 ? 4 : GN == 2 ? 3 : 2;
+constexpr int V_NSTG = GN == 1 ? 4 : 3;
 constexpr int V_TMEM_COLS = 2 * 64 * GN;               // two accumulators of 64 * GN columns
 static_assert(V_NSTG * V_STAGE_ALL <= OFF_STAGE && V_NSTG <= NSTG && V_TMEM_COLS <= 512, "ring / TMEM budget");
 #define PI05_NGRP(p) ((PI05_NB(p) + GN - 1) / GN)      // groups of observations that share MMAs

@@ -35,9 +35,9 @@
 #include "pi05_common.cuh"
 using namespace pi05;
 
-// Five builds of the same device code (see pi05_chunk_kernel.cuh): the production kernel for one observation, the
-// batched kernels with one, two or four observations per MMA, and the traced kernel that serves any batch when the
-// caller asks for stamps or debug controls.
+// Four builds of the same device code (see pi05_chunk_kernel.cuh): the production kernel for one observation, the
+// batched kernels with one or two observations per MMA, and the traced kernel (one observation per MMA) for
+// callers that ask for stamps or debug controls.
 #ifndef PI05_QF_KEPT
 #define PI05_QF_KEPT 8
 #endif
@@ -68,15 +68,6 @@ namespace k_pairs {
 #undef PI05_BATCHED
 #undef PI05_GN
 }  // namespace k_pairs
-namespace k_quads {
-#define PI05_TRACE 0
-#define PI05_BATCHED 1
-#define PI05_GN 4
-#include "pi05_chunk_kernel.cuh"
-#undef PI05_TRACE
-#undef PI05_BATCHED
-#undef PI05_GN
-}  // namespace k_quads
 namespace k_traced {
 #define PI05_TRACE 1
 #define PI05_BATCHED 1
@@ -88,14 +79,11 @@ namespace k_traced {
 }  // namespace k_traced
 
 #ifndef PI05_PAIRS_FROM
-#define PI05_PAIRS_FROM 8       // batch sizes from this one on run two observations per MMA
-#endif
-#ifndef PI05_QUADS_FROM
-#define PI05_QUADS_FROM 1000    // ... and from this one on four
+#define PI05_PAIRS_FROM 9       // batch sizes from this one on run two observations per MMA (measured: equal at 8, 5 % faster at 16)
 #endif
 namespace {
 const void* const kAllKernels[] = {(const void*)k_plain::pi05_chunk_kernel, (const void*)k_batched::pi05_chunk_kernel,
-                                   (const void*)k_pairs::pi05_chunk_kernel, (const void*)k_quads::pi05_chunk_kernel,
+                                   (const void*)k_pairs::pi05_chunk_kernel,
                                    (const void*)k_traced::pi05_chunk_kernel};
 }  // namespace
 
@@ -129,7 +117,7 @@ struct pi05_engine {
   std::vector<int> sched_n;
   int n_units[4] = {0, 0, 0, 0};
   TMaps maps;
-  int obs_per_mma = 0;           // 0: chosen from the batch size at bind; 1 / 2 / 4: forced (tuning knob)
+  int obs_per_mma = 0;           // 0: chosen from the batch size at bind; 1 / 2: forced (tuning knob)
   int gn = 1;                    // observations per MMA of the bound batch
   bool balanced = true;          // several observations: the throughput schedule (tuning knob PI05_LATENCY_SCHEDULE: off)
   int max_stage = 0x7fffffff;
@@ -290,7 +278,7 @@ bool schedule_groups(pi05_engine* h, std::vector<std::vector<Unit>>& per, int ng
 bool build_schedule(pi05_engine* h, int ngroups = 1) {
   const int ng = h->n_gemm;
   const bool grouped = h->batch > 2 && h->balanced;   // two observations still do best on the latency schedule
-  if (ng < (grouped ? 32 : 64 + 8)) return false;
+  if (ng < 64 + 8) return false;
   h->sched.assign((size_t)h->grid * MAX_UNITS, Unit{0, 0, 0, 0});
   h->sched_n.assign(h->grid, 0);
   std::vector<std::vector<Unit>> per(h->grid);
@@ -412,9 +400,9 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   if (!build_schedule(h)) { delete h; return PI05_ERR_UNSUPPORTED; }
   build_layout(h);
   if (const char* e = getenv("PI05_POLL_NS")) h->poll_ns = atoi(e);   // tuning knob, not part of the interface
-  if (const char* e = getenv("PI05_OBS_PER_MMA")) {                   // tuning knob: 1, 2 or 4 observations per MMA
+  if (const char* e = getenv("PI05_OBS_PER_MMA")) {                   // tuning knob: 1 or 2 observations per MMA
     const int v = atoi(e);
-    if (v == 1 || v == 2 || v == 4) h->obs_per_mma = v;
+    if (v == 1 || v == 2) h->obs_per_mma = v;
   }
   if (getenv("PI05_LATENCY_SCHEDULE")) h->balanced = false;          // tuning knob: the one-observation schedule for batches too
   DeviceGuard guard(device);
@@ -551,12 +539,12 @@ int pi05_bind_view(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], c
     const int chunks = (prefix_len + 63) / 64 + 1;
     int groups = batch >= 8 ? 3 : batch >= 2 ? 2 : (chunks >= 8 ? 3 : chunks >= 6 ? 2 : 1);
     if (const char* kg = getenv("PI05_KEY_GROUPS")) { if (batch == 1) groups = std::max(1, std::min(atoi(kg), (int)MAX_KEY_GROUPS)); }   // tuning knob
-    if (const char* rg = getenv("PI05_ROW_GROUPS")) { if (batch > 1) groups = std::max(1, std::min(atoi(rg), 4)); }   // tuning knob
-    while (groups > 1 && h->grid - groups * NROW_CTAS < (batch > 2 && h->balanced ? 32 : 64 + NKVTILES)) --groups;
+    if (const char* rg = getenv("PI05_ROW_GROUPS")) { if (batch > 1) groups = std::max(1, std::min(atoi(rg), 3)); }   // tuning knob
+    while (groups > 1 && h->grid - groups * NROW_CTAS < 64 + NKVTILES) --groups;
     h->row_groups = batch > 1 ? groups : 1;
     h->key_groups = batch > 1 ? 1 : groups;
     h->n_gemm = h->grid - groups * NROW_CTAS;
-    h->gn = batch == 1 ? 1 : h->obs_per_mma ? h->obs_per_mma : batch >= PI05_QUADS_FROM ? 4 : batch >= PI05_PAIRS_FROM ? 2 : 1;
+    h->gn = batch == 1 ? 1 : h->obs_per_mma ? h->obs_per_mma : batch >= PI05_PAIRS_FROM ? 2 : 1;
     if (!build_schedule(h, (batch + h->gn - 1) / h->gn)) { h->last_error = "no schedule for this GPU"; return PI05_ERR_UNSUPPORTED; }
   }
   cudaError_t e = cudaMemset(workspace, 0, h->ws_bytes);
@@ -666,7 +654,9 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.poll_ns = h->poll_ns;
   for (int g = 0; g < 4; ++g) p.n_units[g] = h->n_units[g];
   p.cta_perm = h->cta_perm;
-  p.row_order = getenv("PI05_ROW_ORDER") ? atoi(getenv("PI05_ROW_ORDER")) : 0;
+  // the throughput schedule runs the O units of every group before any gate/up unit, so the row CTAs do all their
+  // attentions first; the latency schedule interleaves the residual of one observation with the attention of the next
+  p.row_order = h->batch > 2 && h->balanced ? 1 : 0;
   const double dt = -1.0 / NS;
   for (int s = 0; s < NS; ++s) p.t_steps[s] = (float)(1.0 + s * dt);
   p.dt = (float)dt;
@@ -683,7 +673,6 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   }
   const void* kern = debug ? (const void*)k_traced::pi05_chunk_kernel
                      : h->batch == 1 ? (const void*)k_plain::pi05_chunk_kernel
-                     : gn == 4 ? (const void*)k_quads::pi05_chunk_kernel
                      : gn == 2 ? (const void*)k_pairs::pi05_chunk_kernel
                                : (const void*)k_batched::pi05_chunk_kernel;
   cudaError_t e;
