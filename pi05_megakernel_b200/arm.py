@@ -141,6 +141,8 @@ class Pi05Arm:
             tensors += [kv_pages.k, kv_pages.v]
             del keep
         self.tensors = tensors
+        # the engine chooses its schedule when it knows the batch: record what it chose
+        self.config.update(json.loads(self.lib.pi05_config_json(self.handle).decode()))
 
     def refresh_weights(self) -> None:
         _lib.check(self.lib, self.handle, self.lib.pi05_refresh(self.handle))

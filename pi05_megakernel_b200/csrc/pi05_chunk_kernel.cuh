@@ -38,13 +38,17 @@ static_assert(V_NSTG * V_STAGE_ALL <= OFF_STAGE && V_NSTG <= NSTG && V_TMEM_COLS
 __device__ __constant__ int kGemmStage[4] = {ST_QKV, ST_O, ST_GU, ST_DOWN};
 
 // A schedule entry of a batched build may name the one group of observations it serves: bits 8.. of `gemm` hold
-// group + 1, or 0 for "every group in turn".  Returns the range of groups and strips the field.
-__device__ __forceinline__ void unit_groups(const Params& p, Unit& un, int& g0, int& g1) {
-  if (!PI05_BATCHED) { g0 = 0; g1 = 1; return; }
-  const int g = un.gemm >> 8;
-  un.gemm &= 0xff;
+// group + 1, or 0 for "every group in turn".  Returns the range of groups, strips the fields, and returns the entry's
+// lag: with the two-stream schedule a CTA's list describes one CYCLE, in which the entries of stream B's gate/up and
+// down phases belong to the layer pass before the cycle's (lag 1), and there is one cycle more than layer passes.
+__device__ __forceinline__ int unit_groups(const Params& p, Unit& un, int& g0, int& g1) {
+  if (!PI05_BATCHED) { g0 = 0; g1 = 1; return 0; }
+  const int g = un.gemm >> 8, lag = (un.gemm >> 7) & 1;
+  un.gemm &= 0x7f;
   if (g == 0) { g0 = 0; g1 = PI05_NGRP(p); } else { g0 = g - 1; g1 = g; }
+  return lag;
 }
+#define PI05_CYCLES(p, npass) ((npass) + ((PI05_BATCHED && (p).stream_split > 0) ? 1 : 0))
 
 __device__ __forceinline__ ObsPtrs obs(const Params& p, int b) {
   ObsPtrs o = p.ob;
@@ -890,15 +894,19 @@ __device__ void weight_producer(const Params& p, const Ctx& c, const Unit* units
   if (nunits == 0) { st.done = true; return; }
   const bool once = PI05_NGRP(p) == 1;   // one group of observations: every weight byte is used once, mark it evict-first in L2
   while (!st.done && st.it < until) {
-    if (st.pass >= npass) { st.done = true; break; }
+    if (st.pass >= PI05_CYCLES(p, npass)) { st.done = true; break; }   // st.pass counts cycles
     Unit un = units[st.u];
     int ug0, ug1;
-    unit_groups(p, un, ug0, ug1);
-    const int stage = stage_of(st.pass, un.gemm);
+    const int pass = st.pass - unit_groups(p, un, ug0, ug1);
+    if (PI05_BATCHED && (pass < 0 || pass >= npass)) {      // the entry has no layer pass in this cycle
+      if (++st.u >= nunits) { st.u = 0; ++st.pass; }
+      continue;
+    }
+    const int stage = stage_of(pass, un.gemm);
     if (stage >= PI05_MAXSTAGE(p)) { st.done = true; break; }
     const CUtensorMap *ma, *mb;
     int ra, rbw;
-    weight_rows(p, un, st.pass % p.n_layers, ma, mb, ra, rbw);
+    weight_rows(p, un, pass % p.n_layers, ma, mb, ra, rbw);
     int kc = (un.k0 + st.a) * KSTAGE;
     uint32_t slot = st.slot, par = st.par, it = st.it;
     int a = st.a;
@@ -939,11 +947,12 @@ __device__ void act_producer(const Params& p, const Ctx& c, const Unit* units, i
                              bool leader) {
   const int npass = p.n_steps * p.n_layers;
   uint32_t slot = 0, par = 0;
-  for (int pass = 0; pass < npass; ++pass) {
+  for (int cyc = 0; cyc < PI05_CYCLES(p, npass); ++cyc) {
     for (int u = 0; u < nunits; ++u)
     for (int gi = 0, ug0 = 0, ug1 = 1; gi < ug1 - ug0; ++gi) {   // one group of up to GN observations per round of MMAs
       Unit un = units[u];
-      unit_groups(p, un, ug0, ug1);
+      const int pass = cyc - unit_groups(p, un, ug0, ug1);
+      if (PI05_BATCHED && (pass < 0 || pass >= npass)) break;    // the entry has no layer pass in this cycle
       const int ob0 = (ug0 + gi) * GN;
       const int stage = stage_of(pass, un.gemm);
       if (stage >= PI05_MAXSTAGE(p)) return;
@@ -996,11 +1005,12 @@ __device__ uint32_t mma_issuer(const Params& p, const Ctx& c, const Unit* units,
   const uint32_t idesc = ptx::umma_idesc_bf16(128, 64 * GN);
   const uint64_t adesc0 = ptx::umma_smem_desc(ring), bdesc0 = ptx::umma_smem_desc(ring + W_STAGE_BYTES);
   uint32_t it = 0, uit = 0, slot = 0, par = 0;
-  for (int pass = 0; pass < npass; ++pass) {
+  for (int cyc = 0; cyc < PI05_CYCLES(p, npass); ++cyc) {
     for (int u = 0; u < nunits; ++u)
     for (int gi = 0, ug0 = 0, ug1 = 1; gi < ug1 - ug0; ++gi, ++uit) {
       Unit un = units[u];
-      unit_groups(p, un, ug0, ug1);
+      const int pass = cyc - unit_groups(p, un, ug0, ug1);
+      if (PI05_BATCHED && (pass < 0 || pass >= npass)) break;    // the entry has no layer pass in this cycle
       const int stage = stage_of(pass, un.gemm);
       if (stage >= PI05_MAXSTAGE(p)) return it;
       const uint32_t buf = uit & 1;
@@ -1034,11 +1044,12 @@ __device__ void epilogue(const Params& p, const Ctx& c, const Unit* units, int n
   const int ew = et >> 5;                    // TMEM lane quadrant of this warp (warp index % 4)
   __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + OFF_STAGE);
   uint32_t uit = 0;
-  for (int pass = 0; pass < npass; ++pass) {
+  for (int cyc = 0; cyc < PI05_CYCLES(p, npass); ++cyc) {
     for (int u = 0; u < nunits; ++u)
     for (int gi = 0, ug0 = 0, ug1 = 1; gi < ug1 - ug0; ++gi, ++uit) {   // one accumulator holds a group of up to GN observations
       Unit un = units[u];
-      unit_groups(p, un, ug0, ug1);
+      const int pass = cyc - unit_groups(p, un, ug0, ug1);
+      if (PI05_BATCHED && (pass < 0 || pass >= npass)) break;    // the entry has no layer pass in this cycle
       const int ob0 = (ug0 + gi) * GN;
       const int stage = stage_of(pass, un.gemm);
       if (stage >= PI05_MAXSTAGE(p)) return;
@@ -1264,6 +1275,26 @@ __device__ void row_cta(const Params& p, const Ctx& c, uint8_t* smem, int unit, 
   }
   const bool stamp0 = PI05_TRACE && p.stamps != nullptr && unit == 0 && group == 0 && threadIdx.x == 0;
   const int nobs = (PI05_NB(p) - group + G - 1) / G;       // observations of this group
+  if (PI05_BATCHED && p.stream_split > 0) {
+    // Two-stream schedule.  The GEMM CTAs run, cycle after cycle, q(A) gate/up(B, pass before) O(A) down(B, pass before)
+    // gate/up(A) q(B) down(A) O(B): between a phase and the one that depends on it through row CTAs there is always a
+    // phase of the other stream.  The row CTAs follow in the order in which those phases feed them.
+    // op: 0 attention(A) 1 first residual(A) 2 second residual(B, pass before) 3 attention(B) 4 second residual(A)
+    //     5 first residual(B)
+    for (int cyc = 0; cyc <= npass; ++cyc)
+      for (int op = 0; op < 6; ++op) {
+        const int stream = (0x2c >> op) & 1;                        // ops 2, 3, 5 serve stream B
+        const int pass = op == 2 ? cyc - 1 : cyc;
+        if (pass < 0 || pass >= npass) continue;
+        for (int k = 0; k < nobs; ++k) {
+          const int ob = group + k * G;
+          if (((ob / GN < p.stream_split) ? 0 : 1) != stream) continue;
+          if (op == 0 || op == 3) { if (!row_attention(p, c, smem, unit, pass, ob, 0, bars, false)) return; }
+          else if (!row_residual(p, c, smem, unit, pass, ob, (op == 1 || op == 5) ? ROW_ATT : ROW_FFN, hn, false)) return;
+        }
+      }
+    return;
+  }
   for (int pass = 0; pass < npass; ++pass) {
     if (pass * NSTAGE + ST_ATT >= PI05_MAXSTAGE(p)) return;
     const bool do_ratt = pass * NSTAGE + ST_RATT < PI05_MAXSTAGE(p);
@@ -1403,6 +1434,7 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
 
 #undef PI05_NB
 #undef PI05_NGRP
+#undef PI05_CYCLES
 #undef PI05_NG
 #undef PI05_MAXSTAGE
 #undef PI05_DROP

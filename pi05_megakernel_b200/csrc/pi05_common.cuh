@@ -90,7 +90,9 @@ constexpr int CTRL_BYTES = 128 * (1 + NEVENTS * MAXB);
 enum { WAIT_W_EMPTY = 1, WAIT_W_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_T_EMPTY, WAIT_T_FULL, WAIT_EVENT,
        WAIT_DRAIN };
 
-struct Unit { int gemm, tile, k0, nk; };   // gemm: kind in bits 0..7; batched schedules: group of observations + 1 above (0: all)
+// gemm: kind in bits 0..6; batched schedules: bit 7 = the entry belongs to the layer pass before the cycle's (two-stream
+// schedule), bits 8.. = group of observations + 1 (0: every group in turn)
+struct Unit { int gemm, tile, k0, nk; };
 constexpr int MAX_UNITS = 32;              // schedule entries per CTA and layer pass
 constexpr long long DRAIN_CYCLES = 400000;          // exit-time grace period for TMA loads still in flight after an abort
 
@@ -137,6 +139,7 @@ struct Params {
   float* att_part;         // [MAX_KEY_GROUPS - 1][NROW_CTAS][ATT_PART_FLOATS] partial attention results of groups >= 1
   int poll_ns;             // pause between two samples of a stage counter
   int drop_event;          // debug: this event is never signalled (exercises the bounded waits); -1 = none
+  int stream_split;        // two-stream schedule: groups below this index form stream A, the rest stream B (0: one stream)
   int row_order;           // several observations: 0 = attention of one, then the residual of the one before; 1 = all attentions first
   int cta_perm;            // role permutation over the blocks of the grid (see the kernel's first lines)
   int n_units[4];          // units per GEMM kind (event targets)

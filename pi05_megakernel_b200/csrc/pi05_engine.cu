@@ -79,7 +79,10 @@ namespace k_traced {
 }  // namespace k_traced
 
 #ifndef PI05_PAIRS_FROM
-#define PI05_PAIRS_FROM 9       // batch sizes from this one on run two observations per MMA (measured: equal at 8, 5 % faster at 16)
+// Batch sizes from this one on run two observations per MMA.  Beyond the largest batch: with the two-stream schedule
+// one observation per MMA is faster at every batch size measured (B = 16: 18.8 against 19.4 ms per launch), so pairs
+// only run when the tuning variable PI05_OBS_PER_MMA asks for them.
+#define PI05_PAIRS_FROM 1000
 #endif
 namespace {
 const void* const kAllKernels[] = {(const void*)k_plain::pi05_chunk_kernel, (const void*)k_batched::pi05_chunk_kernel,
@@ -119,6 +122,8 @@ struct pi05_engine {
   TMaps maps;
   int obs_per_mma = 0;           // 0: chosen from the batch size at bind; 1 / 2: forced (tuning knob)
   int gn = 1;                    // observations per MMA of the bound batch
+  bool two_streams = true;       // throughput schedule as two streams of groups half a pass apart (tuning knob PI05_ONE_STREAM: off)
+  int stream_split = 0;          // groups in the first stream (0: one stream)
   bool balanced = true;          // several observations: the throughput schedule (tuning knob PI05_LATENCY_SCHEDULE: off)
   int max_stage = 0x7fffffff;
   int drop_event = -1;
@@ -243,41 +248,67 @@ bool schedule_one(pi05_engine* h, std::vector<std::vector<Unit>>& per) {
 bool schedule_groups(pi05_engine* h, std::vector<std::vector<Unit>>& per, int ngroups) {
   const int ng = h->n_gemm;
   std::vector<int> total(ng, 0);
-  auto deal = [&](int gemm, int ntiles, int tile0, int stages, int parts, std::vector<int>& load, int grp) {
-    for (int t = 0; t < ntiles; ++t)
-      for (int j = 0; j < parts; ++j) {
-        const int a0 = stages * j / parts, a1 = stages * (j + 1) / parts;
-        if (a1 <= a0) continue;
-        int best = 0;
-        for (int cta = 1; cta < ng; ++cta)
-          if (load[cta] < load[best] || (load[cta] == load[best] && total[cta] < total[best])) best = cta;
-        per[best].push_back(Unit{gemm | ((grp + 1) << 8), tile0 + t, a0, a1 - a0});
-        load[best] += a1 - a0;
-        total[best] += a1 - a0;
-      }
+  // deal the entries of one phase for groups [g0, g1) over the CTAs, least loaded (in this phase, then overall) first
+  auto deal = [&](int gemm, int ntiles, int tile0, int stages, int parts, std::vector<int>& load, int g0, int g1, int lag) {
+    for (int g = g0; g < g1; ++g)
+      for (int t = 0; t < ntiles; ++t)
+        for (int j = 0; j < parts; ++j) {
+          const int a0 = stages * j / parts, a1 = stages * (j + 1) / parts;
+          if (a1 <= a0) continue;
+          int best = 0;
+          for (int cta = 1; cta < ng; ++cta)
+            if (load[cta] < load[best] || (load[cta] == load[best] && total[cta] < total[best])) best = cta;
+          per[best].push_back(Unit{gemm | (lag << 7) | ((g + 1) << 8), tile0 + t, a0, a1 - a0});
+          load[best] += a1 - a0;
+          total[best] += a1 - a0;
+        }
   };
+  // K parts per tile: about two entries per CTA and phase.  Every group gets the same split (the event targets count
+  // units per observation), so with two streams the larger one decides.
+  const int phase_groups = h->stream_split > 0 ? h->stream_split : ngroups;
   auto parts_for = [&](int ntiles, int stages) {
-    const int want = (2 * ng + ntiles * ngroups / 2) / (ntiles * ngroups);
+    const int want = (2 * ng + ntiles * phase_groups / 2) / (ntiles * phase_groups);
     return std::max(1, std::min(stages, want));
   };
-  const int pq = std::min(4, parts_for(16, W / KSTAGE)), po = parts_for(W / 128, QD / KSTAGE),
-            pd = parts_for(W / 128, FF / KSTAGE);
-  {
+  auto phase_qkv = [&](int g0, int g1) {
     std::vector<int> load(ng, 0);
-    for (int g = 0; g < ngroups; ++g) {
-      deal(G_QKV, NKVTILES, 16, W / KSTAGE, 1, load, g);    // k / v first: attention waits for them last
-      deal(G_QKV, 16, 0, W / KSTAGE, pq, load, g);
+    const int pq = std::min(4, parts_for(16, W / KSTAGE));
+    for (int g = g0; g < g1; ++g) {
+      deal(G_QKV, NKVTILES, 16, W / KSTAGE, 1, load, g, g + 1, 0);    // k / v first: attention waits for them last
+      deal(G_QKV, 16, 0, W / KSTAGE, pq, load, g, g + 1, 0);
     }
+  };
+  auto phase = [&](int gemm, int g0, int g1, int lag) {
+    std::vector<int> load(ng, 0);
+    if (gemm == G_O) deal(G_O, W / 128, 0, QD / KSTAGE, parts_for(W / 128, QD / KSTAGE), load, g0, g1, lag);
+    else if (gemm == G_GU) deal(G_GU, 64, 0, W / KSTAGE, 1, load, g0, g1, lag);
+    else deal(G_DOWN, W / 128, 0, FF / KSTAGE, parts_for(W / 128, FF / KSTAGE), load, g0, g1, lag);
+  };
+  const int na = h->stream_split;
+  if (na > 0) {
+    // two streams of groups, A = [0, na) and B = [na, ngroups), half a layer pass apart (see row_cta in the kernel)
+    phase_qkv(0, na);
+    phase(G_GU, na, ngroups, 1);
+    phase(G_O, 0, na, 0);
+    phase(G_DOWN, na, ngroups, 1);
+    phase(G_GU, 0, na, 0);
+    phase_qkv(na, ngroups);
+    phase(G_DOWN, 0, na, 0);
+    phase(G_O, na, ngroups, 0);
+  } else {
+    phase_qkv(0, ngroups);
+    phase(G_O, 0, ngroups, 0);
+    phase(G_GU, 0, ngroups, 0);
+    phase(G_DOWN, 0, ngroups, 0);
   }
-  { std::vector<int> load(ng, 0); for (int g = 0; g < ngroups; ++g) deal(G_O, W / 128, 0, QD / KSTAGE, po, load, g); }
-  { std::vector<int> load(ng, 0); for (int g = 0; g < ngroups; ++g) deal(G_GU, 64, 0, W / KSTAGE, 1, load, g); }
-  { std::vector<int> load(ng, 0); for (int g = 0; g < ngroups; ++g) deal(G_DOWN, W / 128, 0, FF / KSTAGE, pd, load, g); }
   return true;
 }
 
 bool build_schedule(pi05_engine* h, int ngroups = 1) {
   const int ng = h->n_gemm;
   const bool grouped = h->batch > 2 && h->balanced;   // two observations still do best on the latency schedule
+  // two streams of groups half a layer pass apart pay from five observations on (measured; below that they cost 1-2 %)
+  h->stream_split = grouped && h->two_streams && h->batch >= 5 && ngroups >= 2 ? (ngroups + 1) / 2 : 0;
   if (ng < 64 + 8) return false;
   h->sched.assign((size_t)h->grid * MAX_UNITS, Unit{0, 0, 0, 0});
   h->sched_n.assign(h->grid, 0);
@@ -290,7 +321,7 @@ bool build_schedule(pi05_engine* h, int ngroups = 1) {
     for (size_t i = 0; i < per[ctaid].size(); ++i) {
       const Unit& un = per[ctaid][i];
       h->sched[(size_t)ctaid * MAX_UNITS + i] = un;
-      if ((un.gemm >> 8) <= 1) h->n_units[un.gemm & 0xff]++;   // units per observation: count one group's entries
+      if ((un.gemm >> 8) <= 1) h->n_units[un.gemm & 0x7f]++;   // units per observation: count one group's entries
     }
   }
   return true;
@@ -353,6 +384,25 @@ int encode_suffix_kv(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t 
   return PI05_OK;
 }
 
+// The engine's description for the caller's records: geometry of the launch and the schedule of the bound batch.
+void describe(pi05_engine* h) {
+  char buf[1280];
+  const bool grouped = h->batch > 2 && h->balanced;
+  snprintf(buf, sizeof buf,
+           "{\"kernel\": \"pi05_chunk_kernel\", \"arch\": \"sm_100a\", \"launches_per_chunk\": 1, \"grid\": %d, "
+           "\"threads\": %d, \"smem_bytes\": %d, \"gemm_ctas\": %d, \"row_ctas\": %d, \"stages\": %d, "
+           "\"stage_bytes\": %d, \"units\": {\"qkv\": %d, \"o\": %d, \"gate_up\": %d, \"down\": %d}, "
+           "\"mma\": \"tcgen05 cta_group::1 M128 N%d K16 bf16\", \"sync\": \"device-scope counters, bounded waits\", "
+           "\"clusters_of_2\": %s, \"observations_per_mma\": %d, \"schedule\": \"%s\"}",
+           h->grid, THREADS, SMEM_BYTES, h->n_gemm, h->grid - h->n_gemm, h->gn == 1 ? NSTG : 3,
+           W_STAGE_BYTES + h->gn * A_STAGE_BYTES, h->n_units[0], h->n_units[1], h->n_units[2], h->n_units[3], 64 * h->gn,
+           h->clustered ? "true" : "false", h->gn,
+           !grouped ? "one observation (units serve every observation in turn)"
+                    : h->stream_split > 0 ? "throughput, two streams of groups half a layer pass apart"
+                                          : "throughput, one stream");
+  h->config = buf;
+}
+
 bool valid_handle(pi05_handle_t h) { return h != nullptr; }
 
 }  // namespace
@@ -404,6 +454,7 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
     const int v = atoi(e);
     if (v == 1 || v == 2) h->obs_per_mma = v;
   }
+  if (getenv("PI05_ONE_STREAM")) h->two_streams = false;             // tuning knob
   if (getenv("PI05_LATENCY_SCHEDULE")) h->balanced = false;          // tuning knob: the one-observation schedule for batches too
   DeviceGuard guard(device);
   if (!guard.ok) { delete h; return PI05_ERR_CUDA; }
@@ -439,15 +490,7 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
     h->clustered = want;
     if (const char* pm = getenv("PI05_CTA_PERM")) h->cta_perm = atoi(pm) != 0 && h->grid % 2 == 0;   // tuning knob
   }
-  char buf[1024];
-  snprintf(buf, sizeof buf,
-           "{\"kernel\": \"pi05_chunk_kernel\", \"arch\": \"sm_100a\", \"launches_per_chunk\": 1, \"grid\": %d, "
-           "\"threads\": %d, \"smem_bytes\": %d, \"gemm_ctas\": %d, \"row_ctas\": %d, \"stages\": %d, "
-           "\"stage_bytes\": %d, \"units\": {\"qkv\": %d, \"o\": %d, \"gate_up\": %d, \"down\": %d}, "
-           "\"mma\": \"tcgen05 cta_group::1 M128 N64 K16 bf16\", \"sync\": \"device-scope counters, bounded waits\", \"clusters_of_2\": %s}",
-           h->grid, THREADS, SMEM_BYTES, h->n_gemm, NROW_CTAS, NSTG, STAGE_BYTES_ALL, h->n_units[0], h->n_units[1], h->n_units[2],
-           h->n_units[3], h->clustered ? "true" : "false");
-  h->config = buf;
+  describe(h);
   *out = h;
   return PI05_OK;
 }
@@ -546,6 +589,7 @@ int pi05_bind_view(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], c
     h->n_gemm = h->grid - groups * NROW_CTAS;
     h->gn = batch == 1 ? 1 : h->obs_per_mma ? h->obs_per_mma : batch >= PI05_PAIRS_FROM ? 2 : 1;
     if (!build_schedule(h, (batch + h->gn - 1) / h->gn)) { h->last_error = "no schedule for this GPU"; return PI05_ERR_UNSUPPORTED; }
+    describe(h);
   }
   cudaError_t e = cudaMemset(workspace, 0, h->ws_bytes);
   if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(workspace)", e);
@@ -657,6 +701,7 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   // the throughput schedule runs the O units of every group before any gate/up unit, so the row CTAs do all their
   // attentions first; the latency schedule interleaves the residual of one observation with the attention of the next
   p.row_order = h->batch > 2 && h->balanced ? 1 : 0;
+  p.stream_split = h->stream_split;
   const double dt = -1.0 / NS;
   for (int s = 0; s < NS; ++s) p.t_steps[s] = (float)(1.0 + s * dt);
   p.dt = (float)dt;
@@ -666,9 +711,12 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   // there are several (a weight stage in shared memory then serves all of them)
   const bool debug = stamps != nullptr || h->max_stage != 0x7fffffff || h->drop_event >= 0;
   const int gn = h->gn;
+  if (debug && h->stream_split > 0 && (h->max_stage != 0x7fffffff)) {
+    h->last_error = "the stage limit is not available with the two-stream schedule of a batch (create the engine with PI05_ONE_STREAM set)";
+    return PI05_ERR_UNSUPPORTED;
+  }
   if (debug && gn != 1) {   // the traced build runs one observation per MMA; the bound schedule is for groups of gn
-    h->last_error = "stamps and debug controls need one observation per MMA: batch < " + std::to_string(PI05_PAIRS_FROM) +
-                    ", or PI05_OBS_PER_MMA=1 when the engine is created";
+    h->last_error = "stamps and debug controls need one observation per MMA (PI05_OBS_PER_MMA unset or 1 when the engine is created)";
     return PI05_ERR_UNSUPPORTED;
   }
   const void* kern = debug ? (const void*)k_traced::pi05_chunk_kernel

@@ -329,13 +329,14 @@ def test_batched_observations(batch, variant):
     arm.close()
 
 
-@pytest.mark.parametrize("per_mma,batch", [(1, 3), (1, 8), (2, 2), (2, 3), (2, 8)])
+@pytest.mark.parametrize("per_mma,batch", [(1, 3), (1, 5), (1, 8), (2, 2), (2, 3), (2, 7)])
 def test_observations_per_mma(per_mma, batch, monkeypatch):
-    """The batched kernels put one or two observations side by side in every MMA of the GEMM CTAs (the engine picks
-    two from a batch of nine on; the tuning variable forces a width), and from three observations on the schedule
-    names, entry by entry, the group of observations it serves.  Every combination must give every observation a
-    result in the band of its own oracle run, also when the batch does not fill the last group (3 of 4) and the
-    spare accumulator columns hold whatever the ring held before."""
+    """The batched kernels put one or two observations side by side in every MMA of the GEMM CTAs (two only when the
+    tuning variable asks for it), from three observations on the schedule names, entry by entry, the group of
+    observations it serves, and from five on the groups form two streams half a layer pass apart.  Every combination
+    must give every observation a result in the band of its own oracle run, also when the batch does not fill the last
+    group (3 of 4, 7 of 8), when the two streams have different numbers of groups (5, 7), and with the spare
+    accumulator columns holding whatever the ring held before."""
     from pi05_megakernel_b200.arm import Pi05Arm
     monkeypatch.setenv("PI05_OBS_PER_MMA", str(per_mma))
     geo, ogeo = FX.Geometry(prefix=128), O.Geo(prefix=128)
