@@ -139,6 +139,20 @@ int pi05_debug(pi05_handle_t h, int max_stage, long long wait_limit_cycles, int 
 /* Replaces build_config() (mk/pi05_mk.cu:3632-3656): a JSON object describing the build and the schedule. */
 const char* pi05_config_json(pi05_handle_t h);
 
+/* The work schedule the engine would bind for `batch` observations of `prefix_len` prefix tokens on a GPU of `sms`
+ * SMs, computed on the host without touching a device (the reference's schedule is compiled into its kernel,
+ * mk/pi05_mk.cu:2420-2470, and has no such query; this one exists so that the schedule's invariants can be tested
+ * without a GPU).  Writes up to `capacity` entries of PI05_PLAN_ENTRY ints, in the order the CTAs execute them:
+ * {cta, gemm (0 QKV, 1 O, 2 gate/up, 3 down), lag (1: the entry belongs to the layer pass before the cycle's),
+ * group of observations (-1: every group in turn), tile, first 128-k stage, number of stages}; and info =
+ * {GEMM CTAs, row-CTA groups, key groups, observations per MMA, groups of observations, groups in the first of two
+ * streams (0: one stream), units per observation of QKV, O, gate/up, down}.  *count receives the number of entries
+ * there are, which may exceed capacity.  The tuning variables of the environment apply as in pi05_create. */
+#define PI05_PLAN_ENTRY 7
+#define PI05_PLAN_INFO 10
+int pi05_schedule_plan(int sms, int batch, int prefix_len, int* entries, int capacity, int* count,
+                       int info[PI05_PLAN_INFO]);
+
 /* Number of kernel launches issued by this handle since creation (one per pi05_launch). */
 int pi05_launch_count(pi05_handle_t h, unsigned long long* count);
 

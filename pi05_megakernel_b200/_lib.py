@@ -15,6 +15,7 @@ NUM_INPUTS = 25
 NUM_STAMPS = 256
 STATIC_SCRATCH_BYTES = 12 << 20
 STATIC_MAX_PREFIX = 1024
+PLAN_ENTRY, PLAN_INFO = 7, 10
 
 EVENT_ATTENTION_DONE, EVENT_FFN_NORM_READY = 7, 9
 WAIT_EVENT = 7
@@ -49,6 +50,8 @@ SIGNATURES = {
     "pi05_error_string": (_c.c_char_p, [_c.c_int]),
     "pi05_last_error": (_c.c_char_p, [_c.c_void_p]),
     "pi05_destroy": (_c.c_int, [_c.c_void_p]),
+    "pi05_schedule_plan": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_int), _c.c_int,
+                                      _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
     "pi05_chunk_static": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_void_p), _c.c_int, _c.c_void_p, _c.c_int, _c.c_int,
                                      _c.c_void_p]),
 }
@@ -82,3 +85,22 @@ def check(lib, handle, rc: int) -> None:
     if rc != OK:
         detail = lib.pi05_last_error(handle).decode() if handle else ""
         raise EngineError(rc, lib.pi05_error_string(rc).decode() + (f" ({detail})" if detail else ""))
+
+
+def schedule_plan(sms: int, batch: int, prefix: int) -> tuple[list[tuple[int, ...]], dict]:
+    """The work schedule the engine would bind on a GPU of ``sms`` SMs (host arithmetic only, no GPU needed):
+    entries ``(cta, gemm, lag, group, tile, k0, nk)`` in execution order per CTA, and the plan's summary."""
+    lib = load()
+    count, info = _c.c_int(), (_c.c_int * PLAN_INFO)()
+    rc = lib.pi05_schedule_plan(sms, batch, prefix, None, 0, _c.byref(count), info)
+    if rc != OK:
+        raise EngineError(rc, lib.pi05_error_string(rc).decode())
+    buf = (_c.c_int * (count.value * PLAN_ENTRY))()
+    rc = lib.pi05_schedule_plan(sms, batch, prefix, buf, count.value, _c.byref(count), info)
+    if rc != OK:
+        raise EngineError(rc, lib.pi05_error_string(rc).decode())
+    entries = [tuple(buf[i * PLAN_ENTRY:(i + 1) * PLAN_ENTRY]) for i in range(count.value)]
+    names = ("gemm_ctas", "row_groups", "key_groups", "obs_per_mma", "groups", "stream_split")
+    summary = dict(zip(names, info[:6]))
+    summary["units"] = dict(zip(("qkv", "o", "gate_up", "down"), info[6:10]))
+    return entries, summary

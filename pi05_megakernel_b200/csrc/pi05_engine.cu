@@ -384,6 +384,36 @@ int encode_suffix_kv(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t 
   return PI05_OK;
 }
 
+// Tuning variables (environment, read once per engine; not part of the interface).
+void read_knobs(pi05_engine* h) {
+  if (const char* e = getenv("PI05_POLL_NS")) h->poll_ns = atoi(e);
+  if (const char* e = getenv("PI05_OBS_PER_MMA")) {                   // tuning knob: 1 or 2 observations per MMA
+    const int v = atoi(e);
+    if (v == 1 || v == 2) h->obs_per_mma = v;
+  }
+  if (getenv("PI05_ONE_STREAM")) h->two_streams = false;             // tuning knob
+  if (getenv("PI05_LATENCY_SCHEDULE")) h->balanced = false;          // tuning knob: the one-observation schedule for batches too
+}
+
+// Everything the engine decides when it learns the batch and the prefix length: groups of row CTAs (or of keys),
+// GEMM CTAs, observations per MMA, and the schedule.  Pure host arithmetic.
+bool plan_batch(pi05_engine* h, int batch, int prefix_len) {
+  h->batch = batch;
+  // More observations keep more row CTAs busy: one group of 25 per observation in flight, as long as the GEMM
+  // side keeps its 64 gate/up CTAs plus the 4 k / v CTAs.
+  // One observation with a long prefix uses the extra groups differently: they split the keys of each attention.
+  const int chunks = (prefix_len + 63) / 64 + 1;
+  int groups = batch >= 8 ? 3 : batch >= 2 ? 2 : (chunks >= 8 ? 3 : chunks >= 6 ? 2 : 1);
+  if (const char* kg = getenv("PI05_KEY_GROUPS")) { if (batch == 1) groups = std::max(1, std::min(atoi(kg), (int)MAX_KEY_GROUPS)); }   // tuning knob
+  if (const char* rg = getenv("PI05_ROW_GROUPS")) { if (batch > 1) groups = std::max(1, std::min(atoi(rg), 3)); }   // tuning knob
+  while (groups > 1 && h->grid - groups * NROW_CTAS < 64 + NKVTILES) --groups;
+  h->row_groups = batch > 1 ? groups : 1;
+  h->key_groups = batch > 1 ? 1 : groups;
+  h->n_gemm = h->grid - groups * NROW_CTAS;
+  h->gn = batch == 1 ? 1 : h->obs_per_mma ? h->obs_per_mma : batch >= PI05_PAIRS_FROM ? 2 : 1;
+  return build_schedule(h, (batch + h->gn - 1) / h->gn);
+}
+
 // The engine's description for the caller's records: geometry of the launch and the schedule of the bound batch.
 void describe(pi05_engine* h) {
   char buf[1280];
@@ -449,13 +479,7 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   h->max_batch = max_batch;
   if (!build_schedule(h)) { delete h; return PI05_ERR_UNSUPPORTED; }
   build_layout(h);
-  if (const char* e = getenv("PI05_POLL_NS")) h->poll_ns = atoi(e);   // tuning knob, not part of the interface
-  if (const char* e = getenv("PI05_OBS_PER_MMA")) {                   // tuning knob: 1 or 2 observations per MMA
-    const int v = atoi(e);
-    if (v == 1 || v == 2) h->obs_per_mma = v;
-  }
-  if (getenv("PI05_ONE_STREAM")) h->two_streams = false;             // tuning knob
-  if (getenv("PI05_LATENCY_SCHEDULE")) h->balanced = false;          // tuning knob: the one-observation schedule for batches too
+  read_knobs(h);
   DeviceGuard guard(device);
   if (!guard.ok) { delete h; return PI05_ERR_CUDA; }
   cudaError_t e = cudaSuccess;
@@ -575,22 +599,8 @@ int pi05_bind_view(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], c
   h->ws = static_cast<uint8_t*>(workspace);
   h->prefix = prefix_len;
   h->batch = batch;
-  {
-    // More observations keep more row CTAs busy: one group of 25 per observation in flight, as long as the GEMM
-    // side keeps its 64 gate/up CTAs plus the 4 k / v CTAs.
-    // One observation with a long prefix uses the extra groups differently: they split the keys of each attention.
-    const int chunks = (prefix_len + 63) / 64 + 1;
-    int groups = batch >= 8 ? 3 : batch >= 2 ? 2 : (chunks >= 8 ? 3 : chunks >= 6 ? 2 : 1);
-    if (const char* kg = getenv("PI05_KEY_GROUPS")) { if (batch == 1) groups = std::max(1, std::min(atoi(kg), (int)MAX_KEY_GROUPS)); }   // tuning knob
-    if (const char* rg = getenv("PI05_ROW_GROUPS")) { if (batch > 1) groups = std::max(1, std::min(atoi(rg), 3)); }   // tuning knob
-    while (groups > 1 && h->grid - groups * NROW_CTAS < 64 + NKVTILES) --groups;
-    h->row_groups = batch > 1 ? groups : 1;
-    h->key_groups = batch > 1 ? 1 : groups;
-    h->n_gemm = h->grid - groups * NROW_CTAS;
-    h->gn = batch == 1 ? 1 : h->obs_per_mma ? h->obs_per_mma : batch >= PI05_PAIRS_FROM ? 2 : 1;
-    if (!build_schedule(h, (batch + h->gn - 1) / h->gn)) { h->last_error = "no schedule for this GPU"; return PI05_ERR_UNSUPPORTED; }
-    describe(h);
-  }
+  if (!plan_batch(h, batch, prefix_len)) { h->last_error = "no schedule for this GPU"; return PI05_ERR_UNSUPPORTED; }
+  describe(h);
   cudaError_t e = cudaMemset(workspace, 0, h->ws_bytes);
   if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(workspace)", e);
   e = cudaMemcpy(region_ptr<void>(h, "sched"), h->sched.data(), h->sched.size() * sizeof(Unit), cudaMemcpyHostToDevice);
@@ -769,6 +779,32 @@ int pi05_workspace_region(pi05_handle_t h, const char* name, size_t* offset, siz
   if (!r) return PI05_ERR_ARGUMENT;
   *offset = r->off;
   *bytes = r->bytes;
+  return PI05_OK;
+}
+
+int pi05_schedule_plan(int sms, int batch, int prefix_len, int* entries, int capacity, int* count,
+                       int info[PI05_PLAN_INFO]) {
+  if (sms < 1 || sms > 1024 || batch < 1 || batch > MAXB || prefix_len < 1 || capacity < 0 || (capacity > 0 && !entries) ||
+      !count || !info)
+    return PI05_ERR_ARGUMENT;
+  pi05_engine h;                 // host-side state only: nothing here touches a device
+  h.grid = sms;
+  h.n_gemm = sms - NROW_CTAS;
+  read_knobs(&h);
+  if (h.n_gemm < 1 || !plan_batch(&h, batch, prefix_len)) return PI05_ERR_UNSUPPORTED;
+  info[0] = h.n_gemm; info[1] = h.row_groups; info[2] = h.key_groups; info[3] = h.gn;
+  info[4] = (batch + h.gn - 1) / h.gn; info[5] = h.stream_split;
+  for (int g = 0; g < 4; ++g) info[6 + g] = h.n_units[g];
+  int n = 0;
+  for (int cta = 0; cta < h.grid; ++cta)
+    for (int i = 0; i < h.sched_n[cta]; ++i, ++n) {
+      if (n >= capacity) continue;           // keep counting: *count says how many there are
+      const Unit& un = h.sched[(size_t)cta * MAX_UNITS + i];
+      int* e = entries + (size_t)n * PI05_PLAN_ENTRY;
+      e[0] = cta; e[1] = un.gemm & 0x7f; e[2] = (un.gemm >> 7) & 1; e[3] = (un.gemm >> 8) - 1;
+      e[4] = un.tile; e[5] = un.k0; e[6] = un.nk;
+    }
+  *count = n;
   return PI05_OK;
 }
 

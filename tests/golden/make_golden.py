@@ -133,7 +133,7 @@ SMALL = {
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of garv901/pi05-megakernel (its top-level directory)")
     ap.add_argument("--skip-full", action="store_true")
     args = ap.parse_args()
     torch.manual_seed(0)

@@ -88,3 +88,71 @@ def test_bind_view_argument_errors(lib):
     ptrs = (ctypes.c_void_p * _lib.NUM_INPUTS)()
     assert lib.pi05_bind_view(None, ptrs, ctypes.byref(view), 128, 1, None, None, 0) == _lib.ERR_ARGUMENT
     assert lib.pi05_bind(None, ptrs, 128, 1, None, None, 0) == _lib.ERR_ARGUMENT
+
+
+STAGES = {0: 8, 1: 16, 2: 8, 3: 32}          # 128-k stages of the full K of QKV, O, gate/up, down
+TILES = {0: 20, 1: 8, 2: 64, 3: 8}           # 128-row weight tiles (QKV: 16 q + 2 k + 2 v)
+
+
+@pytest.mark.parametrize("batch,prefix", [(1, 128), (1, 968), (2, 128), (3, 128), (4, 128), (5, 128), (7, 128),
+                                          (8, 128), (12, 128), (16, 128)])
+def test_schedule_plan_invariants(lib, batch, prefix, monkeypatch):
+    """The work schedule of the GEMM CTAs on a 148-SM part, computed on the host.  Whatever the batch: every
+    (GEMM, group of observations, tile) is covered over its whole K exactly once; the units per observation that
+    the stage counters wait for are the same for every group; no row CTA appears; and with named groups every
+    CTA's list follows one global order (cycle position, then group), which is what rules out circular waits."""
+    for name in ("PI05_OBS_PER_MMA", "PI05_LATENCY_SCHEDULE", "PI05_ONE_STREAM", "PI05_ROW_GROUPS", "PI05_KEY_GROUPS"):
+        monkeypatch.delenv(name, raising=False)
+    entries, plan = _lib.schedule_plan(148, batch, prefix)
+    ngroups = plan["groups"]
+    assert ngroups == (batch + plan["obs_per_mma"] - 1) // plan["obs_per_mma"]
+    assert plan["gemm_ctas"] == 148 - 25 * max(plan["row_groups"], plan["key_groups"])
+    cover: dict = {}
+    per_cta: dict = {}
+    for cta, gemm, lag, group, tile, k0, nk in entries:
+        assert 0 <= cta < plan["gemm_ctas"] and nk >= 1 and 0 <= tile < TILES[gemm]
+        groups = range(ngroups) if group < 0 else [group]
+        for g in groups:
+            cover.setdefault((gemm, g, tile), []).append((k0, nk))
+        per_cta.setdefault(cta, []).append((gemm, lag, group))
+    for gemm in range(4):
+        for g in range(ngroups):
+            units = 0
+            for tile in range(TILES[gemm]):
+                runs = sorted(cover[(gemm, g, tile)])
+                units += len(runs)
+                pos = 0
+                for k0, nk in runs:                       # contiguous, no overlap, whole K
+                    assert k0 == pos
+                    pos += nk
+                assert pos == STAGES[gemm]
+            assert units == list(plan["units"].values())[gemm]
+    assert max(len(v) for v in per_cta.values()) <= 32
+    if batch >= 5:
+        assert plan["stream_split"] == (ngroups + 1) // 2
+    named = [e for e in entries if e[3] >= 0]
+    assert bool(named) == (batch >= 3)
+    if named:
+        split = plan["stream_split"]
+
+        def position(gemm, lag, group):
+            if not split:
+                return (gemm, group)
+            b = group >= split
+            assert lag == (1 if b and gemm >= 2 else 0)
+            # q(A) gate/up(B) O(A) down(B) gate/up(A) q(B) down(A) O(B)
+            order = {(0, False): 0, (2, True): 1, (1, False): 2, (3, True): 3, (2, False): 4, (0, True): 5,
+                     (3, False): 6, (1, True): 7}
+            return (order[(gemm, b)], group)
+        for cta, lst in per_cta.items():
+            keys = [position(*e) for e in lst]
+            assert keys == sorted(keys), (cta, lst)
+
+
+def test_schedule_plan_argument_errors(lib):
+    count, info = ctypes.c_int(), (ctypes.c_int * _lib.PLAN_INFO)()
+    assert lib.pi05_schedule_plan(148, 0, 128, None, 0, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
+    assert lib.pi05_schedule_plan(148, 17, 128, None, 0, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
+    assert lib.pi05_schedule_plan(148, 1, 128, None, 4, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
+    assert lib.pi05_schedule_plan(148, 1, 128, None, 0, None, info) == _lib.ERR_ARGUMENT
+    assert lib.pi05_schedule_plan(60, 1, 128, None, 0, ctypes.byref(count), info) == _lib.ERR_UNSUPPORTED
