@@ -511,9 +511,6 @@ __device__ void row_op(const Params& p, const ObsPtrs& o, uint8_t* smem, int uni
 // staged in shared memory in 64-key chunks, three chunks (192 keys) at a time; with a prefix of 128 that is
 // everything, in one pass.  Scores: bf16(q.k) / 16, masked; running max; p = bf16(exp(s - m)); o += p V (FP32);
 // out = bf16(o / sum exp).
-// q / k / v leave the QKV GEMM as FP32 split-K sums.  The row CTAs finish them while staging them for attention:
-// round to BF16 (the GEMM's output rounding), then RoPE on q and k with every product and the sum rounded to BF16
-// (reference/pi05.py:218-229: x * cos + rotate_half(x) * sin on BF16 tensors), written as BF16 rows of 528 B.
 // q leaves the QKV GEMM as FP32 split-K sums.  The row CTA finishes its 16 query rows while staging them: round to
 // BF16 (the GEMM's output rounding), then RoPE with every product and the sum rounded to BF16
 // (reference/pi05.py:218-229: x * cos + rotate_half(x) * sin on BF16 tensors).  One item of 8 rotary pairs per thread.
