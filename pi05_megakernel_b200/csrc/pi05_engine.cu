@@ -122,6 +122,7 @@ struct pi05_engine {
   TMaps maps;
   int obs_per_mma = 0;           // 0: chosen from the batch size at bind; 1 / 2: forced (tuning knob)
   int gn = 1;                    // observations per MMA of the bound batch
+  int grouped_from = 3, streams_from = 5;   // batch sizes from which the throughput schedule / its two streams are used (tuning knobs)
   bool two_streams = true;       // throughput schedule as two streams of groups half a pass apart (tuning knob PI05_ONE_STREAM: off)
   int stream_split = 0;          // groups in the first stream (0: one stream)
   bool balanced = true;          // several observations: the throughput schedule (tuning knob PI05_LATENCY_SCHEDULE: off)
@@ -306,9 +307,9 @@ bool schedule_groups(pi05_engine* h, std::vector<std::vector<Unit>>& per, int ng
 
 bool build_schedule(pi05_engine* h, int ngroups = 1) {
   const int ng = h->n_gemm;
-  const bool grouped = h->batch > 2 && h->balanced;   // two observations still do best on the latency schedule
+  const bool grouped = h->batch >= h->grouped_from && h->balanced;   // two observations still do best on the latency schedule
   // two streams of groups half a layer pass apart pay from five observations on (measured; below that they cost 1-2 %)
-  h->stream_split = grouped && h->two_streams && h->batch >= 5 && ngroups >= 2 ? (ngroups + 1) / 2 : 0;
+  h->stream_split = grouped && h->two_streams && h->batch >= h->streams_from && ngroups >= 2 ? (ngroups + 1) / 2 : 0;
   if (ng < 64 + 8) return false;
   h->sched.assign((size_t)h->grid * MAX_UNITS, Unit{0, 0, 0, 0});
   h->sched_n.assign(h->grid, 0);
@@ -392,6 +393,8 @@ void read_knobs(pi05_engine* h) {
     if (v == 1 || v == 2) h->obs_per_mma = v;
   }
   if (getenv("PI05_ONE_STREAM")) h->two_streams = false;             // tuning knob
+  if (const char* e = getenv("PI05_GROUPED_FROM")) h->grouped_from = std::max(2, atoi(e));   // tuning knob
+  if (const char* e = getenv("PI05_STREAMS_FROM")) h->streams_from = std::max(2, atoi(e));   // tuning knob
   if (getenv("PI05_LATENCY_SCHEDULE")) h->balanced = false;          // tuning knob: the one-observation schedule for batches too
 }
 
@@ -417,7 +420,7 @@ bool plan_batch(pi05_engine* h, int batch, int prefix_len) {
 // The engine's description for the caller's records: geometry of the launch and the schedule of the bound batch.
 void describe(pi05_engine* h) {
   char buf[1280];
-  const bool grouped = h->batch > 2 && h->balanced;
+  const bool grouped = h->batch >= h->grouped_from && h->balanced;
   snprintf(buf, sizeof buf,
            "{\"kernel\": \"pi05_chunk_kernel\", \"arch\": \"sm_100a\", \"launches_per_chunk\": 1, \"grid\": %d, "
            "\"threads\": %d, \"smem_bytes\": %d, \"gemm_ctas\": %d, \"row_ctas\": %d, \"stages\": %d, "
@@ -710,7 +713,7 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.cta_perm = h->cta_perm;
   // the throughput schedule runs the O units of every group before any gate/up unit, so the row CTAs do all their
   // attentions first; the latency schedule interleaves the residual of one observation with the attention of the next
-  p.row_order = h->batch > 2 && h->balanced ? 1 : 0;
+  p.row_order = h->batch >= h->grouped_from && h->balanced ? 1 : 0;
   p.stream_split = h->stream_split;
   const double dt = -1.0 / NS;
   for (int s = 0; s < NS; ++s) p.t_steps[s] = (float)(1.0 + s * dt);
