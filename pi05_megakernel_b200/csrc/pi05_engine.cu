@@ -406,7 +406,8 @@ bool plan_batch(pi05_engine* h, int batch, int prefix_len) {
   // side keeps its 64 gate/up CTAs plus the 4 k / v CTAs.
   // One observation with a long prefix uses the extra groups differently: they split the keys of each attention.
   const int chunks = (prefix_len + 63) / 64 + 1;
-  int groups = batch >= 8 ? 3 : batch >= 2 ? 2 : (chunks >= 8 ? 3 : chunks >= 6 ? 2 : 1);
+  // (measured with the two-stream schedule: three groups beat two by 5-11 % at B = 5..7 and lose 4 % at B = 4)
+  int groups = batch >= 5 ? 3 : batch >= 2 ? 2 : (chunks >= 8 ? 3 : chunks >= 6 ? 2 : 1);
   if (const char* kg = getenv("PI05_KEY_GROUPS")) { if (batch == 1) groups = std::max(1, std::min(atoi(kg), (int)MAX_KEY_GROUPS)); }   // tuning knob
   if (const char* rg = getenv("PI05_ROW_GROUPS")) { if (batch > 1) groups = std::max(1, std::min(atoi(rg), 3)); }   // tuning knob
   while (groups > 1 && h->grid - groups * NROW_CTAS < 64 + NKVTILES) --groups;
