@@ -46,12 +46,15 @@ def measured_peaks() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
-def ncu_traffic() -> float | None:
-    """DRAM bytes per launch from the committed ncu summary (None until one exists)."""
+def ncu_traffic(batch: int, prefix: int) -> float | None:
+    """DRAM bytes per launch from the committed ncu summary of this workload (None where none was captured)."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(path):
         with open(path) as f:
-            return json.load(f).get("dram_bytes_per_launch")
+            for rec in json.load(f).get("captures", []):
+                # a capture of another build of the kernel than the one this run launches is not this run's traffic
+                if rec.get("batch") == batch and rec.get("prefix") == prefix and rec.get("matches_default_build"):
+                    return rec.get("dram_bytes_per_launch")
     return None
 
 
@@ -320,7 +323,7 @@ def main() -> int:
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                          "frac": achieved / peak_gbs, "peak_kind": peak_kind,
-                         "algorithmic_bytes_per_launch": alg_bytes, "traffic": ncu_traffic()},
+                         "algorithmic_bytes_per_launch": alg_bytes, "traffic": ncu_traffic(B, geo.prefix)},
         }
         if world == 1 and B == 1 and not args.no_cpu_baseline:
             cps, cores = cpu_chunks_per_sec(geo, cpu, 5)

@@ -37,7 +37,6 @@ constexpr int STAGE_BYTES_ALL = W_STAGE_BYTES + A_STAGE_BYTES;   // 48 KB: weigh
 constexpr int NSTG = 4;            // pipeline depth (192 KB)
 constexpr int STAGE_STRIDE = 72;   // BF16 elements per row of the epilogue exchange buffer (144 B)
 constexpr int STAGE_BYTES = 128 * STAGE_STRIDE * 2;
-constexpr int TMEM_COLS = 128;     // two 64-column accumulators
 
 constexpr int OFF_RING = 0;
 constexpr int OFF_STAGE = OFF_RING + NSTG * STAGE_BYTES_ALL;   // epilogue exchange buffer; also the prologue's scratch
