@@ -122,6 +122,7 @@ struct pi05_engine {
   TMaps maps;
   int obs_per_mma = 0;           // 0: chosen from the batch size at bind; 1 / 2: forced (tuning knob)
   int gn = 1;                    // observations per MMA of the bound batch
+  int entries_per_phase = 2;     // throughput schedule: K splits aim at this many entries per CTA and phase (tuning knob)
   int grouped_from = 3, streams_from = 5;   // batch sizes from which the throughput schedule / its two streams are used (tuning knobs)
   bool two_streams = true;       // throughput schedule as two streams of groups half a pass apart (tuning knob PI05_ONE_STREAM: off)
   int stream_split = 0;          // groups in the first stream (0: one stream)
@@ -268,7 +269,7 @@ bool schedule_groups(pi05_engine* h, std::vector<std::vector<Unit>>& per, int ng
   // units per observation), so with two streams the larger one decides.
   const int phase_groups = h->stream_split > 0 ? h->stream_split : ngroups;
   auto parts_for = [&](int ntiles, int stages) {
-    const int want = (2 * ng + ntiles * phase_groups / 2) / (ntiles * phase_groups);
+    const int want = (h->entries_per_phase * ng + ntiles * phase_groups / 2) / (ntiles * phase_groups);
     return std::max(1, std::min(stages, want));
   };
   auto phase_qkv = [&](int g0, int g1) {
@@ -393,6 +394,7 @@ void read_knobs(pi05_engine* h) {
     if (v == 1 || v == 2) h->obs_per_mma = v;
   }
   if (getenv("PI05_ONE_STREAM")) h->two_streams = false;             // tuning knob
+  if (const char* e = getenv("PI05_ENTRIES_PER_PHASE")) h->entries_per_phase = std::max(1, std::min(atoi(e), 8));   // tuning knob
   if (const char* e = getenv("PI05_GROUPED_FROM")) h->grouped_from = std::max(2, atoi(e));   // tuning knob
   if (const char* e = getenv("PI05_STREAMS_FROM")) h->streams_from = std::max(2, atoi(e));   // tuning knob
   if (getenv("PI05_LATENCY_SCHEDULE")) h->balanced = false;          // tuning knob: the one-observation schedule for batches too
