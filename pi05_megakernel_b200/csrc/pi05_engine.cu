@@ -122,7 +122,7 @@ struct pi05_engine {
   TMaps maps;
   int obs_per_mma = 0;           // 0: chosen from the batch size at bind; 1 / 2: forced (tuning knob)
   int gn = 1;                    // observations per MMA of the bound batch
-  int entries_per_phase = 2;     // throughput schedule: K splits aim at this many entries per CTA and phase (tuning knob)
+  int entries_per_phase = 0;     // throughput schedule: K splits aim at this many entries per CTA and phase (0: by batch size; tuning knob)
   int grouped_from = 3, streams_from = 5;   // batch sizes from which the throughput schedule / its two streams are used (tuning knobs)
   bool two_streams = true;       // throughput schedule as two streams of groups half a pass apart (tuning knob PI05_ONE_STREAM: off)
   int stream_split = 0;          // groups in the first stream (0: one stream)
@@ -265,11 +265,14 @@ bool schedule_groups(pi05_engine* h, std::vector<std::vector<Unit>>& per, int ng
           total[best] += a1 - a0;
         }
   };
-  // K parts per tile: about two entries per CTA and phase.  Every group gets the same split (the event targets count
+  // K parts per tile: one or two entries per CTA and phase.  Every group gets the same split (the event targets count
   // units per observation), so with two streams the larger one decides.
   const int phase_groups = h->stream_split > 0 ? h->stream_split : ngroups;
+  // entries per CTA and phase to aim for: one from eight observations on (measured: B = 8 11.0 against 11.8 ms, B = 16
+  // 18.7 against 18.9), two below
+  const int per_phase = h->entries_per_phase > 0 ? h->entries_per_phase : h->batch >= 8 ? 1 : 2;
   auto parts_for = [&](int ntiles, int stages) {
-    const int want = (h->entries_per_phase * ng + ntiles * phase_groups / 2) / (ntiles * phase_groups);
+    const int want = (per_phase * ng + ntiles * phase_groups / 2) / (ntiles * phase_groups);
     return std::max(1, std::min(stages, want));
   };
   auto phase_qkv = [&](int g0, int g1) {
