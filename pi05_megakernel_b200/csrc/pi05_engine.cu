@@ -268,8 +268,8 @@ bool schedule_groups(pi05_engine* h, std::vector<std::vector<Unit>>& per, int ng
   // K parts per tile: one or two entries per CTA and phase.  Every group gets the same split (the event targets count
   // units per observation), so with two streams the larger one decides.
   const int phase_groups = h->stream_split > 0 ? h->stream_split : ngroups;
-  // entries per CTA and phase to aim for: one from eight observations on (measured: B = 8 11.0 against 11.8 ms, B = 16
-  // 18.7 against 18.9), two below
+  // entries per CTA and phase to aim for: one from eight observations on (measured: B = 8 11.0 against 11.8 ms per
+  // launch; at B = 16 both give the same splits once O and down keep two parts), two below
   const int per_phase = h->entries_per_phase > 0 ? h->entries_per_phase : h->batch >= 8 ? 1 : 2;
   auto parts_for = [&](int ntiles, int stages) {
     const int want = (per_phase * ng + ntiles * phase_groups / 2) / (ntiles * phase_groups);
@@ -285,9 +285,11 @@ bool schedule_groups(pi05_engine* h, std::vector<std::vector<Unit>>& per, int ng
   };
   auto phase = [&](int gemm, int g0, int g1, int lag) {
     std::vector<int> load(ng, 0);
-    if (gemm == G_O) deal(G_O, W / 128, 0, QD / KSTAGE, parts_for(W / 128, QD / KSTAGE), load, g0, g1, lag);
+    // O and down keep at least two K parts per tile: 16- and 32-stage units would leave most CTAs without work in
+    // these phases (8 tiles per group)
+    if (gemm == G_O) deal(G_O, W / 128, 0, QD / KSTAGE, std::max(2, parts_for(W / 128, QD / KSTAGE)), load, g0, g1, lag);
     else if (gemm == G_GU) deal(G_GU, 64, 0, W / KSTAGE, 1, load, g0, g1, lag);
-    else deal(G_DOWN, W / 128, 0, FF / KSTAGE, parts_for(W / 128, FF / KSTAGE), load, g0, g1, lag);
+    else deal(G_DOWN, W / 128, 0, FF / KSTAGE, std::max(2, parts_for(W / 128, FF / KSTAGE)), load, g0, g1, lag);
   };
   const int na = h->stream_split;
   if (na > 0) {
