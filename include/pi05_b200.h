@@ -140,8 +140,8 @@ int pi05_debug(pi05_handle_t h, int max_stage, long long wait_limit_cycles, int 
 const char* pi05_config_json(pi05_handle_t h);
 
 /* The work schedule the engine would bind for `batch` observations of `prefix_len` prefix tokens on a GPU of `sms`
- * SMs, computed on the host without touching a device (the reference's schedule is compiled into its kernel,
- * mk/pi05_mk.cu:2420-2470, and has no such query; this one exists so that the schedule's invariants can be tested
+ * SMs, computed on the host without touching a device (the reference derives each block's K chunk and
+ * tiles from blockIdx inside its GEMM phases, mk/pi05_mk.cu:736-743, and has no such query; this one exists so that the schedule's invariants can be tested
  * without a GPU).  Writes up to `capacity` entries of PI05_PLAN_ENTRY ints, in the order the CTAs execute them:
  * {cta, gemm (0 QKV, 1 O, 2 gate/up, 3 down), lag (1: the entry belongs to the layer pass before the cycle's),
  * group of observations (-1: every group in turn), tile, first 128-k stage, number of stages}; and info =
