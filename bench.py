@@ -128,6 +128,43 @@ def stage_times(arm, flush) -> None:
     print("stage_times " + json.dumps(out), file=sys.stderr, flush=True)
 
 
+def batch_sweep(args, device) -> None:
+    """A/B aid: ms per launch for several per-GPU batch sizes in one process (weights made once, L2 flushed before
+    every launch, CUDA events), one compact JSON line per batch size.  The engine's tuning variables (PI05_*) are read
+    from the environment when each engine is created, so two runs of this command under different settings on the
+    same box are an A/B pair."""
+    from pi05_megakernel_b200.arm import Pi05Arm
+    geo = FX.Geometry(prefix=args.prefix)
+    weights = {k: v.to(device) for k, v in FX.make_weights(geo, FX.SEEDS[0]).items()}
+    flush = torch.empty(2 * torch.cuda.get_device_properties(device).L2_cache_size, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream(device)
+    for B in [int(x) for x in args.batches.split(",")]:
+        obs = [FX.make_observation(geo, DP.observation_seed(FX.SEEDS[0], 0, i), args.mask) for i in range(B)]
+        dev = dict(weights)
+        for k in FX.ORDER:
+            if k not in weights:
+                dev[k] = (obs[0][k] if B == 1 else torch.stack([o[k] for o in obs]).contiguous()).to(device)
+        arm = Pi05Arm(geo, "b200", str(device), batch=B)
+        arm.bind(dev)
+        times = []
+        for i in range(max(3, args.warmup) + args.steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            arm.launch()
+            b.record(stream)
+            torch.cuda.synchronize(device)
+            if i >= max(3, args.warmup):
+                times.append(a.elapsed_time(b))
+        arm.status()
+        ms = sum(times) / len(times)
+        print(json.dumps({"batch": B, "ms_per_launch": round(ms, 3), "ms_per_chunk": round(ms / B, 3),
+                          "chunks_per_s": round(1e3 * B / ms, 1), "schedule": arm.config.get("schedule"),
+                          "observations_per_mma": arm.config.get("observations_per_mma"),
+                          "gemm_ctas": arm.config.get("gemm_ctas")}), flush=True)
+        arm.close()
+
+
 def cpu_chunks_per_sec(geo, inputs_cpu, runs: int) -> tuple[float, int]:
     """The eager BF16 chunk of the CPU oracle (the restatement of reference/pi05.py::reference)."""
     from oracle import pi05_oracle as O
@@ -184,6 +221,9 @@ def main() -> int:
     ap.add_argument("--kv-pages", type=int, default=0, metavar="TOKENS",
                     help="hand the prefix cache over as a pool of shuffled pages of this many tokens (a multiple of 64) "
                          "through the strided / paged view instead of dense tensors")
+    ap.add_argument("--batches", default="", metavar="B1,B2,...",
+                    help="A/B aid (one GPU): time these per-GPU batch sizes in one process and print one compact line each, "
+                         "instead of the benchmark line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--stage-times", action="store_true",
                     help="also print (stderr) the in-kernel stage timeline of one L2-flushed chunk")
@@ -203,6 +243,10 @@ def main() -> int:
     device = torch.device("cuda", local)
     if dist_on:
         dist.init_process_group("nccl", device_id=device)
+
+    if args.batches:
+        batch_sweep(args, device)
+        return 0
 
     geo = FX.Geometry(prefix=args.prefix)
     B = args.batch
