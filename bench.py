@@ -3,7 +3,8 @@
     python bench.py --gpus 1 --steps 50 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
-    python bench.py --impl reference ...      # the eager CPU path on the box's host cores
+    python bench.py --impl reference ...      # the reference's eager path on the box's host cores
+    python bench.py --impl reference-gpu ...  # the reference's own CUDA megakernel arm on the same GPU (one GPU only)
 
 One "step" is one whole action chunk (10 Euler steps x 18 layers, B=1, prefix 128) = one kernel launch.
 The L2 is flushed (a 2x-L2 zero fill) before every timed chunk and each chunk is timed with CUDA events on
@@ -165,46 +166,158 @@ def batch_sweep(args, device) -> None:
         arm.close()
 
 
-def cpu_chunks_per_sec(geo, inputs_cpu, runs: int) -> tuple[float, int]:
-    """The eager BF16 chunk of the CPU oracle (the restatement of reference/pi05.py::reference)."""
-    from oracle import pi05_oracle as O
+def cpu_chunks_per_sec(geo, inputs_cpu, runs: int) -> tuple[float, int, str]:
+    """Whole chunks per second of the eager BF16 path on the host cores: the reference's own code when it is installed
+    beside this file ("reference"), else the CPU oracle's restatement of it ("port")."""
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    ogeo = O.Geo(prefix=geo.prefix)
-    O.chunk(inputs_cpu, ogeo, False, 1, 2)      # warm the thread pool
+    RFX = reference_package()
+    if RFX is not None:
+        rgeo = RFX.Geometry(prefix=geo.prefix)
+        chunk, kind = (lambda: RFX.reference(rgeo, inputs_cpu)["actions"]), "reference"
+    else:
+        from oracle import pi05_oracle as O
+        ogeo = O.Geo(prefix=geo.prefix)
+        chunk, kind = (lambda: O.chunk(inputs_cpu, ogeo, False)), "port"
+    chunk()      # warm the thread pool
     t0 = time.perf_counter()
     for _ in range(runs):
-        O.chunk(inputs_cpu, ogeo, False)
-    return runs / (time.perf_counter() - t0), torch.get_num_threads()
+        chunk()
+    return runs / (time.perf_counter() - t0), torch.get_num_threads(), kind
+
+
+REF_ROOT = os.path.join(ROOT, "baseline", "_ref")
+
+
+def reference_package():
+    """The unmodified reference as ``baseline/install_reference.py`` lays it out (``baseline/_ref``, not part of the
+    history; absent on calls that leave the folder behind).  Returns its ``fixture`` module or None."""
+    if not os.path.isfile(os.path.join(REF_ROOT, "megabench", "sota", "pi05", "fixture.py")):
+        return None
+    if REF_ROOT not in sys.path:
+        sys.path.insert(0, REF_ROOT)
+    os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(REF_ROOT, "torch_ext"))
+    from megabench.sota.pi05 import fixture as RFX
+    return RFX
 
 
 def run_reference(args, rank: int) -> None:
+    """The reference's own eager BF16 path (reference/pi05.py::reference through its fixture.reference) on all host
+    cores when the reference is installed beside this file, otherwise the CPU oracle's restatement of it."""
     if rank != 0:
         return
     geo = FX.Geometry(prefix=args.prefix)
     cpu = FX.make_inputs(geo, FX.SEEDS[0], "cpu")
-    from oracle import pi05_oracle as O
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    ogeo = O.Geo(prefix=geo.prefix)
-    steps, warm = max(1, min(args.steps, 20)), max(1, min(args.warmup, 2))
+    RFX = reference_package()
+    if RFX is not None:
+        rgeo = RFX.Geometry(prefix=geo.prefix)
+        chunk = lambda: RFX.reference(rgeo, cpu)["actions"]
+        kind, what = "reference", "reference/pi05.py::reference, unmodified, on the host cores"
+    else:
+        from oracle import pi05_oracle as O
+        ogeo = O.Geo(prefix=geo.prefix)
+        chunk = lambda: O.chunk(cpu, ogeo, False)
+        kind, what = "port", "eager CPU path, BF16 rounding schedule of the reference (the reference is not installed here)"
+    steps, warm = max(1, min(args.steps, 30)), max(1, min(args.warmup, 10))     # bounded: about a second per chunk
     for _ in range(warm):
-        O.chunk(cpu, ogeo, False)
+        chunk()
     t0 = time.perf_counter()
     for _ in range(steps):
-        O.chunk(cpu, ogeo, False)
+        chunk()
     dt = (time.perf_counter() - t0) / steps
     value = 1.0 / dt
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"pi0.5 action chunk, B=1, prefix {geo.prefix}, 10 steps x 18 layers "
-                               "(eager CPU path, BF16 rounding schedule of the reference)"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+        "config": {"workload": f"pi0.5 action chunk, B=1, prefix {geo.prefix}, 10 steps x 18 layers ({what})"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
                          "sample": f"{steps} whole chunks (each step is one full chunk)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
+
+
+def run_reference_gpu(args, rank: int, world: int) -> None:
+    """The reference's CUDA megakernel arm (megakernel.py:117-186 there: MegakernelArm(geo, variant, device), bind,
+    launch, outputs) on the same GPU, same inputs, same L2-flushed event timing, checked against the same band.
+    One GPU only: the folder that holds the reference stays behind on calls of two or more GPUs."""
+    if rank != 0:
+        return
+    def unavailable(why: str) -> None:
+        print(json.dumps({"impl": "reference-gpu", "unavailable": why}), flush=True)
+    if world > 1:
+        return unavailable("one GPU only")
+    RFX = reference_package()
+    if RFX is None:
+        return unavailable("the reference is not installed under baseline/_ref (baseline/install_reference.py)")
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+    from megabench.sota.pi05 import megakernel as MK
+    from oracle import pi05_oracle as O
+    geo = FX.Geometry(prefix=args.prefix)
+    variant = args.ref_variant or ("k64" if geo.prefix == 968 else "k16-nofgu")
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    cpu = FX.make_inputs(geo, FX.SEEDS[0], "cpu")
+    dev = {k: v.to(device) for k, v in cpu.items()}
+    t0 = time.time()
+    try:
+        arm = MK.MegakernelArm(RFX.Geometry(prefix=geo.prefix), variant, str(device))
+    except Exception as e:  # noqa: BLE001
+        return unavailable(f"build or set-up of {variant} failed: {type(e).__name__}: {str(e)[-300:]}")
+    build_s = time.time() - t0
+    arm.bind(dev)
+    flush = torch.empty(2 * torch.cuda.get_device_properties(device).L2_cache_size, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream(device)
+    warm = max(3, args.warmup)
+    times = []
+    sampler = ClockSampler(0)
+    for i in range(warm + args.steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        arm.launch()
+        b.record(stream)
+        torch.cuda.synchronize(device)
+        if i >= warm:
+            times.append(a.elapsed_time(b))
+    clocks = sampler.stop()
+    got = arm.outputs()["actions"].cpu()
+    ogeo = O.Geo(prefix=geo.prefix)
+    d = O.band(O.chunk(cpu, ogeo, False), got, O.chunk(cpu, ogeo, True))
+    ms = sum(times) / len(times)
+    print(json.dumps({
+        "impl": "reference-gpu", "metric": METRIC, "value": 1e3 / ms, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": warm, "ms_per_step": ms, "ms_per_launch_median": statistics.median(times), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"pi0.5 action chunk, B=1, prefix {geo.prefix}, 10 steps x 18 layers: the reference's "
+                               f"MegakernelArm variant {variant}, unmodified", "engine": arm.config,
+                   "l2": "flushed before every timed chunk (2x L2 zero fill)", "build_or_load_seconds": round(build_s, 1)},
+        "parity": {"pass": bool(d["pass"]), "relative_error": d["relative_error"],
+                   "reference_relative_error": d["reference_relative_error"]},
+        "clocks": clocks,
+    }), flush=True)
+
+
+def parity_check(arm, geo, weights, obs, B: int) -> dict:
+    """One band check of what the timed arm left in its output buffer, against the CPU oracle (outside every timed
+    region): the rank's observation, or the first and last one of its batch (reference bench.py:220-256)."""
+    from oracle import pi05_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    got = arm.outputs()["actions"].cpu()
+    ogeo = O.Geo(prefix=geo.prefix)
+    which = sorted({0, B - 1})
+    out = {"pass": True, "relative_error": 0.0, "reference_relative_error": 0.0, "observations": which,
+           "checker": "band against the CPU oracle (FP32 and BF16 eager), computed after the timed regions"}
+    for b in which:
+        inputs = {**weights, **obs[b]}
+        d = O.band(O.chunk(inputs, ogeo, False), got if B == 1 else got[b], O.chunk(inputs, ogeo, True))
+        out["pass"] = out["pass"] and bool(d["pass"])
+        if d["relative_error"] >= out["relative_error"]:
+            out["relative_error"], out["reference_relative_error"] = d["relative_error"], d["reference_relative_error"]
+    return out
 
 
 def main() -> int:
@@ -212,7 +325,10 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-gpu"])
+    ap.add_argument("--ref-variant", default="", help="--impl reference-gpu: the reference arm's variant string "
+                                                      "(default k16-nofgu, k64 at prefix 968)")
+    ap.add_argument("--no-parity", action="store_true", help="skip the band check of the timed arm's result")
     ap.add_argument("--prefix", type=int, default=128)
     ap.add_argument("--batch", type=int, default=1, help="independent observations per GPU per launch (1..16)")
     ap.add_argument("--mask", default="full", choices=["full", "pad", "scatter"],
@@ -233,6 +349,9 @@ def main() -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return 0
+    if args.impl == "reference-gpu":
+        run_reference_gpu(args, rank, world)
         return 0
     warmup = max(3, args.warmup)
 
@@ -338,7 +457,25 @@ def main() -> int:
     barrier()
     e2e_step_ms = sum(e2e_ms) / len(e2e_ms)
 
-    ms_step, e2e_step_ms = DP.max_over_ranks([ms_step, e2e_step_ms], device)
+    # ---- steady: back-to-back launches without the flush (the reference harness's second number, bench.py:271-281 there)
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record(stream)
+    for _ in range(args.steps):
+        arm.launch()
+    s1.record(stream)
+    torch.cuda.synchronize(device)
+    steady_ms = s0.elapsed_time(s1) / args.steps
+    arm.status()
+
+    # ---- one band check of the result the timed arm produced, outside every timed region
+    parity = None
+    if not args.no_parity:
+        parity = parity_check(arm, geo, weights, obs, B)
+        all_pass = DP.max_over_ranks([0.0 if parity["pass"] else 1.0], device)[0] == 0.0
+        parity["all_ranks_pass"] = bool(all_pass)
+
+    ms_step, e2e_step_ms, steady_ms = DP.max_over_ranks([ms_step, e2e_step_ms, steady_ms], device)
 
     if rank == 0:
         peak_gbs, peak_kind = measured_peaks()
@@ -358,6 +495,9 @@ def main() -> int:
                        "parallelism": f"dp{world} (independent observations, replicated weights, no collective)",
                        "engine": arm.config},
             "ms_per_chunk": ms_step / B, "ms_per_launch_median": statistics.median(samples), "batch_per_gpu": B,
+            "ms_per_launch_steady": steady_ms, "parity": parity,
+            "reference_gpu": "not part of this command: `bench.py --impl reference-gpu` times the reference's own CUDA arm "
+                             "on the same GPU (one-GPU calls only); vs_baseline divides by a figure published from another machine",
             "x_hbm_floor_nominal": ms_step / (alg_bytes / HBM_NOMINAL * 1e3),
             "x_hbm_floor_measured": ms_step / (alg_bytes / (peak_gbs * 1e9) * 1e3),
             "vs_baseline_note": f"value / (1000 / {SOTA_GRAPH_MS} ms), the reference's published sota-graph arm on one B200",
@@ -370,9 +510,9 @@ def main() -> int:
                          "algorithmic_bytes_per_launch": alg_bytes, "traffic": ncu_traffic(B, geo.prefix)},
         }
         if world == 1 and B == 1 and not args.no_cpu_baseline:
-            cps, cores = cpu_chunks_per_sec(geo, cpu, 5)
-            line["cpu_baseline"] = {"value": cps, "unit": UNIT, "cores": cores, "kind": "port",
-                                    "sample": "5 whole chunks of the same workload (eager BF16 schedule)"}
+            cps, cores, kind = cpu_chunks_per_sec(geo, cpu, 10)
+            line["cpu_baseline"] = {"value": cps, "unit": UNIT, "cores": cores, "kind": kind,
+                                    "sample": "10 whole chunks of the same workload (eager BF16 path)"}
         print(json.dumps(line), flush=True)
     if args.stage_times and rank == 0:
         stage_times(arm, flush)
