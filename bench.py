@@ -301,6 +301,60 @@ def run_reference_gpu(args, rank: int, world: int) -> None:
     }), flush=True)
 
 
+def run_tensor_parallel(args, rank: int, local: int, world: int) -> int:
+    """BASELINE config 5: ONE observation shared by the `world` GPUs of the launch (query heads and MLP columns cut
+    across the ranks, partial sums exchanged inside the kernel over NVLink).  Reports the latency of one chunk (slowest
+    rank, L2 flushed, ranks lined up before every chunk) next to nothing else: compare with the one-GPU line."""
+    import torch.distributed as dist
+    from pi05_megakernel_b200.arm import Pi05Arm
+    if world < 2:
+        print(json.dumps({"impl": "b200-tp", "unavailable": "tensor parallel needs 2, 4 or 8 ranks (torchrun)"}), flush=True)
+        return 0
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    geo = FX.Geometry(prefix=args.prefix)
+    weights = FX.make_weights(geo, FX.SEEDS[0])
+    obs = FX.make_observation(geo, DP.observation_seed(FX.SEEDS[0], 0, 0), args.mask)      # the same one on every rank
+    cpu = {**weights, **obs}
+    arm = Pi05Arm(geo, "b200", str(device), tp=(rank, world))
+    arm.bind({k: cpu[k].to(device) for k in FX.ORDER})
+    arm.tp_attach_all()
+    flush = torch.empty(2 * torch.cuda.get_device_properties(device).L2_cache_size, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream(device)
+    warm, times = max(3, args.warmup), []
+    sampler = ClockSampler(local) if rank == 0 else None
+    for i in range(warm + args.steps):
+        flush.zero_()
+        dist.barrier()                       # on the stream: the ranks' kernels start together
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        arm.launch()
+        b.record(stream)
+        torch.cuda.synchronize(device)
+        if i >= warm:
+            times.append(a.elapsed_time(b))
+    arm.status()
+    clocks = sampler.stop() if sampler else None
+    ms = DP.max_over_ranks([sum(times) / len(times)], device)[0]
+    parity = None
+    if not args.no_parity:
+        parity = parity_check(arm, geo, weights, [obs], 1)
+        parity["all_ranks_pass"] = DP.max_over_ranks([0.0 if parity["pass"] else 1.0], device)[0] == 0.0
+    if rank == 0:
+        print(json.dumps({
+            "impl": "b200-tp", "metric": "ms per action chunk, one observation across the GPUs (tensor parallel, L2 flushed)",
+            "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms,
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"pi0.5 action chunk, B=1, prefix {geo.prefix} ({args.mask} mask), 10 x 18, tensor parallel "
+                                   f"over {world} GPUs: heads and MLP columns cut, per-layer partial sums pushed between "
+                                   "the row CTAs of the ranks with peer stores", "engine": arm.config},
+            "ms_per_launch_median": statistics.median(times), "parity": parity, "clocks": clocks}), flush=True)
+    arm.close()
+    dist.destroy_process_group()
+    return 0
+
+
 def parity_check(arm, geo, weights, obs, B: int) -> dict:
     """One band check of what the timed arm left in its output buffer, against the CPU oracle (outside every timed
     region): the rank's observation, or the first and last one of its batch (reference bench.py:220-256)."""
@@ -329,6 +383,9 @@ def main() -> int:
     ap.add_argument("--ref-variant", default="", help="--impl reference-gpu: the reference arm's variant string "
                                                       "(default k16-nofgu, k64 at prefix 968)")
     ap.add_argument("--no-parity", action="store_true", help="skip the band check of the timed arm's result")
+    ap.add_argument("--tp", action="store_true",
+                    help="tensor parallel: all ranks of the launch share ONE observation (latency line instead of the "
+                         "data-parallel benchmark line)")
     ap.add_argument("--prefix", type=int, default=128)
     ap.add_argument("--batch", type=int, default=1, help="independent observations per GPU per launch (1..16)")
     ap.add_argument("--mask", default="full", choices=["full", "pad", "scatter"],
@@ -353,6 +410,8 @@ def main() -> int:
     if args.impl == "reference-gpu":
         run_reference_gpu(args, rank, world)
         return 0
+    if args.tp:
+        return run_tensor_parallel(args, rank, local, world)
     warmup = max(3, args.warmup)
 
     import torch.distributed as dist

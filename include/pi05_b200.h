@@ -51,9 +51,30 @@ enum {
 /* Replaces setup(device) (mk/pi05_mk.cu:3363-3380).  max_prefix bounds the prefix length accepted by
  * pi05_bind; max_batch (1..16) is the largest number of independent observations one launch may serve (the
  * workspace grows with it; the weights are streamed from HBM once per launch for all of them); tp_rank and
- * tp_size select the tensor-parallel build (only tp_size = 1 exists today; anything else returns
- * PI05_ERR_UNSUPPORTED). */
+ * tp_size (1, 2, 4 or 8; more than 1 only with max_batch = 1) make this engine one of tp_size ranks, one per GPU,
+ * that share a single observation: see "tensor parallel" below. */
 int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_size, pi05_handle_t* out);
+
+/* Tuning settings of a handle: the counterpart of the reference's build variants and -D macros (megakernel.py:29-78,
+ * mk/pi05_mk.cu:34-320), as run-time values.  The library reads no environment variable; a host program that wants
+ * settings from its environment fills this struct itself.  pi05_tuning_defaults writes the values a fresh handle
+ * uses; pi05_tune replaces a handle's settings (values out of range are clamped) and un-binds it: the schedule and
+ * the launch shape are chosen by the next pi05_bind. */
+typedef struct pi05_tuning {
+  int poll_ns;            /* pause between two samples of a stage counter (default 20) */
+  int obs_per_mma;        /* observations side by side in one MMA of a batch: 0 = engine's choice, 1, 2 */
+  int two_streams;        /* batches: the throughput schedule as two streams of groups half a layer pass apart (default 1) */
+  int entries_per_phase;  /* batches: schedule entries per CTA and phase the K splits aim at; 0 = by batch size */
+  int grouped_from;       /* smallest batch that gets the throughput schedule (default 3) */
+  int streams_from;       /* smallest batch that gets its two streams (default 5) */
+  int latency_schedule;   /* 1: the one-observation schedule for every batch size (default 0) */
+  int key_groups;         /* one observation: groups of row CTAs that share the keys of an attention; 0 = by prefix length */
+  int row_groups;         /* batches: groups of row CTAs; 0 = by batch size */
+  int clusters;           /* launch the grid as clusters of two CTAs when the device takes it that way (default 1) */
+  int cta_perm;           /* 1: the two blocks of a cluster play CTA i and CTA grid / 2 + i (default 0) */
+} pi05_tuning;
+int pi05_tuning_defaults(pi05_tuning* t);
+int pi05_tune(pi05_handle_t h, const pi05_tuning* t);
 
 /* Replaces workspace_bytes() (mk/pi05_mk.cu:3659-3660): size of the scratch buffer the caller allocates
  * on the engine's GPU (256-byte aligned) and passes to pi05_bind. */
@@ -63,7 +84,8 @@ int pi05_workspace_bytes(pi05_handle_t h, size_t* bytes);
  * (megakernel.py:167-176): records the 25 device pointers (caller-owned, read-only, kept across launches and
  * across in-place refills), the output buffer actions [50,32] f32 and the workspace, clears the workspace and
  * encodes the TMA descriptors.  prefix_len is P (1..max_prefix), batch the number of observations (1..max_batch).
- * Synchronises the device. */
+ * Waits for the handle's last launch (a re-bind must not pull the workspace from under a running chunk) and
+ * synchronises the device. */
 int pi05_bind(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, int batch,
               void* actions, void* workspace, size_t workspace_bytes);
 
@@ -108,9 +130,12 @@ int pi05_refresh(pi05_handle_t h);
 int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsigned long long* stamps);
 #define PI05_NUM_STAMPS 256
 
-/* Replaces fg_timeouts()/att_timeouts() (mk/pi05_mk.cu:3505-3520): synchronises the device and reads the status
- * word the kernel writes when a bounded wait gives up.  code = 0 when the last launches completed; otherwise
- * code is a PI05_WAIT_* value and where = (cta << 16) | stage.  Clears the word. */
+/* Replaces fg_timeouts()/att_timeouts() (mk/pi05_mk.cu:3505-3520): waits for this handle's last launch (not for the
+ * whole device: other handles and streams keep running) and reads the status word the kernel writes when a bounded
+ * wait gives up.  code = 0 when the last launches completed; otherwise code is a PI05_WAIT_* value and where =
+ * (cta << 16) | stage, PI05_ERR_DEVICE_TIMEOUT is returned, and the word is cleared.  A chunk whose wait gave up has
+ * filled its actions with NaN, so a caller that skips this call cannot take an earlier chunk's result for this one's.
+ * pi05_launch itself does not look at the word. */
 int pi05_status(pi05_handle_t h, int* code, int* where);
 
 /* Replaces layout_offsets() (mk/pi05_mk.cu:3622-3627): byte offset and size of a named workspace buffer
@@ -147,11 +172,33 @@ const char* pi05_config_json(pi05_handle_t h);
  * group of observations (-1: every group in turn), tile, first 128-k stage, number of stages}; and info =
  * {GEMM CTAs, row-CTA groups, key groups, observations per MMA, groups of observations, groups in the first of two
  * streams (0: one stream), units per observation of QKV, O, gate/up, down}.  *count receives the number of entries
- * there are, which may exceed capacity.  The tuning variables of the environment apply as in pi05_create. */
+ * there are, which may exceed capacity.  tuning = NULL: the defaults of a fresh handle. */
 #define PI05_PLAN_ENTRY 7
 #define PI05_PLAN_INFO 10
-int pi05_schedule_plan(int sms, int batch, int prefix_len, int* entries, int capacity, int* count,
-                       int info[PI05_PLAN_INFO]);
+int pi05_schedule_plan(int sms, int batch, int prefix_len, const pi05_tuning* tuning, int* entries, int capacity,
+                       int* count, int info[PI05_PLAN_INFO]);
+
+/* Tensor parallel (no counterpart in the reference, which runs on one GPU only): tp_size engines, one per GPU, each
+ * bound to the SAME 25 inputs in its own GPU's memory, compute one chunk together.  Rank r streams only its share of
+ * the weights - query heads 8 r / tp_size .. of wq (and the matching columns of wo), MLP columns 4096 r / tp_size ..
+ * of wg / wu (and the matching columns of wd), as reference/pi05.py:254-265 and 268-279 would be cut; wk / wv and the
+ * single KV head, the norms and the small FP32 layers run on every rank - and after the O and the down projection
+ * every rank stores its [50, 1024] FP32 partial sums into a receive buffer in every PEER's workspace with plain
+ * stores over NVLink, bumps a counter there (release at system scope), waits (bounded) for its own counters and adds
+ * the partial sums in rank order, so that all ranks keep the same residual stream and every rank's actions buffer
+ * receives the result.  Set-up, after every rank has bound its inputs: exchange the pi05_tp_export blobs between the
+ * ranks (any host transport), pi05_tp_attach each peer's blob, make sure every rank has attached (a host barrier),
+ * then launch the same (n_steps, n_layers) on every rank.  A rank whose peer never arrives reports
+ * PI05_ERR_DEVICE_TIMEOUT through pi05_status like any other bounded wait; all ranks then have to bind again.
+ * pi05_tp_attach_pointer takes the peer's workspace address directly (one process that drives several GPUs with
+ * peer access enabled). */
+#define PI05_TP_HANDLE_BYTES 96
+int pi05_tp_export(pi05_handle_t h, void* out, size_t out_bytes);
+int pi05_tp_attach(pi05_handle_t h, int peer_rank, const void* exported);
+int pi05_tp_attach_pointer(pi05_handle_t h, int peer_rank, void* peer_workspace);
+/* pi05_schedule_plan for rank tp_rank of tp_size. */
+int pi05_schedule_plan_tp(int sms, int batch, int prefix_len, int tp_rank, int tp_size, const pi05_tuning* tuning,
+                          int* entries, int capacity, int* count, int info[PI05_PLAN_INFO]);
 
 /* Number of kernel launches issued by this handle since creation (one per pi05_launch). */
 int pi05_launch_count(pi05_handle_t h, unsigned long long* count);
@@ -175,9 +222,13 @@ int pi05_destroy(pi05_handle_t h);
  * stream before launching), and two calls that overlap on the same GPU - different streams, different host
  * threads - race on it and give wrong results; issue them on one stream or order them yourself.
  *
- * The first call on a device does the set-up (host-side state, address of the array, shared-memory opt-in), and
- * the first call with a given set of pointers / prefix length encodes the TMA descriptors and clears the array;
- * both synchronise the device, so make that call once before any stream capture or latency-critical region.
+ * The first call on a device does the set-up (host-side state with one event and one small stream, address of the
+ * array, shared-memory opt-in), and the first call with a given set of pointers / prefix length encodes the TMA
+ * descriptors and clears the array after waiting for the previous call out of the array, on whatever stream that
+ * was; both synchronise the device, so make that call once before any stream capture or latency-critical region.
+ * A device-side wait that gave up cannot be reported by the asynchronous call that hit it: the kernel then fills
+ * actions with NaN, and the NEXT call on that GPU that finds the earlier kernel finished returns
+ * PI05_ERR_DEVICE_TIMEOUT instead of launching (call again to go on).
  * Later calls with the same pointers only enqueue a memset of the control block (about 30 KB) and the kernel on `stream`.  No cudaMalloc,
  * cudaFree or allocating library routine is called on any of these paths.
  *

@@ -74,7 +74,10 @@ class PagedPrefix:
 class Pi05Arm:
     name = "b200-megakernel"
 
-    def __init__(self, geo: Geometry, variant: str = "b200", device: str = "cuda", batch: int = 1) -> None:
+    def __init__(self, geo: Geometry, variant: str = "b200", device: str = "cuda", batch: int = 1,
+                 tp: tuple[int, int] = (0, 1)) -> None:
+        """``tp = (rank, size)``: this arm is one of ``size`` arms, one per GPU, that compute the same observation
+        together (tensor parallel; see ``tp_export`` / ``tp_attach``)."""
         if (geo.horizon, geo.action_dim, geo.layers, geo.steps, geo.hidden, geo.intermediate,
                 geo.q_heads, geo.kv_heads, geo.head_dim) != (50, 32, 18, 10, 1024, 4096, 8, 1, 256):
             raise ValueError("the engine is specialised for horizon 50, action 32, 18 layers, 10 steps, "
@@ -94,8 +97,12 @@ class Pi05Arm:
         index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.device = torch.device("cuda", index)
         handle = ctypes.c_void_p()
-        _lib.check(self.lib, None, self.lib.pi05_create(index, geo.prefix, batch, 0, 1, ctypes.byref(handle)))
+        self.tp_rank, self.tp_size = tp
+        _lib.check(self.lib, None, self.lib.pi05_create(index, geo.prefix, batch, self.tp_rank, self.tp_size,
+                                                        ctypes.byref(handle)))
         self.handle = handle
+        self.tuning = _lib.tuning_from_env(self.lib)         # defaults, or the PI05_* overrides of a development run
+        _lib.check(self.lib, handle, self.lib.pi05_tune(handle, ctypes.byref(self.tuning)))
         nbytes = ctypes.c_size_t()
         _lib.check(self.lib, handle, self.lib.pi05_workspace_bytes(handle, ctypes.byref(nbytes)))
         self.ws = torch.empty(nbytes.value, dtype=torch.uint8, device=self.device)
@@ -143,6 +150,29 @@ class Pi05Arm:
         self.tensors = tensors
         # the engine chooses its schedule when it knows the batch: record what it chose
         self.config.update(json.loads(self.lib.pi05_config_json(self.handle).decode()))
+
+    # ------------------------------------------------------------------ tensor parallel
+    def tp_export(self) -> bytes:
+        """After ``bind``: what the other ranks need to reach this arm's receive buffers (send it to them by any means)."""
+        buf = ctypes.create_string_buffer(_lib.TP_HANDLE_BYTES)
+        _lib.check(self.lib, self.handle, self.lib.pi05_tp_export(self.handle, buf, _lib.TP_HANDLE_BYTES))
+        return buf.raw
+
+    def tp_attach(self, peer_rank: int, exported: bytes) -> None:
+        """Open rank ``peer_rank``'s receive buffers (its ``tp_export()``); needed for every peer before ``launch``."""
+        buf = ctypes.create_string_buffer(exported, _lib.TP_HANDLE_BYTES)
+        _lib.check(self.lib, self.handle, self.lib.pi05_tp_attach(self.handle, peer_rank, buf))
+
+    def tp_attach_all(self, group=None) -> None:
+        """The usual set-up under ``torch.distributed`` (one process per GPU): all-gather the exports, attach every peer,
+        and line the ranks up so that nobody launches before everybody has attached."""
+        import torch.distributed as dist
+        blobs = [None] * self.tp_size
+        dist.all_gather_object(blobs, self.tp_export(), group=group)
+        for r, blob in enumerate(blobs):
+            if r != self.tp_rank:
+                self.tp_attach(r, blob)
+        dist.barrier(group=group)
 
     def refresh_weights(self) -> None:
         _lib.check(self.lib, self.handle, self.lib.pi05_refresh(self.handle))

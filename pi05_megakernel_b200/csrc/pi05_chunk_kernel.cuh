@@ -5,6 +5,10 @@
 //                    are sensitive to every instruction: the production kernel is ~3 % faster without it)
 //   PI05_BATCHED  1: any number of observations per launch; 0: exactly one, and all per-observation pointer
 //                    arithmetic and loops fold away
+//   PI05_TP       1: tensor parallel, one observation shared by several GPUs: every rank runs the query heads and
+//                    MLP columns its schedule names, and the partial sums of the O and down projections are exchanged
+//                    between the ranks' row CTAs over NVLink (peer stores and system-scope counters) inside the
+//                    gated-residual operation; 0: none of that code exists
 //   PI05_GN       observations per MMA (1 or 2): the GEMM CTAs put the activations of GN observations side by
 //                    side on the N side of one MMA (N = 64 * GN), so a weight stage in shared memory is fetched
 //                    once for all of them.  The activation half of a stage grows to GN x 16 KB and the ring keeps
@@ -91,6 +95,22 @@ __device__ __forceinline__ bool wait_mbar(const Ctx& c, uint32_t bar, uint32_t p
   }
 }
 
+#if PI05_TP
+// The same wait on a counter that other GPUs bump.
+__device__ __forceinline__ bool wait_event_sys(const Ctx& c, const unsigned int* ev, unsigned int target, int stage) {
+  if ((int)(ptx::ld_acquire_sys(ev) - target) >= 0) return true;
+  const long long t0 = clock64();
+  for (unsigned i = 0;; ++i) {
+    if ((int)(ptx::ld_acquire_sys(ev) - target) >= 0) return true;
+    if ((i & 31u) == 31u) {
+      if (ptx::ld_relaxed(c.status) != 0u) return false;
+      if (clock64() - t0 > c.limit) { report_timeout(c, WAIT_EVENT, stage); return false; }
+    }
+    __nanosleep(c.poll_ns);
+  }
+}
+#endif
+
 __device__ __forceinline__ bool wait_event(const Ctx& c, const unsigned int* ev, unsigned int target, int stage) {
   // One load in flight at a time on purpose: sampling the counter more often (several relaxed loads in flight)
   // was measured slower, the extra reads of the line delay the producers' updates of it.
@@ -140,6 +160,13 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float z = 0.7978845608028654f * (x + 0.044715f * x * x * x);
   return 0.5f * x * (1.0f + tanhf(z));
+}
+
+// A wait that ignores the status word: used only while leaving, for copies that are already in flight.
+__device__ __forceinline__ void drain_mbar(uint32_t bar, uint32_t parity, long long limit) {
+  const long long t0 = clock64();
+  while (!ptx::mbar_try_wait(bar, parity))
+    if (clock64() - t0 > limit) return;
 }
 
 // ------------------------------------------------------------------------------------------- prologue
@@ -373,8 +400,13 @@ __device__ __forceinline__ void row_prefetch(const Params& p, int mode, int step
 //            the step tail: final adaRMS, v = Wout n + b, x += dt v, and (unless it was the last step)
 //            h = bf16(Win x + b), an_attn = adaRMS_attn[0](h) with the next step's modulation.
 //   ROW_INIT: x = noise, h = bf16(Win x + b), an_attn = adaRMS_attn[0](h).
-__device__ void row_op(const Params& p, const ObsPtrs& o, uint8_t* smem, int unit, int mode, int step, int layer,
-                       float (&hn)[8], const RowMod& rm) {
+// Tensor parallel: the accumulator then holds only this rank's share of the sum (its heads, its MLP columns).  Every
+// rank stores its two rows into its slot of every peer's receive buffer, bumps the peer's counter for this row CTA
+// (release at system scope, after a CTA barrier), waits until all peers have done the same here, and adds the
+// size partial sums in rank order - the same order on every rank, so every rank keeps the same residual stream.
+// Returns false when that wait gave up.
+__device__ bool row_op(const Params& p, const Ctx& c, const ObsPtrs& o, uint8_t* smem, int unit, int mode, int step, int layer,
+                       int pass, float (&hn)[8], const RowMod& rm) {
   const int tid = threadIdx.x, lane = tid & 31;
   const int half = tid >> 7, i = tid & 127, wq = (tid >> 5) & 3;
   const int t = unit * 2 + half;
@@ -440,7 +472,7 @@ __device__ void row_op(const Params& p, const ObsPtrs& o, uint8_t* smem, int uni
     action_in();
     store_h(hn);
     next_step_norm(0);
-    return;
+    return true;
   }
 
   // gated residual.  With a batch of one the residual stream stays in this thread's registers between row
@@ -456,7 +488,46 @@ __device__ void row_op(const Params& p, const ObsPtrs& o, uint8_t* smem, int uni
     const float4 a0 = __ldcg(reinterpret_cast<const float4*>(acc)), a1 = __ldcg(reinterpret_cast<const float4*>(acc + 4));
     *reinterpret_cast<float4*>(acc) = make_float4(0.f, 0.f, 0.f, 0.f);
     *reinterpret_cast<float4*>(acc + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#if PI05_TP
+    if (p.tp_size > 1) {
+      const int kind = mode == ROW_ATT ? 0 : 1;
+      const size_t at = ((size_t)(kind * p.tp_size + p.tp_rank) * T + t) * W + c0;
+      for (int r = 0; r < p.tp_size; ++r)
+        if (r != p.tp_rank) {
+          *reinterpret_cast<float4*>(p.tp_peer_recv[r] + at) = a0;
+          *reinterpret_cast<float4*>(p.tp_peer_recv[r] + at + 4) = a1;
+        }
+      ptx::fence_acq_rel_sys();
+      __syncthreads();
+      __shared__ int tp_ok;
+      if (tid == 0) {
+        const int slot = (kind * NROW_CTAS + unit) * TP_FLAG_STRIDE;
+        for (int r = 0; r < p.tp_size; ++r)
+          if (r != p.tp_rank) ptx::red_release_sys_add(p.tp_peer_flags[r] + slot, 1u);
+        tp_ok = wait_event_sys(c, p.tp_flags + slot, p.tp_base + (unsigned)((p.tp_size - 1) * (pass + 1)),
+                               pass * NSTAGE + (kind ? ST_RFFN : ST_RATT)) ? 1 : 0;
+      }
+      __syncthreads();
+      if (!tp_ok) return false;
+      float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < p.tp_size; ++r) {
+        float pv[8];
+        if (r == p.tp_rank) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) pv[e] = av[e];
+        } else {
+          const float* src = p.tp_recv + ((size_t)(kind * p.tp_size + r) * T + t) * W + c0;
+          const float4 b0 = __ldcg(reinterpret_cast<const float4*>(src)), b1 = __ldcg(reinterpret_cast<const float4*>(src + 4));
+          pv[0] = b0.x; pv[1] = b0.y; pv[2] = b0.z; pv[3] = b0.w; pv[4] = b1.x; pv[5] = b1.y; pv[6] = b1.z; pv[7] = b1.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum[e] += pv[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) av[e] = sum[e];
+    }
+#endif
 #pragma unroll
     for (int e = 0; e < 8; ++e) hn[e] = rb(hn[e] + rb(rb(av[e]) * rb(rm.gate[e])));
   }
@@ -466,9 +537,9 @@ __device__ void row_op(const Params& p, const ObsPtrs& o, uint8_t* smem, int uni
 #pragma unroll
     for (int e = 0; e < QKVW / 4 / 128; ++e) z[e * 128] = make_float4(0.f, 0.f, 0.f, 0.f);
     ada_norm(hn, rm.scale, rm.shift, o.an_ffn);
-    return;
+    return true;
   }
-  if (layer + 1 < p.n_layers) { ada_norm(hn, rm.scale, rm.shift, o.an_attn); return; }
+  if (layer + 1 < p.n_layers) { ada_norm(hn, rm.scale, rm.shift, o.an_attn); return true; }
   // ---- step tail: final norm, action_out, Euler update
   {
     const float ss = sumsq(hn);
@@ -504,6 +575,7 @@ __device__ void row_op(const Params& p, const ObsPtrs& o, uint8_t* smem, int uni
       next_step_norm(step + 1);
     }
   }
+  return true;
 }
 
 // ------------------------------------------------------------------------------------------- attention
@@ -1238,7 +1310,7 @@ __device__ __forceinline__ bool row_residual(const Params& p, const Ctx& c, uint
   if (!cta_wait_event(p, c, EVB(first ? EV_O : EV_DOWN, ob), p.n_units[first ? G_O : G_DOWN] * (pass + 1),
                       pass * NSTAGE + (first ? ST_RATT : ST_RFFN))) return false;
   if (stamp && sbase + (first ? ST_O : ST_DOWN) < 64) p.stamps[sbase + (first ? ST_O : ST_DOWN)] = globaltimer();
-  row_op(p, o, smem, unit, mode, step, layer, hn, rm);
+  if (!row_op(p, c, o, smem, unit, mode, step, layer, pass, hn, rm)) return false;
   if (stamp && pass == 1 && first) p.stamps[231] = globaltimer();
   ptx::fence_proxy_async_global();
   cta_signal(p, first ? EV_ANF : EV_ANA, ob);
@@ -1394,7 +1466,7 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
       float hn[8];
       RowMod none;
       for (int ob = group; ob < PI05_NB(p); ob += PI05_NG(p)) {
-        row_op(p, obs(p, ob), smem, unit, ROW_INIT, 0, 0, hn, none);
+        row_op(p, c, obs(p, ob), smem, unit, ROW_INIT, 0, 0, 0, hn, none);
         ptx::fence_proxy_async_global();
         cta_signal(p, EV_ANA, ob);
       }
@@ -1408,10 +1480,15 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
   // ---------------- teardown: drain loads still in flight, free TMEM, last CTA out clears the counters
   __syncthreads();
   if (is_gemm && warp == 0 && lane == 0 && s_issued != s_consumed) {
-    // Only after an aborted run: weight loads were issued whose stage was never consumed.  Their stage barrier
-    // also expects the activation half, which may never come, so give the copies in flight a fixed time to land.
-    const long long t0 = clock64();
-    while (clock64() - t0 < DRAIN_CYCLES) { }
+    // Only after an aborted run: weight loads were issued whose stage was never consumed.  A stage's barrier completes
+    // when both halves have arrived and every byte has landed; the activation half may never come, so arrive in its
+    // place and wait (bounded) for the weights.  If the activation half did come, the barrier has completed already
+    // and the extra arrival falls into a phase nobody will use.
+    for (uint32_t it = s_consumed; it != s_issued; ++it) {
+      const uint32_t s = it % (uint32_t)V_NSTG;
+      ptx::mbar_arrive(b.full + 8 * s);
+      drain_mbar(b.full + 8 * s, (it / (uint32_t)V_NSTG) & 1u, p.wait_limit);
+    }
   }
   __syncthreads();
   if (is_gemm && warp == 1) {
@@ -1423,6 +1500,11 @@ __global__ void __launch_bounds__(THREADS, 1) pi05_chunk_kernel(const __grid_con
     const unsigned prev = atomicAdd(p.ctrl + EVW(EV_EXIT), 1u);
     if (prev == (unsigned)ncta - 1) {
       __threadfence();
+      if (ptx::ld_relaxed(p.ctrl) != 0u) {
+        // a bounded wait gave up somewhere: whoever reads the output must not mistake an earlier chunk's actions for
+        // this one's
+        for (int i = 0; i < PI05_NB(p) * T * ADIM; ++i) p.ob.actions[i] = __int_as_float(0x7fc00000);
+      }
       for (int e = 0; e < NEVENTS * MAXB; ++e) p.ctrl[32 * (1 + e)] = 0u;
       __threadfence();
     }

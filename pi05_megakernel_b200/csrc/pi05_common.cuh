@@ -93,7 +93,12 @@ enum { WAIT_W_EMPTY = 1, WAIT_W_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_T_EMPTY, W
 // schedule), bits 8.. = group of observations + 1 (0: every group in turn)
 struct Unit { int gemm, tile, k0, nk; };
 constexpr int MAX_UNITS = 32;              // schedule entries per CTA and layer pass
-constexpr long long DRAIN_CYCLES = 400000;          // exit-time grace period for TMA loads still in flight after an abort
+constexpr int MAX_TP = 8;                  // GPUs that may share one chunk (tensor parallel)
+// Tensor parallel: every rank holds receive slots [2 reductions (after O, after down)][tp_size ranks][T][W] FP32 and one
+// arrival counter per (reduction, row CTA); the peers write into them over NVLink.  Neither is cleared at kernel exit
+// (a peer may be a little ahead or behind): the counters only grow, and a launch waits for values above `tp_base`.
+constexpr int TP_SLOT_FLOATS = T * W;
+constexpr int TP_FLAG_STRIDE = 32;         // one counter per 128-byte line
 
 struct alignas(64) TMaps {
   CUtensorMap wq, wk, wv, wo, wg, wu, wd;   // weights: {K, L*rows} BF16, box {64, 64}, 128-B swizzle
@@ -142,6 +147,13 @@ struct Params {
   int row_order;           // several observations: 0 = attention of one, then the residual of the one before; 1 = all attentions first
   int cta_perm;            // role permutation over the blocks of the grid (see the kernel's first lines)
   int n_units[4];          // units per GEMM kind (event targets)
+  // tensor parallel (tp_size > 1): this rank's receive slots and arrival counters, and where every peer's are
+  int tp_rank, tp_size;
+  unsigned int tp_base;    // arrivals per counter that earlier launches of this binding have consumed
+  float* tp_recv;          // [2][tp_size][T][W]
+  unsigned int* tp_flags;  // [2][NROW_CTAS] counters, TP_FLAG_STRIDE words apart
+  float* tp_peer_recv[MAX_TP];
+  unsigned int* tp_peer_flags[MAX_TP];
   float t_steps[NS];
   float dt;
 };

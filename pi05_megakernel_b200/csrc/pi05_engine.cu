@@ -45,37 +45,56 @@ namespace k_plain {
 #define PI05_TRACE 0
 #define PI05_BATCHED 0
 #define PI05_GN 1
+#define PI05_TP 0
 #include "pi05_chunk_kernel.cuh"
 #undef PI05_TRACE
 #undef PI05_BATCHED
 #undef PI05_GN
+#undef PI05_TP
 }  // namespace k_plain
 namespace k_batched {
 #define PI05_TRACE 0
 #define PI05_BATCHED 1
 #define PI05_GN 1
+#define PI05_TP 0
 #include "pi05_chunk_kernel.cuh"
 #undef PI05_TRACE
 #undef PI05_BATCHED
 #undef PI05_GN
+#undef PI05_TP
 }  // namespace k_batched
 namespace k_pairs {
 #define PI05_TRACE 0
 #define PI05_BATCHED 1
 #define PI05_GN 2
+#define PI05_TP 0
 #include "pi05_chunk_kernel.cuh"
 #undef PI05_TRACE
 #undef PI05_BATCHED
 #undef PI05_GN
+#undef PI05_TP
 }  // namespace k_pairs
+namespace k_tp {
+#define PI05_TRACE 0
+#define PI05_BATCHED 0
+#define PI05_GN 1
+#define PI05_TP 1
+#include "pi05_chunk_kernel.cuh"
+#undef PI05_TRACE
+#undef PI05_BATCHED
+#undef PI05_GN
+#undef PI05_TP
+}  // namespace k_tp
 namespace k_traced {
 #define PI05_TRACE 1
 #define PI05_BATCHED 1
 #define PI05_GN 1
+#define PI05_TP 0
 #include "pi05_chunk_kernel.cuh"
 #undef PI05_TRACE
 #undef PI05_BATCHED
 #undef PI05_GN
+#undef PI05_TP
 }  // namespace k_traced
 
 #ifndef PI05_PAIRS_FROM
@@ -87,7 +106,7 @@ namespace k_traced {
 namespace {
 const void* const kAllKernels[] = {(const void*)k_plain::pi05_chunk_kernel, (const void*)k_batched::pi05_chunk_kernel,
                                    (const void*)k_pairs::pi05_chunk_kernel,
-                                   (const void*)k_traced::pi05_chunk_kernel};
+                                   (const void*)k_traced::pi05_chunk_kernel, (const void*)k_tp::pi05_chunk_kernel};
 }  // namespace
 
 // =========================================================================================== host side
@@ -109,7 +128,6 @@ struct pi05_engine {
   int key_groups = 1;
   int pages_per_obs = 1, page_tokens = 1;
   bool clustered = false;        // launched as clusters of two CTAs: consecutive blocks share a TPC
-  int cta_perm = 0;              // 1: block b plays CTA b / 2 (even b) or grid / 2 + b / 2 (odd b)
   bool bound = false;
   const void* inputs[PI05_NUM_INPUTS] = {};
   void* actions = nullptr;
@@ -120,18 +138,23 @@ struct pi05_engine {
   std::vector<int> sched_n;
   int n_units[4] = {0, 0, 0, 0};
   TMaps maps;
-  int obs_per_mma = 0;           // 0: chosen from the batch size at bind; 1 / 2: forced (tuning knob)
+  int tp_rank = 0, tp_size = 1;  // tensor parallel: this engine's share of one observation
+  unsigned int tp_base = 0;      // arrivals per exchange counter consumed by earlier launches of this binding
+  float* tp_peer_recv[MAX_TP] = {};
+  unsigned int* tp_peer_flags[MAX_TP] = {};
+  void* tp_opened[MAX_TP] = {};  // base addresses opened with cudaIpcOpenMemHandle (closed at destroy)
+  pi05_tuning tune;              // every tuning setting (pi05_tune); defaults from pi05_tuning_defaults
   int gn = 1;                    // observations per MMA of the bound batch
-  int entries_per_phase = 0;     // throughput schedule: K splits aim at this many entries per CTA and phase (0: by batch size; tuning knob)
-  int grouped_from = 3, streams_from = 5;   // batch sizes from which the throughput schedule / its two streams are used (tuning knobs)
-  bool two_streams = true;       // throughput schedule as two streams of groups half a pass apart (tuning knob PI05_ONE_STREAM: off)
   int stream_split = 0;          // groups in the first stream (0: one stream)
-  bool balanced = true;          // several observations: the throughput schedule (tuning knob PI05_LATENCY_SCHEDULE: off)
   int max_stage = 0x7fffffff;
   int drop_event = -1;
-  int poll_ns = 20;
   long long wait_limit = 4000000000ll;    // ~2 s of SM clocks
   unsigned long long launches = 0;
+  cudaEvent_t done = nullptr;    // recorded after this handle's last launch, on that launch's stream
+  cudaStream_t side = nullptr;   // non-blocking stream for the few bytes pi05_status moves (never the legacy default stream,
+                                 // which would serialise against every other stream of the GPU)
+  bool in_flight = false;        // a launch has been issued since the last pi05_status
+  bool can_cluster = false;      // the device takes the whole grid as clusters of two
   std::string config;
   std::string last_error;
 };
@@ -197,6 +220,10 @@ void build_layout(pi05_engine* h) {
   add("d_acc", B * T * W * 4);
   add("act", B * T * FF * 2);
   add("att_part", (size_t)(MAX_KEY_GROUPS - 1) * NROW_CTAS * ATT_PART_FLOATS * 4);
+  if (h->tp_size > 1) {          // what the peers write into (see pi05_common.cuh)
+    add("tp_recv", (size_t)2 * h->tp_size * TP_SLOT_FLOATS * 4);
+    add("tp_flags", (size_t)2 * NROW_CTAS * TP_FLAG_STRIDE * 4);
+  }
   add("page_table", (size_t)h->max_batch * ((h->max_prefix + 63) / 64) * sizeof(int));
   add("sched", (size_t)h->grid * MAX_UNITS * sizeof(Unit));
   add("sched_n", (size_t)h->grid * sizeof(int));
@@ -219,8 +246,29 @@ Tp* region_ptr(const pi05_engine* h, const char* name) {
 //   gate/up: 64 tiles (64 gate rows + the matching 64 up rows), full K, one per CTA 0..63
 //   QKV:     16 q tiles x 4 K parts on the gate/up CTAs, 4 k / v tiles x full K on CTAs 64..67
 //   O, down: 8 row tiles each, K split in contiguous runs over all GEMM CTAs (partial sums meet in L2)
+// Tensor parallel (rank r of n): the same lists restricted to this rank's share - query heads 8 r / n .. (wq rows, and
+// the matching K range of wo), MLP columns 4096 r / n .. (wg / wu rows, K range of wd) - with the single KV head's k / v
+// tiles on every rank (reference/pi05.py:254-265 and 268-279 are what gets cut).
 bool schedule_one(pi05_engine* h, std::vector<std::vector<Unit>>& per) {
   const int ng = h->n_gemm;
+  if (h->tp_size > 1) {
+    const int n = h->tp_size, r = h->tp_rank;
+    for (int u = 0; u < NKVTILES; ++u) per[64 + u].push_back(Unit{G_QKV, 16 + u, 0, W / KSTAGE});
+    const int qt = 16 / n, gt = 64 / n;                       // q tiles and gate/up tiles of this rank
+    for (int u = 0; u < qt * 4; ++u) per[u].push_back(Unit{G_QKV, r * qt + u / 4, (u % 4) * 2, 2});
+    const int per_tile = ng / (W / 128);
+    auto split = [&](int gemm, int tiles, int stage0, int stages) {
+      for (int t = 0; t < tiles; ++t)
+        for (int j = 0; j < per_tile; ++j) {
+          const int a0 = stages * j / per_tile, a1 = stages * (j + 1) / per_tile;
+          if (a1 > a0) per[t * per_tile + j].push_back(Unit{gemm, t, stage0 + a0, a1 - a0});
+        }
+    };
+    split(G_O, W / 128, r * (QD / KSTAGE / n), QD / KSTAGE / n);
+    for (int u = 0; u < gt; ++u) per[u].push_back(Unit{G_GU, r * gt + u, 0, W / KSTAGE});
+    split(G_DOWN, W / 128, r * (FF / KSTAGE / n), FF / KSTAGE / n);
+    return true;
+  }
   // QKV: the 4 k / v tiles over the full K on CTAs 64..67 (BF16 keys / values with RoPE straight from the epilogue);
   // the 16 q tiles in 4 two-stage K parts, one on each gate/up CTA (FP32 sums, finished by attention)
   for (int u = 0; u < NKVTILES; ++u) per[64 + u].push_back(Unit{G_QKV, 16 + u, 0, W / KSTAGE});
@@ -270,7 +318,7 @@ bool schedule_groups(pi05_engine* h, std::vector<std::vector<Unit>>& per, int ng
   const int phase_groups = h->stream_split > 0 ? h->stream_split : ngroups;
   // entries per CTA and phase to aim for: one from eight observations on (measured: B = 8 11.0 against 11.8 ms per
   // launch; at B = 16 both give the same splits once O and down keep two parts), two below
-  const int per_phase = h->entries_per_phase > 0 ? h->entries_per_phase : h->batch >= 8 ? 1 : 2;
+  const int per_phase = h->tune.entries_per_phase > 0 ? h->tune.entries_per_phase : h->batch >= 8 ? 1 : 2;
   auto parts_for = [&](int ntiles, int stages) {
     const int want = (per_phase * ng + ntiles * phase_groups / 2) / (ntiles * phase_groups);
     return std::max(1, std::min(stages, want));
@@ -311,12 +359,16 @@ bool schedule_groups(pi05_engine* h, std::vector<std::vector<Unit>>& per, int ng
   return true;
 }
 
+// Fewest GEMM CTAs any schedule works with: the 64 gate/up tiles of the one-observation schedule plus one CTA per
+// row tile of the O / down projections.  plan_batch sheds groups of row CTAs until this many are left.
+constexpr int MIN_GEMM_CTAS = 64 + 8;
+
 bool build_schedule(pi05_engine* h, int ngroups = 1) {
   const int ng = h->n_gemm;
-  const bool grouped = h->batch >= h->grouped_from && h->balanced;   // two observations still do best on the latency schedule
+  const bool grouped = h->batch >= h->tune.grouped_from && !h->tune.latency_schedule;   // two observations still do best on the latency schedule
   // two streams of groups half a layer pass apart pay from five observations on (measured; below that they cost 1-2 %)
-  h->stream_split = grouped && h->two_streams && h->batch >= h->streams_from && ngroups >= 2 ? (ngroups + 1) / 2 : 0;
-  if (ng < 64 + 8) return false;
+  h->stream_split = grouped && h->tune.two_streams && h->batch >= h->tune.streams_from && ngroups >= 2 ? (ngroups + 1) / 2 : 0;
+  if (ng < MIN_GEMM_CTAS) return false;
   h->sched.assign((size_t)h->grid * MAX_UNITS, Unit{0, 0, 0, 0});
   h->sched_n.assign(h->grid, 0);
   std::vector<std::vector<Unit>> per(h->grid);
@@ -391,18 +443,26 @@ int encode_suffix_kv(pi05_engine* h, CUtensorMap* m, const void* base, uint64_t 
   return PI05_OK;
 }
 
-// Tuning variables (environment, read once per engine; not part of the interface).
-void read_knobs(pi05_engine* h) {
-  if (const char* e = getenv("PI05_POLL_NS")) h->poll_ns = atoi(e);
-  if (const char* e = getenv("PI05_OBS_PER_MMA")) {                   // tuning knob: 1 or 2 observations per MMA
-    const int v = atoi(e);
-    if (v == 1 || v == 2) h->obs_per_mma = v;
-  }
-  if (getenv("PI05_ONE_STREAM")) h->two_streams = false;             // tuning knob
-  if (const char* e = getenv("PI05_ENTRIES_PER_PHASE")) h->entries_per_phase = std::max(1, std::min(atoi(e), 8));   // tuning knob
-  if (const char* e = getenv("PI05_GROUPED_FROM")) h->grouped_from = std::max(2, atoi(e));   // tuning knob
-  if (const char* e = getenv("PI05_STREAMS_FROM")) h->streams_from = std::max(2, atoi(e));   // tuning knob
-  if (getenv("PI05_LATENCY_SCHEDULE")) h->balanced = false;          // tuning knob: the one-observation schedule for batches too
+void default_tuning(pi05_tuning* t) {
+  memset(t, 0, sizeof *t);
+  t->poll_ns = 20;
+  t->two_streams = 1;
+  t->grouped_from = 3;
+  t->streams_from = 5;
+  t->clusters = 1;
+}
+
+// Clamp a caller's settings to what the engine implements.
+pi05_tuning checked_tuning(const pi05_tuning& in) {
+  pi05_tuning t = in;
+  t.poll_ns = std::max(0, std::min(t.poll_ns, 10000));
+  if (t.obs_per_mma != 1 && t.obs_per_mma != 2) t.obs_per_mma = 0;
+  t.entries_per_phase = std::max(0, std::min(t.entries_per_phase, 8));
+  t.grouped_from = std::max(2, t.grouped_from);
+  t.streams_from = std::max(2, t.streams_from);
+  t.key_groups = std::max(0, std::min(t.key_groups, (int)MAX_KEY_GROUPS));
+  t.row_groups = std::max(0, std::min(t.row_groups, 3));
+  return t;
 }
 
 // Everything the engine decides when it learns the batch and the prefix length: groups of row CTAs (or of keys),
@@ -415,29 +475,29 @@ bool plan_batch(pi05_engine* h, int batch, int prefix_len) {
   const int chunks = (prefix_len + 63) / 64 + 1;
   // (measured with the two-stream schedule: three groups beat two by 5-11 % at B = 5..7 and lose 4 % at B = 4)
   int groups = batch >= 5 ? 3 : batch >= 2 ? 2 : (chunks >= 8 ? 3 : chunks >= 6 ? 2 : 1);
-  if (const char* kg = getenv("PI05_KEY_GROUPS")) { if (batch == 1) groups = std::max(1, std::min(atoi(kg), (int)MAX_KEY_GROUPS)); }   // tuning knob
-  if (const char* rg = getenv("PI05_ROW_GROUPS")) { if (batch > 1) groups = std::max(1, std::min(atoi(rg), 3)); }   // tuning knob
-  while (groups > 1 && h->grid - groups * NROW_CTAS < 64 + NKVTILES) --groups;
+  if (batch == 1 && h->tune.key_groups > 0) groups = h->tune.key_groups;
+  if (batch > 1 && h->tune.row_groups > 0) groups = h->tune.row_groups;
+  while (groups > 1 && h->grid - groups * NROW_CTAS < MIN_GEMM_CTAS) --groups;
   h->row_groups = batch > 1 ? groups : 1;
   h->key_groups = batch > 1 ? 1 : groups;
   h->n_gemm = h->grid - groups * NROW_CTAS;
-  h->gn = batch == 1 ? 1 : h->obs_per_mma ? h->obs_per_mma : batch >= PI05_PAIRS_FROM ? 2 : 1;
+  h->gn = batch == 1 ? 1 : h->tune.obs_per_mma ? h->tune.obs_per_mma : batch >= PI05_PAIRS_FROM ? 2 : 1;
   return build_schedule(h, (batch + h->gn - 1) / h->gn);
 }
 
 // The engine's description for the caller's records: geometry of the launch and the schedule of the bound batch.
 void describe(pi05_engine* h) {
   char buf[1280];
-  const bool grouped = h->batch >= h->grouped_from && h->balanced;
+  const bool grouped = h->batch >= h->tune.grouped_from && !h->tune.latency_schedule;
   snprintf(buf, sizeof buf,
            "{\"kernel\": \"pi05_chunk_kernel\", \"arch\": \"sm_100a\", \"launches_per_chunk\": 1, \"grid\": %d, "
            "\"threads\": %d, \"smem_bytes\": %d, \"gemm_ctas\": %d, \"row_ctas\": %d, \"stages\": %d, "
            "\"stage_bytes\": %d, \"units\": {\"qkv\": %d, \"o\": %d, \"gate_up\": %d, \"down\": %d}, "
            "\"mma\": \"tcgen05 cta_group::1 M128 N%d K16 bf16\", \"sync\": \"device-scope counters, bounded waits\", "
-           "\"clusters_of_2\": %s, \"observations_per_mma\": %d, \"schedule\": \"%s\"}",
+           "\"clusters_of_2\": %s, \"observations_per_mma\": %d, \"tp_rank\": %d, \"tp_size\": %d, \"schedule\": \"%s\"}",
            h->grid, THREADS, SMEM_BYTES, h->n_gemm, h->grid - h->n_gemm, h->gn == 1 ? NSTG : 3,
            W_STAGE_BYTES + h->gn * A_STAGE_BYTES, h->n_units[0], h->n_units[1], h->n_units[2], h->n_units[3], 64 * h->gn,
-           h->clustered ? "true" : "false", h->gn,
+           h->clustered ? "true" : "false", h->gn, h->tp_rank, h->tp_size,
            !grouped ? "one observation (units serve every observation in turn)"
                     : h->stream_split > 0 ? "throughput, two streams of groups half a layer pass apart"
                                           : "throughput, one stream");
@@ -472,7 +532,8 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   if (device < 0 || max_prefix < 1 || max_prefix > 4096 || max_batch < 1 || tp_size < 1 || tp_rank < 0 ||
       tp_rank >= tp_size)
     return PI05_ERR_ARGUMENT;
-  if (max_batch > MAXB || tp_size != 1) return PI05_ERR_UNSUPPORTED;
+  if (max_batch > MAXB) return PI05_ERR_UNSUPPORTED;
+  if (tp_size != 1 && !((tp_size == 2 || tp_size == 4 || tp_size == 8) && max_batch == 1)) return PI05_ERR_UNSUPPORTED;
   int ndev = 0;
   if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) { cudaGetLastError(); return PI05_ERR_NO_DEVICE; }
   if (device >= ndev) return PI05_ERR_ARGUMENT;
@@ -488,9 +549,11 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   h->n_gemm = h->grid - NROW_CTAS;
   h->max_prefix = max_prefix;
   h->max_batch = max_batch;
+  h->tp_rank = tp_rank;
+  h->tp_size = tp_size;
+  default_tuning(&h->tune);
   if (!build_schedule(h)) { delete h; return PI05_ERR_UNSUPPORTED; }
   build_layout(h);
-  read_knobs(h);
   DeviceGuard guard(device);
   if (!guard.ok) { delete h; return PI05_ERR_CUDA; }
   cudaError_t e = cudaSuccess;
@@ -505,8 +568,8 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
   {
     // Clusters of two CTAs when the whole grid fits that way: the kernel uses no cluster feature, but the launch then
     // places consecutive blocks on the two SMs of a TPC, which measured ~1 % faster than the plain cooperative
-    // launch's placement.  PI05_NO_CLUSTER (a tuning knob) selects the plain launch.
-    bool want = (h->grid % 2 == 0) && getenv("PI05_NO_CLUSTER") == nullptr;
+    // launch's placement.  The tuning setting `clusters = 0` selects the plain launch.
+    bool want = h->grid % 2 == 0;
     for (const void* kern : kAllKernels) {
       if (!want) break;
       cudaLaunchAttribute attr;
@@ -522,11 +585,30 @@ int pi05_create(int device, int max_prefix, int max_batch, int tp_rank, int tp_s
         want = false;
       }
     }
+    h->can_cluster = want;
     h->clustered = want;
-    if (const char* pm = getenv("PI05_CTA_PERM")) h->cta_perm = atoi(pm) != 0 && h->grid % 2 == 0;   // tuning knob
   }
+  // marks the end of this handle's last launch: pi05_status and a re-bind wait for it instead of for the whole device
+  e = cudaEventCreateWithFlags(&h->done, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->side, cudaStreamNonBlocking);
+  if (e != cudaSuccess) { cudaGetLastError(); if (h->done) cudaEventDestroy(h->done); delete h; return PI05_ERR_CUDA; }
   describe(h);
   *out = h;
+  return PI05_OK;
+}
+
+int pi05_tuning_defaults(pi05_tuning* t) {
+  if (!t) return PI05_ERR_ARGUMENT;
+  default_tuning(t);
+  return PI05_OK;
+}
+
+int pi05_tune(pi05_handle_t h, const pi05_tuning* t) {
+  if (!valid_handle(h) || !t) return PI05_ERR_ARGUMENT;
+  h->tune = checked_tuning(*t);
+  h->clustered = h->can_cluster && h->tune.clusters != 0;
+  h->bound = false;              // the schedule and the launch shape are chosen at bind
+  describe(h);
   return PI05_OK;
 }
 
@@ -602,6 +684,11 @@ int pi05_bind_view(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], c
   DeviceGuard guard(h->device);
   if (!guard.ok) return PI05_ERR_CUDA;
   h->bound = false;
+  if (h->in_flight) {
+    // a launch of this handle may still be running out of the workspace that is about to be cleared and re-described
+    cudaError_t e = cudaEventSynchronize(h->done);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaEventSynchronize", e);
+  }
   for (int i = 0; i < PI05_NUM_INPUTS; ++i) h->inputs[i] = inputs[i];
   h->inputs[22] = kv->k; h->inputs[23] = kv->v;
   h->pages_per_obs = kv->pages_per_obs;
@@ -610,6 +697,7 @@ int pi05_bind_view(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], c
   h->ws = static_cast<uint8_t*>(workspace);
   h->prefix = prefix_len;
   h->batch = batch;
+  h->tp_base = 0;                 // the workspace, counters included, is cleared below
   if (!plan_batch(h, batch, prefix_len)) { h->last_error = "no schedule for this GPU"; return PI05_ERR_UNSUPPORTED; }
   describe(h);
   cudaError_t e = cudaMemset(workspace, 0, h->ws_bytes);
@@ -630,6 +718,8 @@ int pi05_bind_view(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], c
   if ((rc = encode_2d(h, &h->maps.an_ffn, region_ptr<void>(h, "an_ffn"), W, (uint64_t)T * batch * AN_COPIES, A_BOX_ROWS))) return rc;
   if ((rc = encode_2d(h, &h->maps.attn, region_ptr<void>(h, "attn"), QD, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
   if ((rc = encode_2d(h, &h->maps.act, region_ptr<void>(h, "act"), FF, (uint64_t)T * batch, A_BOX_ROWS))) return rc;
+  if ((rc = encode_suffix_kv(h, &h->maps.sk, region_ptr<void>(h, "k"), (uint64_t)batch))) return rc;
+  if ((rc = encode_suffix_kv(h, &h->maps.sv, region_ptr<void>(h, "v"), (uint64_t)batch))) return rc;
   {
     // full pages, and the last page of an observation cut at its last valid token
     const uint64_t full_rows = (uint64_t)kv->page_tokens;
@@ -644,8 +734,6 @@ int pi05_bind_view(pi05_handle_t h, const void* const inputs[PI05_NUM_INPUTS], c
                           (uint64_t)kv->layer_stride, (uint64_t)kv->page_stride))) return rc;
     }
   }
-  if ((rc = encode_suffix_kv(h, &h->maps.sk, region_ptr<void>(h, "k"), (uint64_t)batch))) return rc;
-  if ((rc = encode_suffix_kv(h, &h->maps.sv, region_ptr<void>(h, "v"), (uint64_t)batch))) return rc;
   e = cudaMemcpy(region_ptr<void>(h, "page_table"), kv->page_table, (size_t)batch * kv->pages_per_obs * sizeof(int),
                  cudaMemcpyHostToDevice);
   if (e != cudaSuccess) return fail_cuda(h, "cudaMemcpy(page table)", e);
@@ -715,13 +803,24 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   p.att_part = region_ptr<float>(h, "att_part");
   p.page_table = region_ptr<int>(h, "page_table");
   p.pages_per_obs = h->pages_per_obs; p.page_tokens = h->page_tokens;
+  p.tp_rank = h->tp_rank; p.tp_size = h->tp_size; p.tp_base = h->tp_base;
+  if (h->tp_size > 1) {
+    p.tp_recv = region_ptr<float>(h, "tp_recv");
+    p.tp_flags = region_ptr<unsigned int>(h, "tp_flags");
+    for (int r = 0; r < h->tp_size; ++r) {
+      if (r == h->tp_rank) continue;
+      if (!h->tp_peer_recv[r]) { h->last_error = "tensor parallel: peer " + std::to_string(r) + " is not attached"; return PI05_ERR_NOT_BOUND; }
+      p.tp_peer_recv[r] = h->tp_peer_recv[r];
+      p.tp_peer_flags[r] = h->tp_peer_flags[r];
+    }
+  }
   p.drop_event = h->drop_event;
-  p.poll_ns = h->poll_ns;
+  p.poll_ns = h->tune.poll_ns;
   for (int g = 0; g < 4; ++g) p.n_units[g] = h->n_units[g];
-  p.cta_perm = h->cta_perm;
+  p.cta_perm = h->tune.cta_perm && h->grid % 2 == 0 ? 1 : 0;
   // the throughput schedule runs the O units of every group before any gate/up unit, so the row CTAs do all their
   // attentions first; the latency schedule interleaves the residual of one observation with the attention of the next
-  p.row_order = h->batch >= h->grouped_from && h->balanced ? 1 : 0;
+  p.row_order = h->batch >= h->tune.grouped_from && !h->tune.latency_schedule ? 1 : 0;
   p.stream_split = h->stream_split;
   const double dt = -1.0 / NS;
   for (int s = 0; s < NS; ++s) p.t_steps[s] = (float)(1.0 + s * dt);
@@ -732,15 +831,20 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   // there are several (a weight stage in shared memory then serves all of them)
   const bool debug = stamps != nullptr || h->max_stage != 0x7fffffff || h->drop_event >= 0;
   const int gn = h->gn;
+  if (debug && h->tp_size > 1) {
+    h->last_error = "stamps and debug controls are not available in a tensor-parallel engine";
+    return PI05_ERR_UNSUPPORTED;
+  }
   if (debug && h->stream_split > 0 && (h->max_stage != 0x7fffffff)) {
-    h->last_error = "the stage limit is not available with the two-stream schedule of a batch (create the engine with PI05_ONE_STREAM set)";
+    h->last_error = "the stage limit is not available with the two-stream schedule of a batch (tune the engine with two_streams = 0)";
     return PI05_ERR_UNSUPPORTED;
   }
   if (debug && gn != 1) {   // the traced build runs one observation per MMA; the bound schedule is for groups of gn
-    h->last_error = "stamps and debug controls need one observation per MMA (PI05_OBS_PER_MMA unset or 1 when the engine is created)";
+    h->last_error = "stamps and debug controls need one observation per MMA (tuning setting obs_per_mma 0 or 1)";
     return PI05_ERR_UNSUPPORTED;
   }
   const void* kern = debug ? (const void*)k_traced::pi05_chunk_kernel
+                     : h->tp_size > 1 ? (const void*)k_tp::pi05_chunk_kernel
                      : h->batch == 1 ? (const void*)k_plain::pi05_chunk_kernel
                      : gn == 2 ? (const void*)k_pairs::pi05_chunk_kernel
                                : (const void*)k_batched::pi05_chunk_kernel;
@@ -761,6 +865,27 @@ int pi05_launch(pi05_handle_t h, int n_steps, int n_layers, void* stream, unsign
   }
   if (e != cudaSuccess) return fail_cuda(h, "kernel launch", e);
   h->launches++;
+  h->tp_base += (unsigned)((h->tp_size - 1) * n_steps * n_layers);   // two exchanges per layer pass, one counter each
+  e = cudaEventRecord(h->done, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail_cuda(h, "cudaEventRecord", e);
+  h->in_flight = true;
+  return PI05_OK;
+}
+
+// Reads (and, when set, clears) the status word of a handle whose last launch has completed.
+static int read_status(pi05_engine* h, int* code, int* where) {
+  unsigned int st[2] = {0, 0};
+  cudaError_t e = cudaMemcpyAsync(st, h->ws, sizeof st, cudaMemcpyDeviceToHost, h->side);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(h->side);
+  if (e != cudaSuccess) return fail_cuda(h, "copy of the status word", e);
+  *code = (int)st[0];
+  *where = (int)st[1];
+  if (st[0]) {
+    e = cudaMemsetAsync(h->ws, 0, CTRL_BYTES, h->side);   // status and every counter: the next launch starts clean
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->side);
+    if (e != cudaSuccess) return fail_cuda(h, "clearing of the status word", e);
+    return PI05_ERR_DEVICE_TIMEOUT;
+  }
   return PI05_OK;
 }
 
@@ -769,19 +894,11 @@ int pi05_status(pi05_handle_t h, int* code, int* where) {
   if (!h->ws) return PI05_ERR_NOT_BOUND;
   DeviceGuard guard(h->device);
   if (!guard.ok) return PI05_ERR_CUDA;
-  cudaError_t e = cudaDeviceSynchronize();
-  if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceSynchronize", e);
-  unsigned int st[2] = {0, 0};
-  e = cudaMemcpy(st, h->ws, sizeof st, cudaMemcpyDeviceToHost);
-  if (e != cudaSuccess) return fail_cuda(h, "cudaMemcpy(status)", e);
-  *code = (int)st[0];
-  *where = (int)st[1];
-  if (st[0]) {
-    e = cudaMemset(h->ws, 0, CTRL_BYTES);   // status and every counter: the next launch starts clean
-    if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(status)", e);
-    return PI05_ERR_DEVICE_TIMEOUT;
-  }
-  return PI05_OK;
+  // wait for this handle's last launch only (other handles and streams of the GPU keep running)
+  cudaError_t e = h->in_flight ? cudaEventSynchronize(h->done) : cudaSuccess;
+  if (e != cudaSuccess) return fail_cuda(h, "cudaEventSynchronize", e);
+  h->in_flight = false;
+  return read_status(h, code, where);
 }
 
 int pi05_workspace_region(pi05_handle_t h, const char* name, size_t* offset, size_t* bytes) {
@@ -793,15 +910,23 @@ int pi05_workspace_region(pi05_handle_t h, const char* name, size_t* offset, siz
   return PI05_OK;
 }
 
-int pi05_schedule_plan(int sms, int batch, int prefix_len, int* entries, int capacity, int* count,
-                       int info[PI05_PLAN_INFO]) {
+int pi05_schedule_plan(int sms, int batch, int prefix_len, const pi05_tuning* tuning, int* entries, int capacity,
+                       int* count, int info[PI05_PLAN_INFO]) {
+  return pi05_schedule_plan_tp(sms, batch, prefix_len, 0, 1, tuning, entries, capacity, count, info);
+}
+
+int pi05_schedule_plan_tp(int sms, int batch, int prefix_len, int tp_rank, int tp_size, const pi05_tuning* tuning,
+                          int* entries, int capacity, int* count, int info[PI05_PLAN_INFO]) {
   if (sms < 1 || sms > 1024 || batch < 1 || batch > MAXB || prefix_len < 1 || capacity < 0 || (capacity > 0 && !entries) ||
-      !count || !info)
+      !count || !info || tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size)
     return PI05_ERR_ARGUMENT;
+  if (tp_size != 1 && !((tp_size == 2 || tp_size == 4 || tp_size == 8) && batch == 1)) return PI05_ERR_UNSUPPORTED;
   pi05_engine h;                 // host-side state only: nothing here touches a device
   h.grid = sms;
   h.n_gemm = sms - NROW_CTAS;
-  read_knobs(&h);
+  h.tp_rank = tp_rank; h.tp_size = tp_size;
+  default_tuning(&h.tune);
+  if (tuning) h.tune = checked_tuning(*tuning);
   if (h.n_gemm < 1 || !plan_batch(&h, batch, prefix_len)) return PI05_ERR_UNSUPPORTED;
   info[0] = h.n_gemm; info[1] = h.row_groups; info[2] = h.key_groups; info[3] = h.gn;
   info[4] = (batch + h.gn - 1) / h.gn; info[5] = h.stream_split;
@@ -819,6 +944,82 @@ int pi05_schedule_plan(int sms, int batch, int prefix_len, int* entries, int cap
   return PI05_OK;
 }
 
+// ---- tensor parallel: how the ranks learn where each other's receive buffers are
+namespace {
+struct TpHandle {                 // what pi05_tp_export writes: PI05_TP_HANDLE_BYTES
+  cudaIpcMemHandle_t ipc;         // the allocation that holds the workspace
+  unsigned long long offset;      // of the workspace inside that allocation
+  unsigned long long ws_bytes;
+};
+static_assert(sizeof(TpHandle) <= PI05_TP_HANDLE_BYTES, "handle size");
+
+int tp_attach_at(pi05_engine* h, int peer, uint8_t* peer_ws) {
+  const Region* recv = find_region(h, "tp_recv");
+  const Region* flags = find_region(h, "tp_flags");
+  if (!recv || !flags) return PI05_ERR_UNSUPPORTED;
+  h->tp_peer_recv[peer] = reinterpret_cast<float*>(peer_ws + recv->off);
+  h->tp_peer_flags[peer] = reinterpret_cast<unsigned int*>(peer_ws + flags->off);
+  return PI05_OK;
+}
+}  // namespace
+
+int pi05_tp_export(pi05_handle_t h, void* out, size_t out_bytes) {
+  if (!valid_handle(h) || !out || out_bytes < PI05_TP_HANDLE_BYTES) return PI05_ERR_ARGUMENT;
+  if (h->tp_size < 2) return PI05_ERR_UNSUPPORTED;
+  if (!h->bound) return PI05_ERR_NOT_BOUND;
+  DeviceGuard guard(h->device);
+  if (!guard.ok) return PI05_ERR_CUDA;
+  TpHandle th;
+  memset(&th, 0, sizeof th);
+  // the workspace may sit anywhere inside a larger allocation of the caller's allocator: export that allocation and
+  // the offset
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || !fn) {
+    h->last_error = "cuMemGetAddressRange is not available from this driver";
+    return PI05_ERR_CUDA;
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (reinterpret_cast<RangeFn>(fn)(&base, &size, reinterpret_cast<CUdeviceptr>(h->ws)) != CUDA_SUCCESS) {
+    h->last_error = "cuMemGetAddressRange failed on the workspace";
+    return PI05_ERR_CUDA;
+  }
+  cudaError_t e = cudaIpcGetMemHandle(&th.ipc, reinterpret_cast<void*>(base));
+  if (e != cudaSuccess) return fail_cuda(h, "cudaIpcGetMemHandle(workspace)", e);
+  th.offset = reinterpret_cast<CUdeviceptr>(h->ws) - base;
+  th.ws_bytes = h->ws_bytes;
+  memset(out, 0, PI05_TP_HANDLE_BYTES);
+  memcpy(out, &th, sizeof th);
+  return PI05_OK;
+}
+
+int pi05_tp_attach(pi05_handle_t h, int peer_rank, const void* exported) {
+  if (!valid_handle(h) || !exported) return PI05_ERR_ARGUMENT;
+  if (h->tp_size < 2) return PI05_ERR_UNSUPPORTED;
+  if (peer_rank < 0 || peer_rank >= h->tp_size || peer_rank == h->tp_rank) return PI05_ERR_ARGUMENT;
+  TpHandle th;
+  memcpy(&th, exported, sizeof th);
+  if (th.ws_bytes != h->ws_bytes) { h->last_error = "the peer's workspace has another layout"; return PI05_ERR_ARGUMENT; }
+  DeviceGuard guard(h->device);
+  if (!guard.ok) return PI05_ERR_CUDA;
+  if (h->tp_opened[peer_rank]) { cudaIpcCloseMemHandle(h->tp_opened[peer_rank]); h->tp_opened[peer_rank] = nullptr; }
+  void* base = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&base, th.ipc, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail_cuda(h, "cudaIpcOpenMemHandle(peer workspace)", e);
+  h->tp_opened[peer_rank] = base;
+  return tp_attach_at(h, peer_rank, static_cast<uint8_t*>(base) + th.offset);
+}
+
+int pi05_tp_attach_pointer(pi05_handle_t h, int peer_rank, void* peer_workspace) {
+  if (!valid_handle(h) || !peer_workspace) return PI05_ERR_ARGUMENT;
+  if (h->tp_size < 2) return PI05_ERR_UNSUPPORTED;
+  if (peer_rank < 0 || peer_rank >= h->tp_size || peer_rank == h->tp_rank) return PI05_ERR_ARGUMENT;
+  return tp_attach_at(h, peer_rank, static_cast<uint8_t*>(peer_workspace));
+}
+
 const char* pi05_config_json(pi05_handle_t h) { return valid_handle(h) ? h->config.c_str() : "{}"; }
 
 int pi05_launch_count(pi05_handle_t h, unsigned long long* count) {
@@ -829,6 +1030,13 @@ int pi05_launch_count(pi05_handle_t h, unsigned long long* count) {
 
 int pi05_destroy(pi05_handle_t h) {
   if (!valid_handle(h)) return PI05_ERR_ARGUMENT;
+  if (h->done) {
+    DeviceGuard guard(h->device);
+    cudaEventDestroy(h->done);
+    if (h->side) cudaStreamDestroy(h->side);
+    for (int r = 0; r < MAX_TP; ++r)
+      if (h->tp_opened[r]) cudaIpcCloseMemHandle(h->tp_opened[r]);
+  }
   delete h;
   return PI05_OK;
 }
@@ -889,10 +1097,26 @@ extern "C" int pi05_chunk_static(int device, const void* const inputs[PI05_NUM_I
     slot.scratch = ptr;
     slot.bound = false;
   }
+  if (slot.h->in_flight) {
+    // An earlier call whose kernel has finished by now: look at the status word it left before this call clears it.
+    // (A kernel whose bounded wait gave up fills its actions with NaN and leaves a code here; this is where the caller
+    // of this entry point learns of it.  A call that is still running is not waited for.)
+    DeviceGuard guard(device);
+    if (!guard.ok) return PI05_ERR_CUDA;
+    if (cudaEventQuery(slot.h->done) == cudaSuccess) {
+      slot.h->in_flight = false;
+      int code = 0, where = 0;
+      const int rc = read_status(slot.h, &code, &where);
+      if (rc != PI05_OK) return rc;
+    } else {
+      cudaGetLastError();
+    }
+  }
   bool same = slot.bound && slot.prefix == prefix_len && slot.actions == actions;
   for (int i = 0; same && i < PI05_NUM_INPUTS; ++i) same = slot.inputs[i] == inputs[i];
   if (!same) {
-    // New tensors or a new prefix length: re-encode the TMA descriptors and clear the scratch (synchronises the device).
+    // New tensors or a new prefix length: re-encode the TMA descriptors and clear the scratch.  The bind first waits
+    // for the last launch out of this array (whatever stream it is on) and synchronises the device at its end.
     slot.bound = false;
     int rc = pi05_bind(slot.h, inputs, prefix_len, 1, actions, slot.scratch, (size_t)PI05_STATIC_SCRATCH_BYTES);
     if (rc != PI05_OK) return rc;

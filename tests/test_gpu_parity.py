@@ -267,6 +267,8 @@ def test_wait_that_runs_out_reports_and_engine_recovers(case128):
     with pytest.raises(_lib.EngineError) as info:
         arm.status()
     assert info.value.code == _lib.ERR_DEVICE_TIMEOUT
+    # a chunk that gave up must not leave an earlier chunk's actions behind
+    assert bool(torch.isnan(arm.outputs()["actions"]).all())
     arm.debug(-1, WAIT_DEFAULT, -1)
     again = _run(arm)
     want, exact = O.chunk(cpu, ogeo, False, 1, 2), O.chunk(cpu, ogeo, True, 1, 2)

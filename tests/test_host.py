@@ -42,7 +42,8 @@ def test_argument_errors_never_touch_a_gpu(lib):
     assert lib.pi05_create(0, 0, 1, 0, 1, ctypes.byref(h)) == _lib.ERR_ARGUMENT
     assert lib.pi05_create(0, 128, 1, 2, 2, ctypes.byref(h)) == _lib.ERR_ARGUMENT
     assert lib.pi05_create(0, 128, 17, 0, 1, ctypes.byref(h)) == _lib.ERR_UNSUPPORTED
-    assert lib.pi05_create(0, 128, 1, 0, 2, ctypes.byref(h)) == _lib.ERR_UNSUPPORTED
+    assert lib.pi05_create(0, 128, 1, 0, 3, ctypes.byref(h)) == _lib.ERR_UNSUPPORTED     # 2, 4 or 8 ranks
+    assert lib.pi05_create(0, 128, 2, 0, 2, ctypes.byref(h)) == _lib.ERR_UNSUPPORTED     # one observation per launch
     n = ctypes.c_size_t()
     assert lib.pi05_workspace_bytes(None, ctypes.byref(n)) == _lib.ERR_ARGUMENT
     assert lib.pi05_launch(None, 10, 18, None, None) == _lib.ERR_ARGUMENT
@@ -151,8 +152,73 @@ def test_schedule_plan_invariants(lib, batch, prefix, monkeypatch):
 
 def test_schedule_plan_argument_errors(lib):
     count, info = ctypes.c_int(), (ctypes.c_int * _lib.PLAN_INFO)()
-    assert lib.pi05_schedule_plan(148, 0, 128, None, 0, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
-    assert lib.pi05_schedule_plan(148, 17, 128, None, 0, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
-    assert lib.pi05_schedule_plan(148, 1, 128, None, 4, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
-    assert lib.pi05_schedule_plan(148, 1, 128, None, 0, None, info) == _lib.ERR_ARGUMENT
-    assert lib.pi05_schedule_plan(60, 1, 128, None, 0, ctypes.byref(count), info) == _lib.ERR_UNSUPPORTED
+    assert lib.pi05_schedule_plan(148, 0, 128, None, None, 0, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
+    assert lib.pi05_schedule_plan(148, 17, 128, None, None, 0, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
+    assert lib.pi05_schedule_plan(148, 1, 128, None, None, 4, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
+    assert lib.pi05_schedule_plan(148, 1, 128, None, None, 0, None, info) == _lib.ERR_ARGUMENT
+    assert lib.pi05_schedule_plan(60, 1, 128, None, None, 0, ctypes.byref(count), info) == _lib.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("sms", list(range(132, 161, 2)))
+@pytest.mark.parametrize("batch,prefix", [(1, 128), (1, 968), (5, 128), (16, 128)])
+def test_schedule_plan_on_other_sm_counts(lib, sms, batch, prefix):
+    """Parts with a few SMs more or fewer than 148: the plan sheds groups of row CTAs until the GEMM side keeps the
+    fewest CTAs a schedule needs, instead of refusing."""
+    count, info = ctypes.c_int(), (ctypes.c_int * _lib.PLAN_INFO)()
+    assert lib.pi05_schedule_plan(sms, batch, prefix, None, None, 0, ctypes.byref(count), info) == _lib.OK
+    assert info[0] >= 72 and info[0] == sms - 25 * max(info[1], info[2])
+
+
+def test_tuning_defaults_and_clamping(lib):
+    t = _lib.Tuning()
+    assert lib.pi05_tuning_defaults(ctypes.byref(t)) == _lib.OK
+    assert (t.poll_ns, t.two_streams, t.grouped_from, t.streams_from, t.clusters) == (20, 1, 3, 5, 1)
+    assert lib.pi05_tuning_defaults(None) == _lib.ERR_ARGUMENT
+    assert lib.pi05_tune(None, ctypes.byref(t)) == _lib.ERR_ARGUMENT
+    # the plan follows the struct, not the environment
+    count, info = ctypes.c_int(), (ctypes.c_int * _lib.PLAN_INFO)()
+    t.two_streams = 0
+    assert lib.pi05_schedule_plan(148, 8, 128, ctypes.byref(t), None, 0, ctypes.byref(count), info) == _lib.OK
+    assert info[5] == 0
+    t.two_streams, t.row_groups = 1, 99          # out of range: clamped to 3
+    assert lib.pi05_schedule_plan(148, 8, 128, ctypes.byref(t), None, 0, ctypes.byref(count), info) == _lib.OK
+    assert info[5] == 4 and info[1] == 3
+
+
+@pytest.mark.parametrize("size", [2, 4, 8])
+def test_tensor_parallel_plans_partition_the_work(lib, size):
+    """The ranks' schedules together cover exactly the one-GPU schedule's work: the q tiles, the K range of the O
+    projection, the gate/up tiles and the K range of the down projection are cut into `size` disjoint shares, rank r
+    taking share r (heads 8 r / size .., MLP columns 4096 r / size ..); the k / v tiles run on every rank."""
+    cover: dict = {}
+    for rank in range(size):
+        entries, plan = _lib.schedule_plan(148, 1, 128, rank, size)
+        assert plan["gemm_ctas"] == 123
+        mine: dict = {}
+        for cta, gemm, lag, group, tile, k0, nk in entries:
+            assert lag == 0 and group == -1
+            for k in range(k0, k0 + nk):
+                mine.setdefault((gemm, tile), []).append(k)
+        for (gemm, tile), ks in mine.items():
+            assert len(ks) == len(set(ks))
+            if gemm == 0 and tile >= 16:
+                assert sorted(ks) == list(range(STAGES[0]))               # k / v: the whole K on every rank
+                continue
+            if gemm == 0:
+                assert tile // (16 // size) == rank and sorted(ks) == list(range(STAGES[0]))
+            elif gemm == 2:
+                assert tile // (64 // size) == rank and sorted(ks) == list(range(STAGES[2]))
+            else:
+                share = STAGES[gemm] // size
+                assert sorted(ks) == list(range(rank * share, (rank + 1) * share))
+            for k in ks:
+                assert (gemm, tile, k) not in cover
+                cover[(gemm, tile, k)] = rank
+        assert plan["units"]["qkv"] == 4 + (16 // size) * 4
+    for gemm in range(4):
+        tiles = 16 if gemm == 0 else TILES[gemm]
+        assert sum(1 for key in cover if key[0] == gemm) == tiles * STAGES[gemm]
+    count, info = ctypes.c_int(), (ctypes.c_int * _lib.PLAN_INFO)()
+    assert lib.pi05_schedule_plan_tp(148, 1, 128, 2, 2, None, None, 0, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
+    assert lib.pi05_schedule_plan_tp(148, 2, 128, 0, 2, None, None, 0, ctypes.byref(count), info) == _lib.ERR_UNSUPPORTED
+    assert lib.pi05_schedule_plan_tp(148, 1, 128, 0, 3, None, None, 0, ctypes.byref(count), info) == _lib.ERR_UNSUPPORTED

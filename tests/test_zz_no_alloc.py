@@ -43,9 +43,15 @@ def test_static_scratch_entry_matches_regular_entry_twice():
     slack = 2 * (O.ATOL + O.RTOL * float(regular.abs().max()))
     for call in range(2):
         actions.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.pi05_chunk_static(0, ptrs, geo.prefix, actions.data_ptr(), geo.steps, geo.layers, stream)
         assert rc == _lib.OK, lib.pi05_error_string(rc)
         torch.cuda.synchronize()
+        if call == 1:
+            # the defining property: nothing on this path takes device memory (the first call's set-up creates an event
+            # and a stream, which may cost the driver a little; the second call must cost nothing at all)
+            assert torch.cuda.mem_get_info()[0] == free_before
         got = actions.cpu()
         assert bool(torch.isfinite(got).all())
         assert float((got - regular).abs().max()) <= slack, call
@@ -57,3 +63,35 @@ def test_static_scratch_entry_matches_regular_entry_twice():
         == _lib.ERR_UNSUPPORTED
     assert lib.pi05_chunk_static(0, ptrs, 0, actions.data_ptr(), 10, 18, stream) == _lib.ERR_ARGUMENT
     assert lib.pi05_chunk_static(0, None, 128, actions.data_ptr(), 10, 18, stream) == _lib.ERR_ARGUMENT
+
+
+def test_static_scratch_entry_rebinds_behind_a_running_call():
+    """Two calls back to back on a non-blocking stream with different output buffers and prefix lengths: the second one
+    has to re-describe and clear the shared array, and must wait for the first one's kernel before it does.  Both
+    results are checked against the handle-based entry points."""
+    from pi05_megakernel_b200.arm import Pi05Arm
+    lib = _lib.load()
+    cases = []
+    for prefix, seed in ((128, FX.SEEDS[0]), (192, FX.SEEDS[1])):
+        geo = FX.Geometry(prefix=prefix)
+        cpu = FX.make_inputs(geo, seed, "cpu", "pad")
+        dev = {k: v.cuda() for k, v in cpu.items()}
+        arm = Pi05Arm(geo, "b200-s2-l4", "cuda")
+        arm.bind(dev)
+        arm.launch()
+        arm.status()
+        cases.append((geo, dev, arm.outputs()["actions"].clone()))
+        arm.close()
+    side = torch.cuda.Stream()
+    outs = [torch.full((50, 32), float("nan"), dtype=torch.float32, device="cuda") for _ in cases]
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        for (geo, dev, _), out in zip(cases, outs):
+            ptrs = (ctypes.c_void_p * _lib.NUM_INPUTS)(*[dev[k].data_ptr() for k in FX.ORDER])
+            rc = lib.pi05_chunk_static(0, ptrs, geo.prefix, out.data_ptr(), 2, 4, side.cuda_stream)
+            assert rc == _lib.OK, lib.pi05_error_string(rc)
+    side.synchronize()
+    for (geo, dev, regular), out in zip(cases, outs):
+        slack = 2 * (O.ATOL + O.RTOL * float(regular.abs().max()))
+        assert bool(torch.isfinite(out).all())
+        assert float((out - regular).abs().max()) <= slack, geo.prefix
