@@ -127,6 +127,60 @@ def stage_times(arm, flush) -> None:
     out["row_cta0_attention_pass1_us"] = {n: us(st[224 + i]) for i, n in enumerate(
         ["prefix_landed", "scores_done", "softmax_done", "pv_done", "stored", "signalled"])}
     print("stage_times " + json.dumps(out), file=sys.stderr, flush=True)
+    print(stage_table(out, arm.geo.prefix), file=sys.stderr, flush=True)
+
+
+def stage_table(t: dict, prefix: int) -> str:
+    """The seven stages of one layer pass (pass 1 of the stamped chunk) as a table: time, weight / cache bytes the stage
+    streams from HBM, achieved GB/s against the measured copy peak, and for the four GEMM stages the useful tensor
+    work against the measured BF16 peak (with the figure for the padded N = 64 MMAs beside it) and the share of the
+    stage during which the stamped CTA was issuing MMAs."""
+    peak_gbs, _ = measured_peaks()
+    peak_tf = 1672.7
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peak_tf = float(json.load(f).get("bf16_tflops", peak_tf))
+    p0, p1 = t["pass1_us"], t["pass2_us"]
+    gu, q = t.get("cta0_gate_up_pass1_us", {}), t.get("cta0_qkv_pass1_us", {})
+    W, QD, HD, FF, T = 1024, 2048, 256, 4096, 50
+    rows = {"QKV projection": (QD + 2 * HD, W), "O projection": (W, QD), "gate/up projection + GeGLU": (2 * FF, W),
+            "down projection": (W, FF)}
+    # stage boundaries as row CTA 0 and GEMM CTA 0 saw them; the QKV stage of pass 2 starts where pass 1 ended
+    spans = [("QKV projection", p0["residual_norm_2_done"], p1["qkv_seen"], "cta0_qkv_pass1_us"),
+             ("attention", p0["qkv_seen"], p0["attention_done"], None),
+             ("O projection", p0["attention_done"], p0["o_seen"], "cta0_o_pass1_us"),
+             ("gated residual + adaRMS", p0["o_seen"], p0["residual_norm_1_done"], None),
+             ("gate/up projection + GeGLU", p0["residual_norm_1_done"], gu.get("signalled"), "cta0_gate_up_pass1_us"),
+             ("down projection", gu.get("signalled"), p0["down_seen"], "cta0_down_pass1_us"),
+             ("gated residual + adaRMS (next norm)", p0["down_seen"], p0["residual_norm_2_done"], None)]
+    lines = ["| stage | us | HBM bytes | GB/s | of measured HBM peak | useful TFLOP/s (padded N=64) | of measured BF16 peak | MMA issue share of the stage |",
+             "|---|---|---|---|---|---|---|---|"]
+    total_us = total_b = 0.0
+    for name, a, b, cta in spans:
+        if a is None or b is None:
+            continue
+        us = b - a
+        if name in rows:
+            r, k = rows[name]
+            nbytes, flops = r * k * 2, 2.0 * T * r * k
+        elif name == "attention":
+            nbytes, flops = prefix * HD * 2 * 2, 4.0 * T * QD * (prefix + T)
+        else:
+            nbytes, flops = 2 * 3 * W * 4, 0.0
+        gbs = nbytes / us / 1e3
+        tf = flops / us / 1e6
+        share = ""
+        if cta and cta in t and t[cta].get("first_operands") and t[cta].get("mma_issued"):
+            share = f"{100 * (t[cta]['mma_issued'] - t[cta]['first_operands']) / us:.0f} %"
+        tcol = f"{tf:.1f} ({tf * 64 / T:.1f})" if name in rows else (f"{tf:.1f} (warp MMA)" if flops else "-")
+        lines.append(f"| {name} | {us:.2f} | {int(nbytes):,} | {gbs:.0f} | {100 * gbs / peak_gbs:.1f} % | {tcol} | "
+                     f"{(str(round(100 * tf / peak_tf, 2)) + ' %') if name in rows else '-'} | {share or '-'} |")
+        total_us += us
+        total_b += nbytes
+    lines.append(f"| one layer pass | {total_us:.2f} | {int(total_b):,} | {total_b / total_us / 1e3:.0f} | "
+                 f"{100 * total_b / total_us / 1e3 / peak_gbs:.1f} % | - | - | - |")
+    return "stage_table\n" + "\n".join(lines)
 
 
 def batch_sweep(args, device) -> None:
