@@ -631,7 +631,8 @@ __device__ __forceinline__ uint32_t att_bar(uint8_t* smem, int isv, int stage) {
 __device__ __forceinline__ bool att_wait(const Ctx& c, uint8_t* smem, AttBars& bars, int isv, int stage, int st) {
   const uint32_t bit = 1u << (8 * isv + stage);
   const bool ok = wait_mbar(c, att_bar(smem, isv, stage), (bars.parity & bit) ? 1u : 0u, WAIT_A_FULL, st);
-  if (ok) { bars.parity ^= bit; bars.pending &= ~bit; }   // a copy whose wait gave up stays marked for the drain at exit
+  bars.parity ^= bit;
+  bars.pending &= ~bit;
   return ok;
 }
 
@@ -739,9 +740,6 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
   const float NEG = -INFINITY;
 
   float m_lo = -1e30f, m_hi = -1e30f, l_lo = 0.f, l_hi = 0.f;
-  // A wait on a copy may give up in one thread and succeed in its neighbour.  Nobody leaves in the middle of a phase:
-  // the outcome is kept here and the whole CTA leaves together at the next CTA-wide barrier.
-  bool ok = true;
   uint32_t qf[QF_KEPT][4];
   float oa[4][4];
 #pragma unroll
@@ -767,7 +765,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
 #pragma unroll
     for (int j = 0; j < ATT_STAGES; ++j)
       if (j < early) {
-        ok = att_wait(issue.c, smem, bars, 0, j, wst) && ok;
+        if (!att_wait(issue.c, smem, bars, 0, j, wst)) return false;
         att_qk(qf, qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
       }
     if (early < nst) {
@@ -775,7 +773,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
 #pragma unroll
       for (int j = 0; j < ATT_STAGES; ++j)
         if (j >= early && j < nst) {
-          ok = att_wait(issue.c, smem, bars, 0, j, wst) && ok;
+          if (!att_wait(issue.c, smem, bars, 0, j, wst)) return false;
           att_qk(qf, qs, ptx::smem_u32(smem + OFF_KS + j * KV_STAGE_BYTES), warp, lane, sc[j]);
         }
     }
@@ -799,7 +797,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
     cm_hi = fmaxf(cm_hi, __shfl_xor_sync(0xffffffffu, cm_hi, 1));
     cm_hi = fmaxf(cm_hi, __shfl_xor_sync(0xffffffffu, cm_hi, 2));
     if (qd == 0) { red[warp * 16 + g] = cm_lo; red[warp * 16 + g + 8] = cm_hi; }
-    if (__syncthreads_or(ok ? 0 : 1)) return false;
+    __syncthreads();
     float mn_lo = m_lo, mn_hi = m_hi;
 #pragma unroll
     for (int w8 = 0; w8 < 8; ++w8) {
@@ -835,7 +833,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
 #pragma unroll
     for (int j = 0; j < ATT_STAGES; ++j) {
       if (j < nst) {
-        ok = att_wait(issue.c, smem, bars, 1, j, wst) && ok;
+        if (!att_wait(issue.c, smem, bars, 1, j, wst)) return false;
         const uint32_t vs = ptx::smem_u32(smem + OFF_VS + j * KV_STAGE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
@@ -856,7 +854,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
     if (tr && c0 == cbeg) p.stamps[227] = globaltimer();
     if (tr && c0 != cbeg && !more) p.stamps[235] = globaltimer();
     if (more) {
-      if (__syncthreads_or(ok ? 0 : 1)) return false;   // every warp is done with P and these value stages
+      __syncthreads();   // every warp is done with P and these value stages
       for (int j = 0; j < ATT_STAGES; ++j)
         if (!issue(c0 + ATT_STAGES + j, j, 2)) return false;
     }
@@ -864,7 +862,7 @@ __device__ bool attention_unit(const Params& p, const ObsPtrs& o, uint8_t* smem,
   // ---- normalise and store
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-  if (__syncthreads_or(ok ? 0 : 1)) return false;   // (red[] still holds the last maxima)
+  __syncthreads();   // red[] still holds the last maxima
   if (qd == 0) { red[warp * 16 + g] = l_lo; red[warp * 16 + g + 8] = l_hi; }
   __syncthreads();
   float tl_lo = 0.f, tl_hi = 0.f;

@@ -39,7 +39,7 @@ using namespace pi05;
 // batched kernels with one or two observations per MMA, and the traced kernel (one observation per MMA) for
 // callers that ask for stamps or debug controls.
 #ifndef PI05_QF_KEPT
-#define PI05_QF_KEPT 10
+#define PI05_QF_KEPT 8
 #endif
 namespace k_plain {
 #define PI05_TRACE 0
