@@ -297,3 +297,49 @@ def stages(v: dict, geo: Geo, step: int, layer: int, h_in: torch.Tensor) -> dict
         h = rb(h + rb(rb(d_acc) * gate_f))
         out["h_out"] = h
         return out
+
+
+# ------------------------------------------------------------------------------------------- prefix prefill
+def rms_gemma(x: torch.Tensor, weight: torch.Tensor, cast) -> torch.Tensor:
+    """``megabench.tasks.common.rms(x, weight, gemma=True)`` (source not shipped with the reference; call sites
+    reference/pi05.py:178, 192).  Restated as the Gemma RMSNorm the reference's docstrings name as upstream (HF
+    ``GemmaRMSNorm``): normalise in FP32, scale by (1 + weight), cast to the activation dtype.  Parity unpinned for
+    this one function: the stand-in that generated the golden vectors holds the same restatement."""
+    xf = x.float()
+    normalized = xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + EPS)
+    return cast(normalized * (1.0 + weight.float()))
+
+
+def prefill(v: dict, embeddings: torch.Tensor, valid: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,
+            widen: bool = False, layers=None):
+    """reference/pi05.py:167-195: Gemma-2B prefix-LM prefill, returns the post-RoPE keys and the values of every layer
+    ([layers, tokens, kv_heads, head_dim]).  ``widen`` = every BF16 tensor and cast widened to FP32 (the oracle of
+    reference/oracle.py).  Scores are formed in the activation dtype, the finite additive mask is FP32, so the sum that
+    enters the FP32 softmax is FP32 (type promotion), as in the reference."""
+    cast = _cast(widen)
+    steps, d = embeddings.shape[0], head_dim
+    w = (lambda name, layer: v[name][layer].float()) if widen else (lambda name, layer: v[name][layer])
+    x = cast(embeddings)
+    positions = torch.cumsum(valid.long(), 0) - 1
+    bias = torch.where(valid[None, :] & valid[:, None], 0.0, MASK_VALUE)
+    nlayers = v["lq"].shape[0] if layers is None else layers
+    keys, contents = [], []
+    for layer in range(nlayers):
+        normalized = rms_gemma(x, v["ln1"][layer], cast)
+        query = rope((normalized @ w("lq", layer).T).view(steps, q_heads, d), positions, cast)
+        key = rope((normalized @ w("lk", layer).T).view(steps, kv_heads, d), positions, cast)
+        content = (normalized @ w("lv", layer).T).view(steps, kv_heads, d)
+        keys.append(key)
+        contents.append(content)
+        groups = q_heads // kv_heads
+        q, k, c = (t.transpose(0, 1) for t in (query, key.repeat_interleave(groups, 1),
+                                               content.repeat_interleave(groups, 1)))
+        scores = (q @ k.transpose(-1, -2)) * d ** -0.5 + bias
+        mixed = (cast(F.softmax(scores, -1, dtype=torch.float32)) @ c).transpose(0, 1)
+        x = x + mixed.reshape(steps, q_heads * d) @ w("lo", layer).T
+        if layer + 1 == nlayers:
+            break                       # the last MLP does not affect any cached K/V
+        normalized = rms_gemma(x, v["ln2"][layer], cast)
+        gated = F.gelu(normalized @ w("lg", layer).T, approximate="tanh") * (normalized @ w("lu", layer).T)
+        x = x + gated @ w("ld", layer).T
+    return torch.stack(keys), torch.stack(contents)

@@ -140,3 +140,52 @@ def sol(geo: Geometry, batch: int = 1) -> dict:
     return {"expert_weight_bytes": expert, "fp32_cond_weight_bytes": fp32_once,
             "prefix_kv_bytes": kv, "bytes_restream": bytes_stream, "flops": flops,
             "floor_restream_ms": bytes_stream / 8.0e12 * 1e3}
+
+
+# ------------------------------------------------------------------------------------------- prefix prefill
+# The step before the action chunk: the Gemma-2B prefix-LM prefill that produces the per-layer K/V cache
+# (reference/pi05.py:167-195, weights as in reference/pi05.py:100-116).
+PREFILL_WEIGHTS = ("ln1", "ln2", "lq", "lk", "lv", "lo", "lg", "lu", "ld")
+
+
+@dataclass(frozen=True)
+class PrefillGeometry:
+    tokens: int = 968           # prefix length P: 3 x 256 image tokens + 200 prompt tokens in the graded case
+    layers: int = 18
+    hidden: int = 2048
+    intermediate: int = 16384
+    q_heads: int = 8
+    kv_heads: int = 1
+    head_dim: int = 256
+
+
+def prefill_shapes(geo: PrefillGeometry) -> dict:
+    h, L, inter = geo.hidden, geo.layers, geo.intermediate
+    qd, kvd = geo.q_heads * geo.head_dim, geo.kv_heads * geo.head_dim
+    bf16 = torch.bfloat16
+    return {"ln1": ((L, h), bf16), "ln2": ((L, h), bf16),
+            "lq": ((L, qd, h), bf16), "lk": ((L, kvd, h), bf16), "lv": ((L, kvd, h), bf16), "lo": ((L, h, qd), bf16),
+            "lg": ((L, inter, h), bf16), "lu": ((L, inter, h), bf16), "ld": ((L, h, inter), bf16),
+            "embeddings": ((geo.tokens, h), bf16), "valid": ((geo.tokens,), torch.bool)}
+
+
+def make_prefill_inputs(geo: PrefillGeometry, seed: int, mask: str = "pad") -> dict:
+    """Synthetic prefill inputs: projection weights N(0, 1/fan_in) in BF16 (the reference's ``fill_layer_weights``),
+    norm weights N(0, 0.1), unit-variance embeddings, and a validity mask ("full", or "pad": a right-padded prompt as
+    ``prompt`` builds it, reference/pi05.py:143-164, valid count uniform in [tokens/2, tokens])."""
+    g = torch.Generator().manual_seed(seed ^ 0x9A11)
+    out = {}
+    for name, (shape, dtype) in prefill_shapes(geo).items():
+        if name in ("ln1", "ln2"):
+            out[name] = (torch.randn(shape, generator=g) * 0.1).to(dtype)
+        elif name in PREFILL_WEIGHTS:
+            out[name] = (torch.randn(shape, generator=g) * shape[-1] ** -0.5).to(dtype)
+    out["embeddings"] = torch.randn((geo.tokens, geo.hidden), generator=g).to(torch.bfloat16)
+    if mask == "full":
+        out["valid"] = torch.ones(geo.tokens, dtype=torch.bool)
+    elif mask == "pad":
+        n = int(torch.randint(geo.tokens // 2, geo.tokens + 1, (), generator=g))
+        out["valid"] = torch.arange(geo.tokens) < n
+    else:
+        raise ValueError(f"unknown mask kind {mask!r}")
+    return out

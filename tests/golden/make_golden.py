@@ -16,6 +16,10 @@ Outputs (numpy .npz, small):
                           inputs regenerated from the seed (fingerprints stored)
   full_p256_pad.npz       prefix 256, right-padded random-length mask
   small_*.npz             reduced geometries with every input tensor stored
+  prefill_small_*.npz     the Gemma prefix prefill (reference/pi05.py::prefill and the same under the FP32 oracle's
+                          dispatch mode) on reduced geometries, every input stored
+  prefill_full_p160.npz   the prefill at the full Gemma-2B geometry, 160 tokens with a right-padded mask, inputs
+                          regenerated from the seed (fingerprints stored), keys / values of layers 0, 8 and 17 stored
 """
 
 from __future__ import annotations
@@ -77,8 +81,16 @@ def install_megabench_standin() -> None:
     common = types.ModuleType("megabench.tasks.common")
     vision = types.ModuleType("megabench.tasks.vision")
     cases.Case = Case
+    def rms(x, weight, gemma=False):
+        # the Gemma RMSNorm the reference names as upstream: FP32 normalisation, scale (1 + weight), cast back
+        assert gemma
+        xf = x.float()
+        normalized = xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + 1e-6)
+        return (normalized * (1.0 + weight.float())).to(x.dtype)
+
     common.attention, common.fill_layer_weights = attention, fill_layer_weights
-    common.random_norm = common.random_weight = common.rms = _unused
+    common.rms = rms
+    common.random_norm = common.random_weight = _unused
     vision.vision_inputs = _unused
     for name, mod in (("megabench", mb), ("megabench.cases", cases), ("megabench.tasks", tasks),
                       ("megabench.tasks.common", common), ("megabench.tasks.vision", vision)):
@@ -131,13 +143,60 @@ SMALL = {
 }
 
 
+PREFILL_SMALL = {
+    "prefill_small_a": (FX.PrefillGeometry(tokens=24, layers=2, hidden=64, intermediate=128, q_heads=2, kv_heads=1,
+                                           head_dim=16), "pad", 21),
+    "prefill_small_b": (FX.PrefillGeometry(tokens=40, layers=3, hidden=128, intermediate=256, q_heads=8, kv_heads=1,
+                                           head_dim=32), "full", 22),
+}
+PREFILL_FULL = ("prefill_full_p160", FX.PrefillGeometry(tokens=160), "pad", 23, (0, 8, 17))
+
+
+def run_reference_prefill(fixture, geo: FX.PrefillGeometry, inputs: dict):
+    """reference/pi05.py::prefill as it is, and the same call under the FP32 oracle's dispatch mode."""
+    from types import SimpleNamespace
+    case = SimpleNamespace(params={"head_dim": geo.head_dim, "q_heads": geo.q_heads, "kv_heads": geo.kv_heads,
+                                   "layers": geo.layers})
+    oracle = importlib.import_module(fixture.__name__.rsplit(".", 1)[0] + ".reference.oracle")
+    with torch.no_grad():
+        k, v = fixture.ref.prefill(case, inputs, inputs["embeddings"], inputs["valid"])
+        with oracle.WidenBf16():
+            ke, ve = fixture.ref.prefill(case, inputs, inputs["embeddings"], inputs["valid"])
+    return k, v, ke.float(), ve.float()
+
+
+def make_prefill(fixture) -> None:
+    for name, (geo, mask, seed) in PREFILL_SMALL.items():
+        inputs = FX.make_prefill_inputs(geo, seed, mask)
+        k, v, ke, ve = run_reference_prefill(fixture, geo, inputs)
+        blob = {"in_" + key: to_np(val) for key, val in inputs.items()}
+        blob.update(k=to_np(k), v=to_np(v), k_exact=ke.numpy(), v_exact=ve.numpy(),
+                    geo=np.array(dataclasses.astuple(geo), dtype=np.int64))
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **blob)
+        print(name, "k", float(k.float().abs().max()), "diff", float((k.float() - ke).abs().max()))
+    name, geo, mask, seed, keep = PREFILL_FULL
+    inputs = FX.make_prefill_inputs(geo, seed, mask)
+    k, v, ke, ve = run_reference_prefill(fixture, geo, inputs)
+    blob = {"fp_" + key: val for key, val in fingerprints(inputs).items()}
+    blob.update(seed=np.int64(seed), valid=inputs["valid"].numpy(), layers_kept=np.array(keep, dtype=np.int64),
+                k=to_np(k[list(keep)].contiguous()), v=to_np(v[list(keep)].contiguous()),
+                k_exact=ke[list(keep)].numpy(), v_exact=ve[list(keep)].numpy(),
+                geo=np.array(dataclasses.astuple(geo), dtype=np.int64))
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **blob)
+    print(name, "rel k", float((k.float() - ke).norm() / ke.norm()), "rel v", float((v.float() - ve).norm() / ve.norm()))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of garv901/pi05-megakernel (its top-level directory)")
     ap.add_argument("--skip-full", action="store_true")
+    ap.add_argument("--only-prefill", action="store_true")
     args = ap.parse_args()
     torch.manual_seed(0)
     fixture = load_reference(args.reference)
+    make_prefill(fixture)
+    if args.only_prefill:
+        return
 
     for name, (geo, mask, seed) in SMALL.items():
         inputs = FX.make_inputs(geo, seed, "cpu", mask)

@@ -4,7 +4,7 @@ import torch
 
 from oracle import pi05_oracle as O
 from pi05_megakernel_b200 import fixture as FX
-from tests.helpers import fingerprints_match, load_full, load_small
+from tests.helpers import fingerprints_match, load_full, load_prefill, load_small
 
 
 @pytest.mark.parametrize("name", ["small_gqa1", "small_gqa2", "small_full"])
@@ -82,3 +82,18 @@ def test_sol_bytes_match_reference_numbers():
     for prefix, want in ((128, 6_726_352_896), (256, 6_749_945_856), (512, 6_797_131_776), (968, 6_881_181_696)):
         assert O.sol_bytes(O.Geo(prefix=prefix))["bytes_restream"] == want
         assert FX.sol(FX.Geometry(prefix=prefix))["bytes_restream"] == want
+
+
+@pytest.mark.parametrize("name", ["prefill_small_a", "prefill_small_b", "prefill_full_p160"])
+def test_prefill_bit_exact(name):
+    """The restated Gemma prefix prefill against keys / values the unmodified reference produced
+    (reference/pi05.py:167-195, and the same call under the dispatch mode of reference/oracle.py)."""
+    geo, inputs, fps, kept, k, v, k_exact, v_exact = load_prefill(name)
+    if fps is not None and not fingerprints_match(inputs, fps):
+        pytest.fail("this torch build draws different random inputs than the one that made the golden vectors; "
+                    "regenerate them with tests/golden/make_golden.py")
+    args = (inputs, inputs["embeddings"], inputs["valid"], geo.q_heads, geo.kv_heads, geo.head_dim)
+    gk, gv = O.prefill(*args, widen=False)
+    assert torch.equal(gk[kept], k) and torch.equal(gv[kept], v)
+    ek, ev = O.prefill(*args, widen=True)
+    assert torch.equal(ek[kept], k_exact) and torch.equal(ev[kept], v_exact)
