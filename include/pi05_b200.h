@@ -239,6 +239,34 @@ int pi05_destroy(pi05_handle_t h);
 int pi05_chunk_static(int device, const void* const inputs[PI05_NUM_INPUTS], int prefix_len, void* actions,
                       int n_steps, int n_layers, void* stream);
 
+/* ---- Gemma-2B prefix prefill: the step before the action chunk.
+ * Replaces the reference's eager `prefill(case, values, embeddings, valid)` (reference/pi05.py:167-195), which its
+ * fixture runs to obtain the per-layer key / value cache (fixture.py:66-81): RMSNorm, q / k / v projections with RoPE at
+ * the positions of the valid tokens, bidirectional attention among valid tokens, O projection, GeGLU MLP, 18 layers
+ * (the last layer's MLP is skipped: it affects no cached key or value).  Outputs are the post-RoPE keys and the values,
+ * [18, tokens, 1, 256] BF16 - exactly inputs 22 and 23 of pi05_bind, so the chunk engine chains after it without a copy;
+ * `valid` is input 24 (the prefix mask).  Rows of padded (invalid) tokens are written but carry no meaning.
+ *
+ * Weights, in this order (reference/pi05.py:110-115), all BF16, [out, in] row-major, 16-byte aligned:
+ *   0 ln1 [18,2048]   1 ln2 [18,2048]   2 lq [18,2048,2048]   3 lk [18,256,2048]   4 lv [18,256,2048]
+ *   5 lo [18,2048,2048]   6 lg [18,16384,2048]   7 lu [18,16384,2048]   8 ld [18,2048,16384]                     */
+typedef struct pi05_prefill* pi05_prefill_t;
+#define PI05_PREFILL_NUM_WEIGHTS 9
+int pi05_prefill_create(int device, int max_tokens, pi05_prefill_t* out);
+int pi05_prefill_workspace_bytes(pi05_prefill_t h, size_t* bytes);
+/* Records the nine weight pointers (read in place) and the caller-allocated workspace (256-byte aligned). */
+int pi05_prefill_bind(pi05_prefill_t h, const void* const weights[PI05_PREFILL_NUM_WEIGHTS], void* workspace,
+                      size_t workspace_bytes);
+/* One prefill, asynchronous on `stream`: embeddings [tokens, 2048] BF16 (already scaled, as the reference passes them),
+ * valid [tokens] bytes (non-zero = valid), keys / values [n_layers.., tokens, 1, 256] BF16 outputs laid out for 18
+ * layers ([18, tokens, 1, 256]); n_layers < 18 runs only the first layers (debug). */
+int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid, int tokens, void* keys, void* values,
+                     int n_layers, void* stream);
+/* Synchronises `stream` and reports a bounded device-side wait that gave up (PI05_ERR_DEVICE_TIMEOUT), like pi05_status. */
+int pi05_prefill_status(pi05_prefill_t h, void* stream, int* code, int* where);
+const char* pi05_prefill_last_error(pi05_prefill_t h);
+int pi05_prefill_destroy(pi05_prefill_t h);
+
 #ifdef __cplusplus
 }
 #endif

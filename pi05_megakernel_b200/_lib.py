@@ -17,6 +17,7 @@ STATIC_SCRATCH_BYTES = 12 << 20
 STATIC_MAX_PREFIX = 1024
 PLAN_ENTRY, PLAN_INFO = 7, 10
 TP_HANDLE_BYTES = 96
+PREFILL_NUM_WEIGHTS = 9
 
 EVENT_ATTENTION_DONE, EVENT_FFN_NORM_READY = 7, 9
 WAIT_EVENT = 7
@@ -88,6 +89,14 @@ SIGNATURES = {
     "pi05_tp_export": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t]),
     "pi05_tp_attach": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p]),
     "pi05_tp_attach_pointer": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p]),
+    "pi05_prefill_create": (_c.c_int, [_c.c_int, _c.c_int, _c.POINTER(_c.c_void_p)]),
+    "pi05_prefill_workspace_bytes": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_size_t)]),
+    "pi05_prefill_bind": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_void_p), _c.c_void_p, _c.c_size_t]),
+    "pi05_prefill_run": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int,
+                                    _c.c_void_p]),
+    "pi05_prefill_status": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
+    "pi05_prefill_last_error": (_c.c_char_p, [_c.c_void_p]),
+    "pi05_prefill_destroy": (_c.c_int, [_c.c_void_p]),
     "pi05_tuning_defaults": (_c.c_int, [_c.POINTER(Tuning)]),
     "pi05_tune": (_c.c_int, [_c.c_void_p, _c.POINTER(Tuning)]),
     "pi05_chunk_static": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_void_p), _c.c_int, _c.c_void_p, _c.c_int, _c.c_int,

@@ -7,7 +7,7 @@ import shutil
 import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = [os.path.join(HERE, "csrc", "pi05_engine.cu")]
+SOURCES = [os.path.join(HERE, "csrc", "pi05_engine.cu"), os.path.join(HERE, "csrc", "pi05_prefill.cu")]
 HEADERS = [os.path.join(HERE, "csrc", "ptx_sm100.cuh"), os.path.join(HERE, "csrc", "pi05_common.cuh"),
            os.path.join(HERE, "csrc", "pi05_chunk_kernel.cuh"),
            os.path.join(os.path.dirname(HERE), "include", "pi05_b200.h")]
