@@ -409,6 +409,102 @@ def run_tensor_parallel(args, rank: int, local: int, world: int) -> int:
     return 0
 
 
+def prefill_flops(tokens: int, layers: int = 18) -> float:
+    """Matmul and attention work of the prefill (the last layer's MLP is skipped, as in the reference)."""
+    h, ff, qd, kvd = 2048, 16384, 2048, 256
+    per_layer_attn = 2.0 * tokens * h * (qd + 2 * kvd) + 2.0 * tokens * qd * h + 4.0 * tokens * tokens * qd
+    per_layer_mlp = 2.0 * tokens * h * 2 * ff + 2.0 * tokens * ff * h
+    return layers * per_layer_attn + (layers - 1) * per_layer_mlp
+
+
+def run_prefill(args, rank: int) -> int:
+    """The step before the action chunk: the Gemma-2B prefix prefill (reference/pi05.py:167-195) that produces the
+    key / value cache, timed as one whole prefill (all its kernels) with CUDA events, L2 flushed before each."""
+    if rank != 0:
+        return 0
+    from pi05_megakernel_b200.prefill import Pi05Prefill
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    geo = FX.PrefillGeometry(tokens=args.prefix)
+    cpu = FX.make_prefill_inputs(geo, FX.SEEDS[0], "pad" if args.mask != "full" else "full")
+    dev = {k: v.to(device) for k, v in cpu.items()}
+    pre = Pi05Prefill(geo, str(device))
+    pre.bind(dev)
+    shape = (geo.layers, geo.tokens, 1, 256)
+    out = (torch.zeros(shape, dtype=torch.bfloat16, device=device), torch.zeros(shape, dtype=torch.bfloat16, device=device))
+    flush = torch.empty(2 * torch.cuda.get_device_properties(device).L2_cache_size, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream(device)
+    warm, times = max(3, args.warmup), []
+    sampler = ClockSampler(0)
+    for i in range(warm + args.steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        pre.run(dev["embeddings"], dev["valid"], out=out)
+        b.record(stream)
+        torch.cuda.synchronize(device)
+        if i >= warm:
+            times.append(a.elapsed_time(b))
+    pre.status()
+    clocks = sampler.stop()
+    # end to end: embeddings and mask from pinned host memory, keys / values of the last layer read back
+    pinned = {k: cpu[k].pin_memory() for k in ("embeddings", "valid")}
+    host_k = torch.empty((geo.tokens, 256), dtype=torch.bfloat16).pin_memory()
+    e2e = []
+    for i in range(3 + args.steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for k in pinned:
+            dev[k].copy_(pinned[k], non_blocking=True)
+        pre.run(dev["embeddings"], dev["valid"], out=out)
+        host_k.copy_(out[0][geo.layers - 1, :, 0], non_blocking=True)
+        b.record(stream)
+        b.synchronize()
+        if i >= 3:
+            e2e.append(a.elapsed_time(b))
+    ms, e2e_ms = sum(times) / len(times), sum(e2e) / len(e2e)
+    flops = prefill_flops(geo.tokens)
+    weight_bytes = sum(cpu[k].numel() * 2 for k in FX.PREFILL_WEIGHTS) - 3 * 2048 * 16384 * 2   # (last MLP not read)
+    peak_tf = 1393.7
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peak_tf = float(json.load(f).get("bf16_tflops_sustained", peak_tf))
+    line = {
+        "impl": "b200-prefill", "metric": "ms per prefix prefill (Gemma-2B, 18 layers, L2 flushed)", "value": ms, "unit": "ms",
+        "n_gpus": 1, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "ms_per_launch_median": statistics.median(times),
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"Gemma-2B prefix-LM prefill, {geo.tokens} tokens ({'right-padded' if args.mask != 'full' else 'full'} "
+                               "mask), 18 layers, hidden 2048 / 16384, 8 query heads over 1 KV head of 256; keys and values "
+                               "of every layer as output", "l2": "flushed before every timed prefill (2x L2 zero fill)"},
+        "gpu_launches": None, "clocks": clocks,
+        "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in pinned.values()),
+                "d2h_bytes_per_step": host_k.numel() * 2},
+        "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": peak_tf, "unit": "TFLOP/s",
+                     "frac": flops / (ms * 1e-3) / 1e12 / peak_tf, "peak_kind": "measured (sustained BF16 matmul)",
+                     "algorithmic_flops_per_prefill": flops, "weight_bytes_per_prefill": weight_bytes, "traffic": None},
+    }
+    if not args.no_parity:
+        from oracle import pi05_oracle as O
+        torch.set_num_threads(os.cpu_count() or 1)
+        t0 = time.perf_counter()
+        wk, wv = O.prefill(cpu, cpu["embeddings"], cpu["valid"], 8, 1, 256)
+        cpu_s = time.perf_counter() - t0
+        ek, ev = O.prefill(cpu, cpu["embeddings"], cpu["valid"], 8, 1, 256, widen=True)
+        rows = cpu["valid"]
+        dk = O.band(wk[:, rows].float(), out[0].cpu()[:, rows].float(), ek[:, rows])
+        dv = O.band(wv[:, rows].float(), out[1].cpu()[:, rows].float(), ev[:, rows])
+        line["parity"] = {"pass": bool(dk["pass"] and dv["pass"]), "relative_error": max(dk["relative_error"], dv["relative_error"]),
+                          "reference_relative_error": max(dk["reference_relative_error"], dv["reference_relative_error"]),
+                          "checker": "band of the keys and values of the valid tokens against the CPU oracle"}
+        line["cpu_baseline"] = {"value": cpu_s * 1e3, "unit": "ms", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": "one whole prefill of the same workload (eager BF16 path of the oracle)"}
+    print(json.dumps(line), flush=True)
+    pre.close()
+    return 0
+
+
 def parity_check(arm, geo, weights, obs, B: int) -> dict:
     """One band check of what the timed arm left in its output buffer, against the CPU oracle (outside every timed
     region): the rank's observation, or the first and last one of its batch (reference bench.py:220-256)."""
@@ -437,6 +533,8 @@ def main() -> int:
     ap.add_argument("--ref-variant", default="", help="--impl reference-gpu: the reference arm's variant string "
                                                       "(default k16-nofgu, k64 at prefix 968)")
     ap.add_argument("--no-parity", action="store_true", help="skip the band check of the timed arm's result")
+    ap.add_argument("--prefill", action="store_true",
+                    help="time the Gemma-2B prefix prefill (the step before the chunk) at --prefix tokens instead of the chunk")
     ap.add_argument("--tp", action="store_true",
                     help="tensor parallel: all ranks of the launch share ONE observation (latency line instead of the "
                          "data-parallel benchmark line)")
@@ -466,6 +564,8 @@ def main() -> int:
         return 0
     if args.tp:
         return run_tensor_parallel(args, rank, local, world)
+    if args.prefill:
+        return run_prefill(args, rank)
     warmup = max(3, args.warmup)
 
     import torch.distributed as dist

@@ -13,8 +13,8 @@
 //     of two TMEM accumulators, four epilogue warps read the other one; the epilogues fuse what follows the matmul -
 //     RoPE and the scatter into q / k / v, GeGLU, or the residual add;
 //   * a row kernel for the Gemma RMSNorm, a table kernel for the RoPE factors;
-//   * attention by the chunk engine's own attention code (16 query rows = 2 tokens x 8 heads against 64-key chunks
-//     staged by tiled TMA copies, online softmax), driven by a small wrapper kernel.
+//   * an attention kernel of 64 query rows (8 tokens x 8 heads over the one KV head) per CTA against 64-key chunks staged
+//     by tiled TMA copies, warp MMAs and an online softmax that never leaves the warp.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -319,21 +319,40 @@ __global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_b
   }
 }
 
-// positions = cumsum(valid) - 1 (reference/pi05.py:173) and the BF16 cos / sin of every (token, rotary index)
-// (reference/pi05.py:218-229: FP32 inverse frequencies and phases).  One block; the count is a serial scan by warp 0.
-__global__ void rope_table_kernel(const uint8_t* __restrict__ valid, int tokens, uint32_t* __restrict__ rope, int* __restrict__ positions) {
-  extern __shared__ int s_pos[];
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int t = 0; t < tokens; ++t) { acc += valid[t] ? 1 : 0; s_pos[t] = acc - 1; }
-  }
+// positions = cumsum(valid) - 1 (reference/pi05.py:173): one block, a block-wide scan in chunks of 1024 tokens.
+__global__ void positions_kernel(const uint8_t* __restrict__ valid, int tokens, int* __restrict__ positions) {
+  __shared__ int warp_sum[32];
+  __shared__ int carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < tokens; i += blockDim.x) positions[i] = s_pos[i];
-  for (int i = threadIdx.x; i < tokens * 128; i += blockDim.x) {
+  for (int base = 0; base < tokens; base += 1024) {
+    const int t = base + threadIdx.x;
+    int v = t < tokens && valid[t] ? 1 : 0;
+    for (int sh = 1; sh < 32; sh <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, sh); if (lane >= sh) v += u; }
+    if (lane == 31) warp_sum[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sum[lane];
+      for (int sh = 1; sh < 32; sh <<= 1) { const int u = __shfl_up_sync(0xffffffffu, w, sh); if (lane >= sh) w += u; }
+      warp_sum[lane] = w;
+    }
+    __syncthreads();
+    const int incl = v + (warp ? warp_sum[warp - 1] : 0) + carry;
+    if (t < tokens) positions[t] = incl - 1;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = incl;
+    __syncthreads();
+  }
+}
+
+// The BF16 cos / sin of every (token, rotary index) (reference/pi05.py:218-229: FP32 inverse frequencies and phases).
+__global__ void rope_table_kernel(const int* __restrict__ positions, int tokens, uint32_t* __restrict__ rope) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < tokens * 128; i += gridDim.x * blockDim.x) {
     const int t = i >> 7, j = i & 127;
     const float e = (float)(2 * j) / 256.0f;
     const float inv = 1.0f / (float)pow(10000.0, (double)e);
-    const float phase = (float)s_pos[t] * inv;
+    const float phase = (float)positions[t] * inv;
     __nv_bfloat162 v = __floats2bfloat162_rn((float)cos((double)phase), (float)sin((double)phase));
     rope[i] = *reinterpret_cast<uint32_t*>(&v);
   }
@@ -343,56 +362,168 @@ __global__ void cast_copy_kernel(const uint4* __restrict__ src, uint4* __restric
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) dst[i] = src[i];
 }
 
-}  // namespace pf
+// ------------------------------------------------------------------------------------------- prefill attention
+// 64 query rows per CTA (8 tokens x 8 heads, all sharing the one KV head) against every key of the layer, 64 keys at a
+// time: two shared-memory stages of keys + values filled by tiled TMA copies (the 256 dims of a token as four 64-dim
+// segments, 128-byte swizzle), warp MMAs (m16n8k16) from ldmatrix fragments.  Warp w owns 16 rows (tokens 2 (w & 3),
+// 2 (w & 3) + 1) and half of the output dims (w >> 2): it scores its rows against all 64 keys of a chunk (the two warps
+// of a row group both do), keeps running maxima and sums to itself - nothing crosses warps - and accumulates
+// P V for its 128 dims.  Scores are rounded to BF16 and scaled by 1/16 as the reference's BF16 matmul and scale do,
+// masked keys get -inf, probabilities are rounded to BF16 before P V and the FP32 row sum divides at the end.
+namespace pfa {
+constexpr int TOK = 8, ROWS = 64, KCH = 64, STG = 2, THREADS_A = 256;
+constexpr int QSTRIDE = HD + 8;                               // BF16 per q row (528 B: conflict-free ldmatrix)
+constexpr int KV_CHUNK = 4 * 64 * 128;                        // one chunk of keys or of values: four 64-dim segments
+constexpr int OFF_K = 0, OFF_V = OFF_K + STG * KV_CHUNK, OFF_Q = OFF_V + STG * KV_CHUNK;
+constexpr int OFF_VALID = OFF_Q + ROWS * QSTRIDE * 2, OFF_BAR = OFF_VALID + STG * KCH;
+constexpr int SMEM_A = OFF_BAR + 64 + 1024;
 
-// The chunk engine's device code once more, for its attention (16 query rows against TMA-staged 64-key chunks with an
-// online softmax): the prefill's attention is the same computation without suffix keys.
-#ifndef PI05_QF_KEPT
-#define PI05_QF_KEPT 8
-#endif
-namespace k_pf {
-#define PI05_TRACE 0
-#define PI05_BATCHED 0
-#define PI05_GN 1
-#define PI05_TP 0
-#include "pi05_chunk_kernel.cuh"
-#undef PI05_TRACE
-#undef PI05_BATCHED
-#undef PI05_GN
-#undef PI05_TP
+struct AttnParams {
+  CUtensorMap kmap, vmap;            // {64 dims, tokens, 4 segments, layers, 1}, box {64, 64, 4, 1, 1}
+  const __nv_bfloat16* q;            // [tokens, 2048], rotated
+  const uint8_t* valid;              // [tokens]
+  __nv_bfloat16* out;                // [tokens, 2048]
+  int tokens, layer;
+  unsigned int* status;
+  long long wait_limit;
+};
 
-// Two tokens x eight heads per CTA against all keys of this layer (the prefix itself).  `q` holds the rotated queries.
-__global__ void __launch_bounds__(THREADS, 1) prefill_attention_kernel(const __grid_constant__ Params p,
-                                                                       const __nv_bfloat16* __restrict__ q, int layer) {
+__global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int unit = blockIdx.x, tid = threadIdx.x;
-  const Ctx c{p.ctrl, p.wait_limit, unit, 20u};
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rg = warp & 3, dh = warp >> 2, g = lane >> 2, qd = lane & 3;
+  const int t0 = blockIdx.x * TOK;
+  const int npc = (p.tokens + KCH - 1) / KCH;
+  const uint32_t full = ptx::smem_u32(smem + OFF_BAR), empty = full + 8 * STG;
   if (tid == 0) {
-    reinterpret_cast<int*>(smem + OFF_PAGETAB)[0] = 0;
-    for (int j = 0; j < 2 * ATT_STAGES; ++j) ptx::mbar_init(ptx::smem_u32(smem + OFF_ATTBARS) + 8 * j, 1);
+    for (int i = 0; i < STG; ++i) { ptx::mbar_init(full + 8 * i, 1); ptx::mbar_init(empty + 8 * i, 8); }
     ptx::fence_mbar_init();
+    ptx::fence_proxy_async_shared();
   }
   __syncthreads();
-  AttBars bars;
-  const int npc = (p.prefix + 63) / 64;
-  AttChunkIssue issue{p, p.ob, c, smem, bars, layer, npc, 0, npc};     // no suffix chunk: the keys end with the prefix
-  const int nearly = min(npc, ATT_STAGES);
-  for (int j = 0; j < nearly; ++j) issue(j, j);
-  {
-    const int m = tid >> 4, d0 = (tid & 15) * 16, t = unit * 2 + (m >> 3);
-    uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
-    if (t < p.prefix) {
-      const uint4* src = reinterpret_cast<const uint4*>(q + (size_t)t * QD + (m & 7) * HD + d0);
-      a = src[0]; b = src[1];
+  // One chunk of keys and of values into a stage (rows past the last token arrive as zeros), and its validity bytes.
+  auto issue = [&](int chunk) {
+    const int s = chunk % STG;
+    for (int i = lane; i < KCH; i += 32) {
+      const int t = chunk * KCH + i;
+      smem[OFF_VALID + s * KCH + i] = (t < p.tokens && p.valid[t]) ? 1 : 0;
     }
-    const uint32_t dst = ptx::smem_u32(smem + OFF_QS) + (m * KV_STRIDE + d0) * 2;
-    ptx::st_shared_v4(dst, a.x, a.y, a.z, a.w);
-    ptx::st_shared_v4(dst + 16, b.x, b.y, b.z, b.w);
+    __syncwarp();
+    if (lane == 0) {
+      const uint32_t bar = full + 8 * s;
+      ptx::mbar_expect_tx(bar, 2 * KV_CHUNK);
+      ptx::tma_load_5d(ptx::smem_u32(smem + OFF_K + s * KV_CHUNK), &p.kmap, bar, 0, chunk * KCH, 0, p.layer, 0);
+      ptx::tma_load_5d(ptx::smem_u32(smem + OFF_V + s * KV_CHUNK), &p.vmap, bar, 0, chunk * KCH, 0, p.layer, 0);
+    }
+  };
+  if (warp == 0) issue(0);
+  // ---- q tile: 64 rows (token-local x head) of 256 dims
+  for (int i = tid; i < ROWS * 32; i += THREADS_A) {
+    const int r = i >> 5, piece = i & 31, t = t0 + (r >> 3);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (t < p.tokens) v = *reinterpret_cast<const uint4*>(p.q + (size_t)t * QD + (r & 7) * HD + piece * 8);
+    *reinterpret_cast<uint4*>(smem + OFF_Q + (r * QSTRIDE + piece * 8) * 2) = v;
   }
-  if (!attention_unit(p, p.ob, smem, unit, issue, 0, nearly, 0, false)) att_drain(c, smem, bars, 0);
+  __syncthreads();
+  uint32_t qf[HD / 16][4];
+  {
+    const uint32_t qaddr = ptx::smem_u32(smem + OFF_Q) + (((rg * 16) + (lane & 15)) * QSTRIDE + (lane >> 4) * 8) * 2;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) ptx::ldmatrix_x4(qaddr + kk * 32, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+  }
+  float oa[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oa[i][j] = 0.f;
+  float m_lo = -1e30f, m_hi = -1e30f, l_lo = 0.f, l_hi = 0.f;
+
+  for (int c = 0; c < npc; ++c) {
+    const int s = c % STG;
+    if (warp == 0 && c + 1 < npc) {
+      // the stage of chunk c + 1 held chunk c + 1 - STG: every warp must be done with it
+      if (c + 1 >= STG && !wait_bar(p.status, p.wait_limit, empty + 8 * ((c + 1) % STG), (uint32_t)(((c + 1) / STG - 1) & 1), 5)) return;
+      issue(c + 1);
+    }
+    if (!wait_bar(p.status, p.wait_limit, full + 8 * s, (uint32_t)((c / STG) & 1), 6)) return;
+    const uint32_t ks = ptx::smem_u32(smem + OFF_K + s * KV_CHUNK), vs = ptx::smem_u32(smem + OFF_V + s * KV_CHUNK);
+    // ---- S = Q K^T for this warp's 16 rows and the chunk's 64 keys
+    float sc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float e[4] = {0.f, 0.f, 0.f, 0.f}, o[4] = {0.f, 0.f, 0.f, 0.f};
+      // key row r = 8 j + (lane & 7); 16-byte piece c of the row sits at piece c ^ (r & 7) of its 128-byte line
+      const uint32_t krow = ks + (j * 8 + (lane & 7)) * 128;
+      const uint32_t ksw = lane & 7, kc = lane >> 3;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; kk += 2) {
+        uint32_t b0, b1, b2, b3;
+        ptx::ldmatrix_x4(krow + (kk >> 2) * (64 * 128) + ((((kk & 3) * 2 + kc) ^ ksw) << 4), b0, b1, b2, b3);
+        ptx::mma_16816(e, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+        ptx::mma_16816(o, qf[kk + 1][0], qf[kk + 1][1], qf[kk + 1][2], qf[kk + 1][3], b2, b3);
+      }
+      const uint8_t* kv = smem + OFF_VALID + s * KCH + j * 8 + 2 * qd;
+      const bool v0 = kv[0] != 0, v1 = kv[1] != 0;
+      sc[j][0] = v0 ? rb(e[0] + o[0]) * 0.0625f : -INFINITY; sc[j][1] = v1 ? rb(e[1] + o[1]) * 0.0625f : -INFINITY;
+      sc[j][2] = v0 ? rb(e[2] + o[2]) * 0.0625f : -INFINITY; sc[j][3] = v1 ? rb(e[3] + o[3]) * 0.0625f : -INFINITY;
+    }
+    // ---- online softmax, rows g and g + 8 of the group (a row's 64 scores live in the four lanes of a quad)
+    float cm_lo = -INFINITY, cm_hi = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { cm_lo = fmaxf(cm_lo, fmaxf(sc[j][0], sc[j][1])); cm_hi = fmaxf(cm_hi, fmaxf(sc[j][2], sc[j][3])); }
+    cm_lo = fmaxf(cm_lo, __shfl_xor_sync(0xffffffffu, cm_lo, 1)); cm_lo = fmaxf(cm_lo, __shfl_xor_sync(0xffffffffu, cm_lo, 2));
+    cm_hi = fmaxf(cm_hi, __shfl_xor_sync(0xffffffffu, cm_hi, 1)); cm_hi = fmaxf(cm_hi, __shfl_xor_sync(0xffffffffu, cm_hi, 2));
+    const float mn_lo = fmaxf(m_lo, cm_lo), mn_hi = fmaxf(m_hi, cm_hi);
+    const float al_lo = __expf(m_lo - mn_lo), al_hi = __expf(m_hi - mn_hi);
+    m_lo = mn_lo; m_hi = mn_hi;
+    l_lo *= al_lo; l_hi *= al_hi;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { oa[i][0] *= al_lo; oa[i][1] *= al_lo; oa[i][2] *= al_hi; oa[i][3] *= al_hi; }
+    uint32_t pf_[4][4];                 // P as A fragments: k-step kk covers keys 16 kk .. 16 kk + 15 (score tiles 2 kk, 2 kk + 1)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p00 = __expf(sc[j][0] - mn_lo), p01 = __expf(sc[j][1] - mn_lo);
+      const float p10 = __expf(sc[j][2] - mn_hi), p11 = __expf(sc[j][3] - mn_hi);
+      l_lo += p00 + p01; l_hi += p10 + p11;
+      pf_[j >> 1][(j & 1) * 2] = pack2(p00, p01);
+      pf_[j >> 1][(j & 1) * 2 + 1] = pack2(p10, p11);
+    }
+    // ---- O += P V for this warp's 128 output dims (segments 2 dh and 2 dh + 1)
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      // value row r = 16 kk + (lane & 7) + 8 ((lane >> 3) & 1); dims: segment, then 16-byte piece (lane >> 4) + 2 pp
+      const uint32_t vsw = lane & 7;
+#pragma unroll
+      for (int sg = 0; sg < 2; ++sg) {
+        const uint32_t vrow = vs + (dh * 2 + sg) * (64 * 128) + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 128;
+#pragma unroll
+        for (int pp = 0; pp < 4; ++pp) {
+          uint32_t r0, r1, r2, r3;
+          ptx::ldmatrix_x4_trans(vrow + ((((uint32_t)(lane >> 4) + 2 * pp) ^ vsw) << 4), r0, r1, r2, r3);
+          ptx::mma_16816(oa[sg * 8 + pp * 2], pf_[kk][0], pf_[kk][1], pf_[kk][2], pf_[kk][3], r0, r1);
+          ptx::mma_16816(oa[sg * 8 + pp * 2 + 1], pf_[kk][0], pf_[kk][1], pf_[kk][2], pf_[kk][3], r2, r3);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(empty + 8 * s);
+  }
+  // ---- normalise and store: row g -> token 2 rg, row g + 8 -> token 2 rg + 1, head g
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  const float il_lo = 1.0f / l_lo, il_hi = 1.0f / l_hi;
+  const int ta = t0 + 2 * rg, tb = ta + 1;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int col = g * HD + dh * 128 + i * 8 + 2 * qd;
+    if (ta < p.tokens) *reinterpret_cast<uint32_t*>(p.out + (size_t)ta * QD + col) = pack2(oa[i][0] * il_lo, oa[i][1] * il_lo);
+    if (tb < p.tokens) *reinterpret_cast<uint32_t*>(p.out + (size_t)tb * QD + col) = pack2(oa[i][2] * il_hi, oa[i][3] * il_hi);
+  }
 }
-}  // namespace k_pf
+}  // namespace pfa
+
+}  // namespace pf
 
 // =========================================================================================== host side
 struct pi05_prefill {
@@ -569,7 +700,8 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
   if (e != cudaSuccess) { h->last_error = cudaGetErrorString(e); return PI05_ERR_CUDA; }
   pf::cast_copy_kernel<<<h->sms, 256, 0, stream>>>(static_cast<const uint4*>(embeddings), reinterpret_cast<uint4*>(x),
                                                    (size_t)P * pf::H * 2 / 16);
-  pf::rope_table_kernel<<<1, 1024, (size_t)P * 4, stream>>>(static_cast<const uint8_t*>(valid), P, rope, pos);
+  pf::positions_kernel<<<1, 1024, 0, stream>>>(static_cast<const uint8_t*>(valid), P, pos);
+  pf::rope_table_kernel<<<h->sms, 256, 0, stream>>>(pos, P, rope);
 
   // tensor maps: activations (rows = tokens, zero beyond), weights (all layers stacked), keys / values for the attention
   pf::GemmParams base;
@@ -585,24 +717,17 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
             map_2d(&wd, w[LD], pf::FFN, (uint64_t)pf::LAYERS * pf::H, 64) && map_kv(&kmap, K, P) && map_kv(&vmap, V, P);
   if (!ok) { h->last_error = "cuTensorMapEncodeTiled failed"; return PI05_ERR_CUDA; }
 
-  // the attention's parameter block (the chunk engine's own type): prefix = tokens, one page per "observation"
   static bool att_attr[64] = {};
   if (!att_attr[h->device]) {
-    e = cudaFuncSetAttribute(k_pf::prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    e = cudaFuncSetAttribute(pf::pfa::attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::pfa::SMEM_A);
     if (e != cudaSuccess) { h->last_error = cudaGetErrorString(e); return PI05_ERR_CUDA; }
     att_attr[h->device] = true;
   }
-  Params ap;
+  pf::pfa::AttnParams ap;
   memset(&ap, 0, sizeof ap);
-  ap.maps.pk = ap.maps.pk_tail = kmap;
-  ap.maps.pv = ap.maps.pv_tail = vmap;
-  ap.ob.prefix_mask = static_cast<const uint8_t*>(valid);
-  ap.ob.attn = mixed;
-  ap.ctrl = status;
-  ap.wait_limit = h->wait_limit;
-  ap.prefix = P; ap.key_groups = 1; ap.row_groups = 1; ap.batch = 1;
-  ap.pages_per_obs = 1; ap.page_tokens = P;
-  ap.drop_event = -1; ap.poll_ns = 20;
+  ap.kmap = kmap; ap.vmap = vmap;
+  ap.q = q; ap.valid = static_cast<const uint8_t*>(valid); ap.out = mixed;
+  ap.tokens = P; ap.status = status; ap.wait_limit = h->wait_limit;
 
   const int norm_blocks = (P + 7) / 8;
   for (int l = 0; l < n_layers; ++l) {
@@ -614,7 +739,8 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
       gp.k = K + (size_t)l * P * HD; gp.v = V + (size_t)l * P * HD;
       if ((e = launch_gemm<pf::EPI_QKV, 256>(h, gp, stream)) != cudaSuccess) break;
     }
-    k_pf::prefill_attention_kernel<<<(P + 1) / 2, THREADS, SMEM_BYTES, stream>>>(ap, q, l);
+    ap.layer = l;
+    pf::pfa::attention_kernel<<<(P + pf::pfa::TOK - 1) / pf::pfa::TOK, pf::pfa::THREADS_A, pf::pfa::SMEM_A, stream>>>(ap);
     {
       pf::GemmParams gp = base;
       gp.a = a_mixed; gp.b0 = gp.b1 = wo;
