@@ -478,7 +478,7 @@ def run_prefill(args, rank: int) -> int:
         "config": {"workload": f"Gemma-2B prefix-LM prefill, {geo.tokens} tokens ({'right-padded' if args.mask != 'full' else 'full'} "
                                "mask), 18 layers, hidden 2048 / 16384, 8 query heads over 1 KV head of 256; keys and values "
                                "of every layer as output", "l2": "flushed before every timed prefill (2x L2 zero fill)"},
-        "gpu_launches": None, "clocks": clocks,
+        "gpu_launches": (3 + 4 * geo.layers + 3 * (geo.layers - 1)) * args.steps, "clocks": clocks,
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in pinned.values()),
                 "d2h_bytes_per_step": host_k.numel() * 2},
         "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": peak_tf, "unit": "TFLOP/s",
