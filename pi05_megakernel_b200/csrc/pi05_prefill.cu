@@ -13,8 +13,8 @@
 //     of two TMEM accumulators, four epilogue warps read the other one; the epilogues fuse what follows the matmul -
 //     RoPE and the scatter into q / k / v, GeGLU, or the residual add;
 //   * a row kernel for the Gemma RMSNorm, a table kernel for the RoPE factors;
-//   * an attention kernel of 64 query rows (8 tokens x 8 heads over the one KV head) per CTA against 64-key chunks staged
-//     by tiled TMA copies, warp MMAs and an online softmax that never leaves the warp.
+//   * an attention kernel of 128 query rows (16 tokens x 8 heads over the one KV head) per CTA: tcgen05 MMAs for Q K^T and
+//     P V over 64-key chunks staged by TMA, two passes over the keys (row maxima, then probabilities), one thread per row.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -24,12 +24,17 @@
 
 #include <new>
 #include <string>
+#include <utility>
 
 #include "../../include/pi05_b200.h"
 #include "ptx_sm100.cuh"
 
 #include "pi05_common.cuh"
 using namespace pi05;
+
+#ifndef PI05_PREFILL_OVERLAP
+#define PI05_PREFILL_OVERLAP 1     // 0: every kernel waits for the one before it to finish before it starts (for A/B runs)
+#endif
 
 namespace pf {
 
@@ -52,6 +57,8 @@ struct GemmParams {
   __nv_bfloat16* x;                // EPI_RESID: residual stream [tokens, H], updated in place
   __nv_bfloat16* act;              // EPI_GEGLU: [tokens, FFN]
   __nv_bfloat16 *q, *k, *v;        // EPI_QKV: q [tokens, 2048]; k, v: this layer's [tokens, 256]
+  __nv_bfloat16* vt;               // EPI_QKV: the layer's values once more as V^T [256, vt_stride] for the attention's MMAs
+  int vt_stride;
   const uint32_t* rope;            // [tokens][128]: cos BF16 | sin BF16 << 16
   unsigned int* status;
   long long wait_limit;
@@ -131,6 +138,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
   const uint32_t tmem = s_tmem;
   const int ntiles = p.n_tiles * p.m_tiles;
   const bool leader = ptx::elect_one();
+  // everything up to here overlapped the tail of the kernel before; its outputs are read from here on
+  ptx::grid_dep_launch();
+  ptx::grid_dep_wait();
 
   if (warp == 0) {
     // ---- producer: both operands of every stage, tile after tile (consecutive tiles share the weight rows)
@@ -244,6 +254,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
                 o1[j] = pack2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
                 o2[j] = pack2(__uint_as_float(r2[2 * j]), __uint_as_float(r2[2 * j + 1]));
               }
+              // V^T: a warp's 32 tokens are neighbours in every dim row
+              unsigned short* t1 = reinterpret_cast<unsigned short*>(p.vt) + (size_t)c * p.vt_stride + token;
+              unsigned short* t2 = t1 + (size_t)128 * p.vt_stride;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                t1[(size_t)(2 * j) * p.vt_stride] = (unsigned short)(o1[j] & 0xffffu);
+                t1[(size_t)(2 * j + 1) * p.vt_stride] = (unsigned short)(o1[j] >> 16);
+                t2[(size_t)(2 * j) * p.vt_stride] = (unsigned short)(o2[j] & 0xffffu);
+                t2[(size_t)(2 * j + 1) * p.vt_stride] = (unsigned short)(o2[j] >> 16);
+              }
             } else {
               // RoPE (reference/pi05.py:218-229 on BF16 tensors): x cos + rotate_half(x) sin, every product and the
               // sum rounded to BF16; dims c.. pair with dims 128 + c..
@@ -291,6 +311,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
 __global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                __nv_bfloat16* __restrict__ out, int tokens) {
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  ptx::grid_dep_launch();
+  ptx::grid_dep_wait();
   if (row >= tokens) return;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
   const uint4* wr = reinterpret_cast<const uint4*>(w);
@@ -363,24 +385,34 @@ __global__ void cast_copy_kernel(const uint4* __restrict__ src, uint4* __restric
 }
 
 // ------------------------------------------------------------------------------------------- prefill attention
-// 64 query rows per CTA (8 tokens x 8 heads, all sharing the one KV head) against every key of the layer, 64 keys at a
-// time: two shared-memory stages of keys + values filled by tiled TMA copies (the 256 dims of a token as four 64-dim
-// segments, 128-byte swizzle), warp MMAs (m16n8k16) from ldmatrix fragments.  Warp w owns 16 rows (tokens 2 (w & 3),
-// 2 (w & 3) + 1) and half of the output dims (w >> 2): it scores its rows against all 64 keys of a chunk (the two warps
-// of a row group both do), keeps running maxima and sums to itself - nothing crosses warps - and accumulates
-// P V for its 128 dims.  Scores are rounded to BF16 and scaled by 1/16 as the reference's BF16 matmul and scale do,
-// masked keys get -inf, probabilities are rounded to BF16 before P V and the FP32 row sum divides at the end.
+// 128 query rows per CTA (16 tokens x 8 heads, all sharing the one KV head) against every key of the layer, on the
+// tcgen05 tensor cores, in two passes over the keys so that nothing ever has to be rescaled:
+//   pass 1  S = Q K^T chunk by chunk (64 keys) into one of two TMEM buffers; the softmax threads (one per query row) read
+//           their row and keep the maximum over the valid keys;
+//   pass 2  S again; P = exp(S - max) (0 for masked keys) is rounded to BF16 and written to shared memory in the
+//           K-major swizzled layout an MMA A operand has, the FP32 row sum is kept by the thread, and O += P V
+//           accumulates in 256 TMEM columns with the values read as V^T [256 dims, keys] (written by the QKV epilogue),
+//           so that both MMAs take K-major operands.  O / sum goes out as BF16.
+// Scores are rounded to BF16 and scaled by 1/16 as the reference's BF16 matmul and scale do (reference/pi05.py:184-188).
+// Warp 0 streams Q, the key chunks (the 256 dims of a token as four 64-dim segments, 128-byte swizzle) and the V^T
+// chunks with TMA through two-stage rings; warp 1 issues the MMAs (S of chunk c + 1 before P V of chunk c, so that the
+// tensor core works while chunk c's probabilities are being made); warps 2..5 are the softmax threads.
 namespace pfa {
-constexpr int TOK = 8, ROWS = 64, KCH = 64, STG = 2, THREADS_A = 256;
-constexpr int QSTRIDE = HD + 8;                               // BF16 per q row (528 B: conflict-free ldmatrix)
-constexpr int KV_CHUNK = 4 * 64 * 128;                        // one chunk of keys or of values: four 64-dim segments
-constexpr int OFF_K = 0, OFF_V = OFF_K + STG * KV_CHUNK, OFF_Q = OFF_V + STG * KV_CHUNK;
-constexpr int OFF_VALID = OFF_Q + ROWS * QSTRIDE * 2, OFF_BAR = OFF_VALID + STG * KCH;
-constexpr int SMEM_A = OFF_BAR + 64 + 1024;
+constexpr int TOK = 16, ROWS = 128, KCH = 64, STG = 2, THREADS_A = 192;
+constexpr int Q_BYTES = ROWS * HD * 2;                        // four 64-dim blocks of [128 rows x 128 B]
+constexpr int K_BYTES = KCH * HD * 2;                         // four 64-dim segments of [64 keys x 128 B]
+constexpr int V_BYTES = HD * KCH * 2;                         // [256 dims x 64 keys]
+constexpr int P_BYTES = ROWS * KCH * 2;                       // [128 rows x 64 keys]
+constexpr int OFF_Q = 0, OFF_K = OFF_Q + Q_BYTES, OFF_V = OFF_K + STG * K_BYTES, OFF_P = OFF_V + STG * V_BYTES;
+constexpr int SMEM_A = OFF_P + 2 * P_BYTES + 1024;
+constexpr int TM_O = 0, TM_S = 256, TM_COLS = 512;            // TMEM columns: O [128 x 256], two S buffers [128 x 64]
+constexpr int MASK_WORDS = 128;                               // validity bits of up to 4096 tokens
+static_assert(SMEM_A <= 227 * 1024, "attention shared memory");
 
 struct AttnParams {
-  CUtensorMap kmap, vmap;            // {64 dims, tokens, 4 segments, layers, 1}, box {64, 64, 4, 1, 1}
-  const __nv_bfloat16* q;            // [tokens, 2048], rotated
+  CUtensorMap qmap;                  // q as [tokens * 8 rows, 256 dims], box {64, 128}
+  CUtensorMap kmap;                  // {64 dims, tokens, 4 segments, layers, 1}, box {64, 64, 4, 1, 1}
+  CUtensorMap vtmap;                 // V^T of the layer [256 dims, tokens], box {64 keys, 256}
   const uint8_t* valid;              // [tokens]
   __nv_bfloat16* out;                // [tokens, 2048]
   int tokens, layer;
@@ -388,137 +420,268 @@ struct AttnParams {
   long long wait_limit;
 };
 
+// Four K = 16 MMAs over one 64-k operand block (32-byte steps inside the 128-byte swizzle row).
+__device__ __forceinline__ void umma_k64(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 a1, a2, a3, b1, b2, b3;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "add.u64 a1, %1, 2;\n add.u64 a2, %1, 4;\n add.u64 a3, %1, 6;\n"
+      "add.u64 b1, %2, 2;\n add.u64 b2, %2, 4;\n add.u64 b3, %2, 6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, 1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, 1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, 1;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+#ifdef PI05_PFA_TRACE
+#define PFA_STAMP(i) do { if (blockIdx.x == 0) reinterpret_cast<unsigned long long*>(p.status + 16)[i] = clock64(); } while (0)
+#else
+#define PFA_STAMP(i) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // barriers: q, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2], o_full
+  __shared__ uint64_t bars[20];
+  __shared__ uint32_t s_tmem;
+  __shared__ uint32_t s_mask[MASK_WORDS];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int rg = warp & 3, dh = warp >> 2, g = lane >> 2, qd = lane & 3;
-  const int t0 = blockIdx.x * TOK;
   const int npc = (p.tokens + KCH - 1) / KCH;
-  const uint32_t full = ptx::smem_u32(smem + OFF_BAR), empty = full + 8 * STG;
+  const uint32_t b0 = ptx::smem_u32(bars);
+  const uint32_t q_full = b0, k_full = b0 + 8, k_empty = b0 + 24, v_full = b0 + 40, v_empty = b0 + 56;
+  const uint32_t s_full = b0 + 72, s_empty = b0 + 88, p_full = b0 + 104, p_empty = b0 + 120, o_full = b0 + 136;
   if (tid == 0) {
-    for (int i = 0; i < STG; ++i) { ptx::mbar_init(full + 8 * i, 1); ptx::mbar_init(empty + 8 * i, 8); }
+    ptx::mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(k_full + 8 * i, 1); ptx::mbar_init(k_empty + 8 * i, 1);
+      ptx::mbar_init(v_full + 8 * i, 1); ptx::mbar_init(v_empty + 8 * i, 1);
+      ptx::mbar_init(s_full + 8 * i, 1); ptx::mbar_init(s_empty + 8 * i, 128);
+      ptx::mbar_init(p_full + 8 * i, 128); ptx::mbar_init(p_empty + 8 * i, 1);
+    }
+    ptx::mbar_init(o_full, 1);
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_shared();
   }
-  __syncthreads();
-  // One chunk of keys and of values into a stage (rows past the last token arrive as zeros), and its validity bytes.
-  auto issue = [&](int chunk) {
-    const int s = chunk % STG;
-    for (int i = lane; i < KCH; i += 32) {
-      const int t = chunk * KCH + i;
-      smem[OFF_VALID + s * KCH + i] = (t < p.tokens && p.valid[t]) ? 1 : 0;
-    }
-    __syncwarp();
-    if (lane == 0) {
-      const uint32_t bar = full + 8 * s;
-      ptx::mbar_expect_tx(bar, 2 * KV_CHUNK);
-      ptx::tma_load_5d(ptx::smem_u32(smem + OFF_K + s * KV_CHUNK), &p.kmap, bar, 0, chunk * KCH, 0, p.layer, 0);
-      ptx::tma_load_5d(ptx::smem_u32(smem + OFF_V + s * KV_CHUNK), &p.vmap, bar, 0, chunk * KCH, 0, p.layer, 0);
-    }
-  };
-  if (warp == 0) issue(0);
-  // ---- q tile: 64 rows (token-local x head) of 256 dims
-  for (int i = tid; i < ROWS * 32; i += THREADS_A) {
-    const int r = i >> 5, piece = i & 31, t = t0 + (r >> 3);
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (t < p.tokens) v = *reinterpret_cast<const uint4*>(p.q + (size_t)t * QD + (r & 7) * HD + piece * 8);
-    *reinterpret_cast<uint4*>(smem + OFF_Q + (r * QSTRIDE + piece * 8) * 2) = v;
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&s_tmem), TM_COLS);
+    ptx::tmem_relinquish();
   }
+  ptx::tc_fence_before();
   __syncthreads();
-  uint32_t qf[HD / 16][4];
-  {
-    const uint32_t qaddr = ptx::smem_u32(smem + OFF_Q) + (((rg * 16) + (lane & 15)) * QSTRIDE + (lane >> 4) * 8) * 2;
-#pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) ptx::ldmatrix_x4(qaddr + kk * 32, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
-  }
-  float oa[16][4];
-#pragma unroll
-  for (int i = 0; i < 16; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) oa[i][j] = 0.f;
-  float m_lo = -1e30f, m_hi = -1e30f, l_lo = 0.f, l_hi = 0.f;
+  ptx::tc_fence_after();
+  const uint32_t tmem = s_tmem;
+  const bool leader = ptx::elect_one();
+  const uint32_t sbase = ptx::smem_u32(smem);
+  ptx::grid_dep_launch();
+  ptx::grid_dep_wait();
+  if (tid == 0) PFA_STAMP(0);
 
-  for (int c = 0; c < npc; ++c) {
-    const int s = c % STG;
-    if (warp == 0 && c + 1 < npc) {
-      // the stage of chunk c + 1 held chunk c + 1 - STG: every warp must be done with it
-      if (c + 1 >= STG && !wait_bar(p.status, p.wait_limit, empty + 8 * ((c + 1) % STG), (uint32_t)(((c + 1) / STG - 1) & 1), 5)) return;
-      issue(c + 1);
+  if (warp == 0) {
+    // ---- producer: Q once, the key chunks twice (pass 1, pass 2), the V^T chunks in pass 2
+    if (leader) {
+      ptx::mbar_expect_tx(q_full, Q_BYTES);
+      for (int kb = 0; kb < 4; ++kb)
+        ptx::tma_load_2d(sbase + OFF_Q + kb * (ROWS * 128), &p.qmap, q_full, kb * 64, blockIdx.x * ROWS);
+      PFA_STAMP(1);
     }
-    if (!wait_bar(p.status, p.wait_limit, full + 8 * s, (uint32_t)((c / STG) & 1), 6)) return;
-    const uint32_t ks = ptx::smem_u32(smem + OFF_K + s * KV_CHUNK), vs = ptx::smem_u32(smem + OFF_V + s * KV_CHUNK);
-    // ---- S = Q K^T for this warp's 16 rows and the chunk's 64 keys
-    float sc[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float e[4] = {0.f, 0.f, 0.f, 0.f}, o[4] = {0.f, 0.f, 0.f, 0.f};
-      // key row r = 8 j + (lane & 7); 16-byte piece c of the row sits at piece c ^ (r & 7) of its 128-byte line
-      const uint32_t krow = ks + (j * 8 + (lane & 7)) * 128;
-      const uint32_t ksw = lane & 7, kc = lane >> 3;
-#pragma unroll
-      for (int kk = 0; kk < HD / 16; kk += 2) {
-        uint32_t b0, b1, b2, b3;
-        ptx::ldmatrix_x4(krow + (kk >> 2) * (64 * 128) + ((((kk & 3) * 2 + kc) ^ ksw) << 4), b0, b1, b2, b3);
-        ptx::mma_16816(e, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
-        ptx::mma_16816(o, qf[kk + 1][0], qf[kk + 1][1], qf[kk + 1][2], qf[kk + 1][3], b2, b3);
+    for (int i = 0; i < 2 * npc; ++i) {
+      const int c = i < npc ? i : i - npc, slot = i & 1;
+      if (!wait_bar(p.status, p.wait_limit, k_empty + 8 * slot, ((i >> 1) & 1) ^ 1, 1)) break;
+      if (leader) {
+        ptx::mbar_expect_tx(k_full + 8 * slot, K_BYTES);
+        ptx::tma_load_5d(sbase + OFF_K + slot * K_BYTES, &p.kmap, k_full + 8 * slot, 0, c * KCH, 0, p.layer, 0);
       }
-      const uint8_t* kv = smem + OFF_VALID + s * KCH + j * 8 + 2 * qd;
-      const bool v0 = kv[0] != 0, v1 = kv[1] != 0;
-      sc[j][0] = v0 ? rb(e[0] + o[0]) * 0.0625f : -INFINITY; sc[j][1] = v1 ? rb(e[1] + o[1]) * 0.0625f : -INFINITY;
-      sc[j][2] = v0 ? rb(e[2] + o[2]) * 0.0625f : -INFINITY; sc[j][3] = v1 ? rb(e[3] + o[3]) * 0.0625f : -INFINITY;
-    }
-    // ---- online softmax, rows g and g + 8 of the group (a row's 64 scores live in the four lanes of a quad)
-    float cm_lo = -INFINITY, cm_hi = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { cm_lo = fmaxf(cm_lo, fmaxf(sc[j][0], sc[j][1])); cm_hi = fmaxf(cm_hi, fmaxf(sc[j][2], sc[j][3])); }
-    cm_lo = fmaxf(cm_lo, __shfl_xor_sync(0xffffffffu, cm_lo, 1)); cm_lo = fmaxf(cm_lo, __shfl_xor_sync(0xffffffffu, cm_lo, 2));
-    cm_hi = fmaxf(cm_hi, __shfl_xor_sync(0xffffffffu, cm_hi, 1)); cm_hi = fmaxf(cm_hi, __shfl_xor_sync(0xffffffffu, cm_hi, 2));
-    const float mn_lo = fmaxf(m_lo, cm_lo), mn_hi = fmaxf(m_hi, cm_hi);
-    const float al_lo = __expf(m_lo - mn_lo), al_hi = __expf(m_hi - mn_hi);
-    m_lo = mn_lo; m_hi = mn_hi;
-    l_lo *= al_lo; l_hi *= al_hi;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) { oa[i][0] *= al_lo; oa[i][1] *= al_lo; oa[i][2] *= al_hi; oa[i][3] *= al_hi; }
-    uint32_t pf_[4][4];                 // P as A fragments: k-step kk covers keys 16 kk .. 16 kk + 15 (score tiles 2 kk, 2 kk + 1)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float p00 = __expf(sc[j][0] - mn_lo), p01 = __expf(sc[j][1] - mn_lo);
-      const float p10 = __expf(sc[j][2] - mn_hi), p11 = __expf(sc[j][3] - mn_hi);
-      l_lo += p00 + p01; l_hi += p10 + p11;
-      pf_[j >> 1][(j & 1) * 2] = pack2(p00, p01);
-      pf_[j >> 1][(j & 1) * 2 + 1] = pack2(p10, p11);
-    }
-    // ---- O += P V for this warp's 128 output dims (segments 2 dh and 2 dh + 1)
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-      // value row r = 16 kk + (lane & 7) + 8 ((lane >> 3) & 1); dims: segment, then 16-byte piece (lane >> 4) + 2 pp
-      const uint32_t vsw = lane & 7;
-#pragma unroll
-      for (int sg = 0; sg < 2; ++sg) {
-        const uint32_t vrow = vs + (dh * 2 + sg) * (64 * 128) + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 128;
-#pragma unroll
-        for (int pp = 0; pp < 4; ++pp) {
-          uint32_t r0, r1, r2, r3;
-          ptx::ldmatrix_x4_trans(vrow + ((((uint32_t)(lane >> 4) + 2 * pp) ^ vsw) << 4), r0, r1, r2, r3);
-          ptx::mma_16816(oa[sg * 8 + pp * 2], pf_[kk][0], pf_[kk][1], pf_[kk][2], pf_[kk][3], r0, r1);
-          ptx::mma_16816(oa[sg * 8 + pp * 2 + 1], pf_[kk][0], pf_[kk][1], pf_[kk][2], pf_[kk][3], r2, r3);
+      if (i >= npc) {
+        const int vslot = c & 1;
+        if (!wait_bar(p.status, p.wait_limit, v_empty + 8 * vslot, ((c >> 1) & 1) ^ 1, 2)) break;
+        if (leader) {
+          ptx::mbar_expect_tx(v_full + 8 * vslot, V_BYTES);
+          ptx::tma_load_2d(sbase + OFF_V + vslot * V_BYTES, &p.vtmap, v_full + 8 * vslot, c * KCH, 0);
         }
       }
     }
-    __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(empty + 8 * s);
-  }
-  // ---- normalise and store: row g -> token 2 rg, row g + 8 -> token 2 rg + 1, head g
-  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-  const float il_lo = 1.0f / l_lo, il_hi = 1.0f / l_hi;
-  const int ta = t0 + 2 * rg, tb = ta + 1;
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    const uint32_t idesc_s = ptx::umma_idesc_bf16(ROWS, KCH), idesc_o = ptx::umma_idesc_bf16(ROWS, HD);
+    const uint64_t qdesc = ptx::umma_smem_desc(sbase + OFF_Q), kdesc = ptx::umma_smem_desc(sbase + OFF_K);
+    const uint64_t vdesc = ptx::umma_smem_desc(sbase + OFF_V), pdesc = ptx::umma_smem_desc(sbase + OFF_P);
+    bool ok = wait_bar(p.status, p.wait_limit, q_full, 0, 3);
+    if (leader) PFA_STAMP(2);
+    // S tile i (i counts through both passes) into S buffer i & 1 from key stage i & 1
+    auto issue_s = [&](int i) -> bool {
+      const int slot = i & 1;
+      if (!wait_bar(p.status, p.wait_limit, k_full + 8 * slot, (i >> 1) & 1, 4)) return false;
+      if (!wait_bar(p.status, p.wait_limit, s_empty + 8 * slot, ((i >> 1) & 1) ^ 1, 5)) return false;
+      ptx::tc_fence_after();
+      if (leader) {
+        const uint32_t d = tmem + TM_S + slot * KCH;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int col = g * HD + dh * 128 + i * 8 + 2 * qd;
-    if (ta < p.tokens) *reinterpret_cast<uint32_t*>(p.out + (size_t)ta * QD + col) = pack2(oa[i][0] * il_lo, oa[i][1] * il_lo);
-    if (tb < p.tokens) *reinterpret_cast<uint32_t*>(p.out + (size_t)tb * QD + col) = pack2(oa[i][2] * il_hi, oa[i][3] * il_hi);
+        for (int kb = 0; kb < 4; ++kb)
+          umma_k64(d, qdesc + (uint64_t)(kb * (ROWS * 128 >> 4)), kdesc + (uint64_t)((slot * K_BYTES + kb * (KCH * 128)) >> 4),
+                   idesc_s, kb ? 1u : 0u);
+        ptx::umma_commit(k_empty + 8 * slot);
+        ptx::umma_commit(s_full + 8 * slot);
+      }
+      return true;
+    };
+    // O += P V for chunk c of pass 2
+    auto issue_pv = [&](int c) -> bool {
+      const int slot = c & 1;
+      if (!wait_bar(p.status, p.wait_limit, p_full + 8 * slot, (c >> 1) & 1, 6)) return false;
+      if (!wait_bar(p.status, p.wait_limit, v_full + 8 * slot, (c >> 1) & 1, 7)) return false;
+      ptx::tc_fence_after();
+      if (leader) {
+        umma_k64(tmem + TM_O, pdesc + (uint64_t)((slot * P_BYTES) >> 4), vdesc + (uint64_t)((slot * V_BYTES) >> 4), idesc_o,
+                 c ? 1u : 0u);
+        ptx::umma_commit(v_empty + 8 * slot);
+        ptx::umma_commit(p_empty + 8 * slot);
+      }
+      return true;
+    };
+    for (int i = 0; ok && i < npc; ++i) {
+      ok = issue_s(i);
+      if (leader && i < 4) PFA_STAMP(3 + i);
+    }
+    if (leader) PFA_STAMP(7);
+    for (int c = 0; ok && c < npc; ++c) {
+      ok = issue_s(npc + c);
+      if (ok && c >= 1) {
+        ok = issue_pv(c - 1);
+        if (leader && c <= 3) PFA_STAMP(7 + c);
+      }
+    }
+    if (ok) ok = issue_pv(npc - 1);
+    if (leader) PFA_STAMP(11);
+    if (ok && leader) ptx::umma_commit(o_full);
+  } else {
+    // ---- softmax threads: thread = query row (TMEM lane); warp w may touch lanes 32 (w % 4) .. only
+    const int quad = warp & 3, row = quad * 32 + lane, st = tid - 64;
+    // validity bits of all keys, once
+    for (int w = (st >> 5); w < MASK_WORDS; w += 4) {
+      const int t = w * 32 + lane;
+      const unsigned bits = __ballot_sync(0xffffffffu, t < p.tokens && p.valid[t] != 0);
+      if (lane == 0) s_mask[w] = bits;
+      if (w * 32 >= p.tokens) break;
+    }
+    ptx::named_bar_sync(1, 128);
+    const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
+    bool ok = true;
+    float mraw = -INFINITY;
+    // pass 1: the row maximum over the valid keys
+    for (int i = 0; ok && i < npc; ++i) {
+      const int slot = i & 1;
+      if (!wait_bar(p.status, p.wait_limit, s_full + 8 * slot, (i >> 1) & 1, 8)) { ok = false; break; }
+      ptx::tc_fence_after();
+      uint32_t r0[32], r1[32];
+      ptx::tmem_ld_32x32(trow + TM_S + slot * KCH, r0);
+      ptx::tmem_ld_32x32(trow + TM_S + slot * KCH + 32, r1);
+      ptx::tmem_wait_ld();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(s_empty + 8 * slot);
+      // (rounding to BF16 and the scale are monotonic: the maximum of the raw scores is rounded once, after the pass)
+      const uint32_t m0 = s_mask[2 * i], m1 = s_mask[2 * i + 1];
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if ((m0 & m1) == 0xffffffffu) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(r0[j]));
+          mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(r1[j]));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          mx[j & 3] = fmaxf(mx[j & 3], (m0 & (1u << j)) ? __uint_as_float(r0[j]) : -INFINITY);
+          mx[j & 3] = fmaxf(mx[j & 3], (m1 & (1u << j)) ? __uint_as_float(r1[j]) : -INFINITY);
+        }
+      }
+      mraw = fmaxf(mraw, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
+    }
+    const float m = fmaxf(rb(mraw) * 0.0625f, -1e30f);
+    if (st == 0) PFA_STAMP(15);
+    // pass 2: probabilities
+    float l = 0.f;
+    constexpr float SCALE_LOG2E = 0.0625f * 1.4426950408889634f;
+    const float mneg = -m * 1.4426950408889634f;
+    const uint32_t prow = sbase + OFF_P + row * 128, psw = row & 7;
+    for (int c = 0; ok && c < npc; ++c) {
+      const int i = npc + c, slot = i & 1, pslot = c & 1;
+      if (!wait_bar(p.status, p.wait_limit, s_full + 8 * slot, (i >> 1) & 1, 9)) { ok = false; break; }
+      if (st == 0 && c < 2) PFA_STAMP(16 + 2 * c);
+      ptx::tc_fence_after();
+      uint32_t r0[32], r1[32];
+      ptx::tmem_ld_32x32(trow + TM_S + slot * KCH, r0);
+      ptx::tmem_ld_32x32(trow + TM_S + slot * KCH + 32, r1);
+      ptx::tmem_wait_ld();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(s_empty + 8 * slot);
+      if (st == 0 && c == 1) PFA_STAMP(12);
+      const uint32_t m0 = s_mask[2 * c], m1 = s_mask[2 * c + 1];
+      // p = exp(bf16(s) / 16 - m) as one FMA and one ex2 per score; every score is computed, masked ones are replaced
+      // afterwards, so that the 64 chains stay independent of each other
+      uint32_t pk[32];
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      const bool all_valid = (m0 & m1) == 0xffffffffu;
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const uint32_t s0 = pack2(__uint_as_float(r0[j]), __uint_as_float(r0[j + 1]));
+        const uint32_t s1 = pack2(__uint_as_float(r1[j]), __uint_as_float(r1[j + 1]));
+        float a = ptx::ex2_approx(fmaf(lo16(s0), SCALE_LOG2E, mneg)), b = ptx::ex2_approx(fmaf(hi16(s0), SCALE_LOG2E, mneg));
+        float e = ptx::ex2_approx(fmaf(lo16(s1), SCALE_LOG2E, mneg)), f = ptx::ex2_approx(fmaf(hi16(s1), SCALE_LOG2E, mneg));
+        if (!all_valid) {
+          a = (m0 & (1u << j)) ? a : 0.f; b = (m0 & (2u << j)) ? b : 0.f;
+          e = (m1 & (1u << j)) ? e : 0.f; f = (m1 & (2u << j)) ? f : 0.f;
+        }
+        ls[(j >> 1) & 3] += (a + b) + (e + f);
+        pk[j >> 1] = pack2(a, b);
+        pk[16 + (j >> 1)] = pack2(e, f);
+      }
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      if (st == 0 && c == 1) PFA_STAMP(13);
+      // the P buffer is free once the P V of chunk c - 2 has read it
+      if (!wait_bar(p.status, p.wait_limit, p_empty + 8 * pslot, ((c >> 1) & 1) ^ 1, 10)) { ok = false; break; }
+      if (st == 0 && c == 1) PFA_STAMP(14);
+      const uint32_t dst = prow + pslot * P_BYTES;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)   // 16-byte piece ch of the row sits at piece ch ^ (row & 7) of its 128-byte line
+        ptx::st_shared_v4(dst + (((uint32_t)ch ^ psw) << 4), pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+      if (st == 0 && c == 1) PFA_STAMP(20);
+      ptx::fence_proxy_async_shared();
+      if (st == 0 && c == 1) PFA_STAMP(23);
+      ptx::mbar_arrive(p_full + 8 * pslot);
+      if (st == 0 && c < 2) PFA_STAMP(17 + 2 * c);
+    }
+    // ---- O / l -> BF16: row = token_local * 8 + head, so a row's 256 dims are contiguous in [tokens, 2048]
+    if (ok && wait_bar(p.status, p.wait_limit, o_full, 0, 11)) {
+      if (st == 0) PFA_STAMP(21);
+      ptx::tc_fence_after();
+      const float il = 1.0f / l;
+      const int token = blockIdx.x * TOK + (row >> 3);
+      __nv_bfloat16* orow = p.out + (size_t)token * QD + (row & 7) * HD;
+#pragma unroll 1
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(trow + TM_O + c0, r);
+        ptx::tmem_wait_ld();
+        if (token < p.tokens) {
+          uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            dst[j] = make_uint4(pack2(__uint_as_float(r[8 * j]) * il, __uint_as_float(r[8 * j + 1]) * il),
+                                pack2(__uint_as_float(r[8 * j + 2]) * il, __uint_as_float(r[8 * j + 3]) * il),
+                                pack2(__uint_as_float(r[8 * j + 4]) * il, __uint_as_float(r[8 * j + 5]) * il),
+                                pack2(__uint_as_float(r[8 * j + 6]) * il, __uint_as_float(r[8 * j + 7]) * il));
+        }
+      }
+      ptx::tc_fence_before();
+      if (st == 0) PFA_STAMP(22);
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, TM_COLS);
   }
 }
 }  // namespace pfa
@@ -532,10 +695,12 @@ struct pi05_prefill {
   uint8_t* ws = nullptr;
   size_t ws_bytes = 0;
   bool bound = false;
+  bool overlap = PI05_PREFILL_OVERLAP != 0;   // launch each kernel so that its set-up overlaps the tail of the one before
   long long wait_limit = 4000000000ll;
   std::string last_error;
   // workspace offsets
-  size_t off_status, off_x, off_n, off_q, off_mixed, off_act, off_rope, off_pos;
+  size_t off_status, off_x, off_n, off_q, off_mixed, off_act, off_rope, off_pos, off_vt;
+  int vt_stride = 0;
 };
 
 namespace {
@@ -569,6 +734,20 @@ bool map_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, uin
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The layer's V^T [256 dims, tokens] with rows `stride` elements apart: box {64 keys, 256 dims}; keys at and beyond
+// `tokens` read as zeros.
+bool map_vt(CUtensorMap* m, const void* base, uint64_t tokens, uint64_t stride) {
+  EncodeTiledFn enc = encoder();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {tokens, 256};
+  cuuint64_t strides[1] = {stride * 2};
+  cuuint32_t box[2] = {64, 256};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Keys / values of all layers as the attention's tiled copies read them: {64 dims, tokens, 4 segments, layers, 1}.
 bool map_kv(CUtensorMap* m, const void* base, uint64_t tokens) {
   EncodeTiledFn enc = encoder();
@@ -591,6 +770,21 @@ struct Guard {
 
 size_t up(size_t v) { return (v + 255) / 256 * 256; }
 
+// Launch with programmatic stream serialisation: the kernel may begin (set up its barriers and tensor memory) while the
+// kernel before it in the stream drains; it reads nothing that kernel wrote before its grid_dep_wait.
+template <typename... Params, typename... Args>
+cudaError_t launch_after(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool overlap,
+                         Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = overlap ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <int EPI, int BN>
 cudaError_t launch_gemm(pi05_prefill* h, pf::GemmParams& gp, cudaStream_t stream) {
   static bool attr_set[64] = {};
@@ -602,8 +796,7 @@ cudaError_t launch_gemm(pi05_prefill* h, pf::GemmParams& gp, cudaStream_t stream
   }
   const int tiles = gp.n_tiles * gp.m_tiles;
   const int grid = tiles < h->sms ? tiles : h->sms;
-  pf::gemm_kernel<EPI, BN><<<grid, pf::GEMM_THREADS, pf::RING_BYTES + 1024, stream>>>(gp);
-  return cudaGetLastError();
+  return launch_after(pf::gemm_kernel<EPI, BN>, dim3(grid), dim3(pf::GEMM_THREADS), pf::RING_BYTES + 1024, stream, h->overlap, gp);
 }
 
 }  // namespace
@@ -636,6 +829,8 @@ int pi05_prefill_create(int device, int max_tokens, pi05_prefill_t* out) {
   h->off_act = add(P * (size_t)pf::FFN * 2);
   h->off_rope = add(P * 128 * 4);
   h->off_pos = add(P * 4);
+  h->vt_stride = (max_tokens + 63) / 64 * 64;
+  h->off_vt = add((size_t)HD * h->vt_stride * 2);
   h->ws_bytes = off;
   *out = h;
   return PI05_OK;
@@ -691,6 +886,7 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
   uint32_t* rope = reinterpret_cast<uint32_t*>(ptr(h->off_rope));
   int* pos = reinterpret_cast<int*>(ptr(h->off_pos));
   unsigned int* status = reinterpret_cast<unsigned int*>(ptr(h->off_status));
+  __nv_bfloat16* vt = reinterpret_cast<__nv_bfloat16*>(ptr(h->off_vt));
   const __nv_bfloat16* const* w = reinterpret_cast<const __nv_bfloat16* const*>(h->weights);
   enum { LN1 = 0, LN2, LQ, LK, LV, LO, LG, LU, LD };
   __nv_bfloat16* K = static_cast<__nv_bfloat16*>(keys);
@@ -708,13 +904,15 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
   memset(&base, 0, sizeof base);
   base.tokens = P; base.m_tiles = (P + pf::BM - 1) / pf::BM;
   base.x = x; base.act = act; base.q = q; base.rope = rope; base.status = status; base.wait_limit = h->wait_limit;
-  CUtensorMap a_n, a_mixed, a_act, wq, wk, wv, wo, wg, wu, wd, kmap, vmap;
+  base.vt = vt; base.vt_stride = h->vt_stride;
+  CUtensorMap a_n, a_mixed, a_act, wq, wk, wv, wo, wg, wu, wd, kmap, qmap, vtmap;
   bool ok = map_2d(&a_n, nrm, pf::H, P, pf::BM) && map_2d(&a_mixed, mixed, QD, P, pf::BM) &&
             map_2d(&a_act, act, pf::FFN, P, pf::BM) &&
             map_2d(&wq, w[LQ], pf::H, (uint64_t)pf::LAYERS * QD, 128) && map_2d(&wk, w[LK], pf::H, (uint64_t)pf::LAYERS * HD, 128) &&
             map_2d(&wv, w[LV], pf::H, (uint64_t)pf::LAYERS * HD, 128) && map_2d(&wo, w[LO], QD, (uint64_t)pf::LAYERS * pf::H, 64) &&
             map_2d(&wg, w[LG], pf::H, (uint64_t)pf::LAYERS * pf::FFN, 128) && map_2d(&wu, w[LU], pf::H, (uint64_t)pf::LAYERS * pf::FFN, 128) &&
-            map_2d(&wd, w[LD], pf::FFN, (uint64_t)pf::LAYERS * pf::H, 64) && map_kv(&kmap, K, P) && map_kv(&vmap, V, P);
+            map_2d(&wd, w[LD], pf::FFN, (uint64_t)pf::LAYERS * pf::H, 64) && map_kv(&kmap, K, P) && map_2d(&qmap, q, HD, (uint64_t)P * 8, 128) &&
+            map_vt(&vtmap, vt, P, h->vt_stride);
   if (!ok) { h->last_error = "cuTensorMapEncodeTiled failed"; return PI05_ERR_CUDA; }
 
   static bool att_attr[64] = {};
@@ -725,13 +923,14 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
   }
   pf::pfa::AttnParams ap;
   memset(&ap, 0, sizeof ap);
-  ap.kmap = kmap; ap.vmap = vmap;
-  ap.q = q; ap.valid = static_cast<const uint8_t*>(valid); ap.out = mixed;
+  ap.qmap = qmap; ap.kmap = kmap; ap.vtmap = vtmap;
+  ap.valid = static_cast<const uint8_t*>(valid); ap.out = mixed;
   ap.tokens = P; ap.status = status; ap.wait_limit = h->wait_limit;
 
   const int norm_blocks = (P + 7) / 8;
   for (int l = 0; l < n_layers; ++l) {
-    pf::rmsnorm_kernel<<<norm_blocks, 256, 0, stream>>>(x, w[LN1] + (size_t)l * pf::H, nrm, P);
+    if ((e = launch_after(pf::rmsnorm_kernel, dim3(norm_blocks), dim3(256), 0, stream, h->overlap && l > 0,
+                          (const __nv_bfloat16*)x, w[LN1] + (size_t)l * pf::H, nrm, P)) != cudaSuccess) break;
     {
       pf::GemmParams gp = base;
       gp.a = a_n; gp.b0 = gp.b1 = wq; gp.b2 = wk; gp.b3 = wv;
@@ -740,7 +939,8 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
       if ((e = launch_gemm<pf::EPI_QKV, 256>(h, gp, stream)) != cudaSuccess) break;
     }
     ap.layer = l;
-    pf::pfa::attention_kernel<<<(P + pf::pfa::TOK - 1) / pf::pfa::TOK, pf::pfa::THREADS_A, pf::pfa::SMEM_A, stream>>>(ap);
+    if ((e = launch_after(pf::pfa::attention_kernel, dim3((P + pf::pfa::TOK - 1) / pf::pfa::TOK), dim3(pf::pfa::THREADS_A),
+                          pf::pfa::SMEM_A, stream, h->overlap, ap)) != cudaSuccess) break;
     {
       pf::GemmParams gp = base;
       gp.a = a_mixed; gp.b0 = gp.b1 = wo;
@@ -748,7 +948,8 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
       if ((e = launch_gemm<pf::EPI_RESID, 128>(h, gp, stream)) != cudaSuccess) break;
     }
     if (l + 1 == n_layers) break;          // the last MLP does not affect any cached key or value
-    pf::rmsnorm_kernel<<<norm_blocks, 256, 0, stream>>>(x, w[LN2] + (size_t)l * pf::H, nrm, P);
+    if ((e = launch_after(pf::rmsnorm_kernel, dim3(norm_blocks), dim3(256), 0, stream, h->overlap,
+                          (const __nv_bfloat16*)x, w[LN2] + (size_t)l * pf::H, nrm, P)) != cudaSuccess) break;
     {
       pf::GemmParams gp = base;
       gp.a = a_n; gp.b0 = wg; gp.b1 = wu;
