@@ -62,6 +62,11 @@ struct GemmParams {
   const uint32_t* rope;            // [tokens][128]: cos BF16 | sin BF16 << 16
   unsigned int* status;
   long long wait_limit;
+  // stream-K launches: partial sums [CTA][128 x BN] FP32 and one flag per CTA, which holds the number of the launch (of
+  // this prefill) whose partial sums the CTA wrote last
+  float* sk_partial;
+  unsigned int* sk_flags;
+  unsigned int sk_epoch;
 };
 
 __device__ __forceinline__ float rb(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
@@ -108,8 +113,45 @@ __device__ __forceinline__ void umma_stage4(uint32_t d_tmem, uint64_t adesc, uin
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(commit_bar) : "memory");
 }
 
+// The work of one CTA of a GEMM launch, as segments (tile, first k block, one past the last k block).
+// SK = false: whole tiles blockIdx.x, blockIdx.x + gridDim.x, ...  SK = true ("stream-K"): the launch's tiles x k blocks,
+// taken as one sequence of units, are cut into gridDim.x contiguous, equal ranges, so that a GEMM with fewer tiles than
+// the GPU has SMs (or a ragged last wave) still keeps every SM busy for the same time.  A range that begins inside a
+// tile makes its CTA a contributor to that tile: it leaves its FP32 partial sums in the workspace and raises a flag.  A
+// range that ends inside a tile (having begun it) makes its CTA the tile's owner: it adds the partial sums of the
+// CTAs that follow it, whose ranges hold the rest of the tile, and runs the fused epilogue.  An owner's wait is for CTAs
+// of higher index only, and the partial segment those wait for nobody, so no wait can close a circle.
+template <bool SK>
+struct Segments {
+  int kblocks, ntiles, tile, stride;
+  long long u, uend;
+  __device__ Segments(int kblocks_, int ntiles_) : kblocks(kblocks_), ntiles(ntiles_) {
+    if (SK) {
+      const long long total = (long long)ntiles * kblocks;
+      u = total * blockIdx.x / gridDim.x;
+      uend = total * (blockIdx.x + 1) / gridDim.x;
+    } else {
+      tile = blockIdx.x; stride = gridDim.x;
+    }
+  }
+  __device__ bool next(int& t, int& kb0, int& kb1) {
+    if (SK) {
+      if (u >= uend) return false;
+      t = (int)(u / kblocks);
+      kb0 = (int)(u - (long long)t * kblocks);
+      const long long rest = uend - u;
+      kb1 = rest < kblocks - kb0 ? kb0 + (int)rest : kblocks;
+      u += kb1 - kb0;
+      return true;
+    }
+    if (tile >= ntiles) return false;
+    t = tile; kb0 = 0; kb1 = kblocks; tile += stride;
+    return true;
+  }
+};
+
 // out[tokens, N] = A[tokens, K] . W[N, K]^T with a fused epilogue; tile = 128 tokens x BN features.
-template <int EPI, int BN>
+template <int EPI, int BN, bool SK>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
   constexpr int NST = RING_BYTES / STAGE;
@@ -117,14 +159,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
   static_assert(NST >= 4 && TCOLS <= 512, "ring / TMEM budget");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bars[2 * NST + 4];
+  __shared__ uint64_t bars[2 * NST + 6];
   __shared__ uint32_t s_tmem;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t ring = ptx::smem_u32(smem);
   const uint32_t full = ptx::smem_u32(bars), empty = full + 8 * NST, tfull = empty + 8 * NST, tempty = tfull + 16;
+  const uint32_t fix = tempty + 16;      // stream-K: a peer's partial sums have landed in half of the ring
   if (tid == 0) {
     for (int i = 0; i < NST; ++i) { ptx::mbar_init(full + 8 * i, 1); ptx::mbar_init(empty + 8 * i, 1); }
-    for (int i = 0; i < 2; ++i) { ptx::mbar_init(tfull + 8 * i, 1); ptx::mbar_init(tempty + 8 * i, 128); }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(tfull + 8 * i, 1); ptx::mbar_init(tempty + 8 * i, 128); ptx::mbar_init(fix + 8 * i, 1);
+    }
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_shared();
   }
@@ -141,11 +186,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
   // everything up to here overlapped the tail of the kernel before; its outputs are read from here on
   ptx::grid_dep_launch();
   ptx::grid_dep_wait();
+  Segments<SK> segs(p.kblocks, ntiles);
+  int tile, kb0, kb1;
 
   if (warp == 0) {
-    // ---- producer: both operands of every stage, tile after tile (consecutive tiles share the weight rows)
+    // ---- producer: both operands of every stage, segment after segment (consecutive tiles share the weight rows)
     uint32_t slot = 0, par = 0;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    while (segs.next(tile, kb0, kb1)) {
       const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
       const CUtensorMap *m0 = &p.b0, *m1 = &p.b1;
       int r0, r1;
@@ -160,7 +207,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
         r0 = p.layer * H + nt * BN;
         r1 = r0 + BN / 2;
       }
-      for (int kb = 0; kb < p.kblocks; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!wait_bar(p.status, p.wait_limit, empty + 8 * slot, par ^ 1, 1)) return;
         if (leader) {
           const uint32_t bar = full + 8 * slot, dst = ring + slot * STAGE;
@@ -177,35 +224,115 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
     const uint32_t idesc = ptx::umma_idesc_bf16(BM, BN);
     const uint64_t adesc0 = ptx::umma_smem_desc(ring), bdesc0 = ptx::umma_smem_desc(ring + A_BYTES);
     uint32_t slot = 0, par = 0, it = 0;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
+    bool ok = true;
+    while (ok && segs.next(tile, kb0, kb1)) {
       const uint32_t buf = it & 1;
       if (!wait_bar(p.status, p.wait_limit, tempty + 8 * buf, ((it >> 1) & 1) ^ 1, 2)) break;
       ptx::tc_fence_after();
       const uint32_t d = tmem + buf * BN;
-      for (int kb = 0; kb < p.kblocks; ++kb) {
-        if (!wait_bar(p.status, p.wait_limit, full + 8 * slot, par, 3)) { kb = p.kblocks; tile = ntiles; break; }
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!wait_bar(p.status, p.wait_limit, full + 8 * slot, par, 3)) { ok = false; break; }
         const uint64_t off = (uint64_t)(slot * (STAGE >> 4));
-        if (leader) umma_stage4(d, adesc0 + off, bdesc0 + off, idesc, kb ? 1u : 0u, empty + 8 * slot);
+        if (leader) umma_stage4(d, adesc0 + off, bdesc0 + off, idesc, kb > kb0 ? 1u : 0u, empty + 8 * slot);
         if (++slot == NST) { slot = 0; par ^= 1; }
       }
-      if (leader) ptx::umma_commit(tfull + 8 * buf);
+      if (ok && leader) ptx::umma_commit(tfull + 8 * buf);
+      ++it;
     }
   } else {
     // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) ..; thread = token row of the tile
     const int quad = warp & 3, row = quad * 32 + lane;
     uint32_t it = 0;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
+    while (segs.next(tile, kb0, kb1)) {
       const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
       const uint32_t buf = it & 1;
       const int token = mt * BM + row;
       const bool live = token < p.tokens;
       if (!wait_bar(p.status, p.wait_limit, tfull + 8 * buf, (it >> 1) & 1, 4)) break;
+      ++it;
       ptx::tc_fence_after();
       const uint32_t t0 = tmem + buf * BN + ((uint32_t)(quad * 32) << 16);
-      if (EPI == EPI_RESID) {
-        __nv_bfloat16* xr = p.x + (size_t)token * H + nt * BN;
+      // partial sums of a tile in the workspace: [CTA][column][row] FP32, so that a warp's 32 rows of one column are one line
+      if (SK && kb0 > 0) {
+        // contributor: the tile's owner is a CTA before this one
+        float* mine = p.sk_partial + (size_t)blockIdx.x * (BM * BN) + row;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(t0 + c, r);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) __stcg(mine + (size_t)(c + j) * BM, __uint_as_float(r[j]));
+        }
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(tempty + 8 * buf);
+        ptx::named_bar_sync(1, 128);                       // every row's partial sums are written ...
+        if (tid == 64) ptx::st_release(p.sk_flags + blockIdx.x, p.sk_epoch);   // ... before the flag says so
+        continue;
+      }
+      if (SK && kb1 < p.kblocks) {
+        // owner of a tile whose later k blocks went to the CTAs after this one (their ranges begin inside this tile):
+        // wait for their flags (bounded), then pull their partial sums through the ring - which is idle, this being the
+        // CTA's last segment with all its MMAs complete - half a tile at a time, and add them to the accumulator in TMEM
+        const long long total = (long long)ntiles * p.kblocks, tile_end = (long long)(tile + 1) * p.kblocks;
+        const int first_peer = blockIdx.x + 1;
+        int npeers = 0;
+        while (first_peer + npeers < (int)gridDim.x && total * (first_peer + npeers) / gridDim.x < tile_end) ++npeers;
+        bool ok = true;
+        for (int j = 0; ok && j < npeers; ++j) {
+          const long long t_start = clock64();
+          while (ptx::ld_acquire(p.sk_flags + first_peer + j) != p.sk_epoch) {
+            if (ptx::ld_relaxed(p.status) != 0u) { ok = false; break; }
+            if (clock64() - t_start > p.wait_limit) {
+              if (atomicCAS(p.status, 0u, 12u) == 0u) p.status[1] = blockIdx.x;
+              ok = false;
+              break;
+            }
+            __nanosleep(20);
+          }
+        }
+        if (!ok) break;
+        constexpr int HALF_COLS = BN / 2, HALF_BYTES = HALF_COLS * BM * 4;
+        static_assert(2 * HALF_BYTES <= RING_BYTES, "two half tiles of partial sums fit the ring");
+        const int items = 2 * npeers;
+        auto fetch = [&](int k) {   // item k = (peer k / 2, half k % 2) into ring half k % 2
+          const float* src = p.sk_partial + (size_t)(first_peer + (k >> 1)) * (BM * BN) + (size_t)(k & 1) * HALF_COLS * BM;
+          const uint32_t bar = fix + 8 * (k & 1), dst = ring + (k & 1) * HALF_BYTES;
+          ptx::mbar_expect_tx(bar, HALF_BYTES);
+          for (int q4 = 0; q4 < HALF_BYTES; q4 += 16384) ptx::bulk_load(dst + q4, reinterpret_cast<const uint8_t*>(src) + q4, 16384, bar);
+        };
+        if (tid == 64) { fetch(0); if (items > 1) fetch(1); }
+        for (int k = 0; ok && k < items; ++k) {
+          if (!wait_bar(p.status, p.wait_limit, fix + 8 * (k & 1), (k >> 1) & 1, 13)) { ok = false; break; }
+          const float* part = reinterpret_cast<const float*>(smem + (k & 1) * HALF_BYTES) + row;
+#pragma unroll 1
+          for (int c = 0; c < HALF_COLS; c += 32) {
+            uint32_t r[32];
+            const uint32_t ta = t0 + (k & 1) * HALF_COLS + c;
+            ptx::tmem_ld_32x32(ta, r);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + part[(c + j) * BM]);
+            ptx::tmem_st_32x32(ta, r);
+          }
+          ptx::tmem_wait_st();                             // the next peer's pass reads these columns again
+          ptx::named_bar_sync(1, 128);                     // everybody has read this half of the ring
+          if (tid == 64 && k + 2 < items) fetch(k + 2);
+        }
+        if (!ok) break;
+      }
+      if (EPI == EPI_RESID) {
+        // x += bf16(acc), rounded as the reference's BF16 add does; the old values of the next 32 columns are requested
+        // before this chunk's are used (a thread's row is 4 KB away from its neighbour's, so these loads are slow ones)
+        __nv_bfloat16* xr = p.x + (size_t)(live ? token : 0) * H + nt * BN;
+        uint4 old[4], nxt[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) old[j] = reinterpret_cast<const uint4*>(xr)[j];
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          const int cn = c + 32 < BN ? c + 32 : c;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) nxt[j] = reinterpret_cast<const uint4*>(xr + cn)[j];
           uint32_t r[32];
           ptx::tmem_ld_32x32(t0 + c, r);
           ptx::tmem_wait_ld();
@@ -213,8 +340,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
             uint4* dst = reinterpret_cast<uint4*>(xr + c);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const uint4 old = dst[j];
-              const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+              const uint32_t ow[4] = {old[j].x, old[j].y, old[j].z, old[j].w};
               uint32_t nw[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
@@ -225,6 +351,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
               dst[j] = make_uint4(nw[0], nw[1], nw[2], nw[3]);
             }
           }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) old[j] = nxt[j];
         }
       } else {
         // QKV and GeGLU need columns c and c + BN / 2 of the tile together (rotary partner, gate with up)
@@ -267,20 +395,25 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
             } else {
               // RoPE (reference/pi05.py:218-229 on BF16 tensors): x cos + rotate_half(x) sin, every product and the
               // sum rounded to BF16; dims c.. pair with dims 128 + c..
-              const uint32_t* cs = p.rope + (size_t)token * 128 + c;
+              const uint4* cs4 = reinterpret_cast<const uint4*>(p.rope + (size_t)token * 128 + c);
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                float a[2], b[2];
+              for (int j4 = 0; j4 < 8; ++j4) {
+                const uint4 w4 = __ldg(cs4 + j4);
+                const uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                  const uint32_t w = cs[2 * j + e];
-                  const float co = lo16(w), si = hi16(w);
-                  const float x1 = rb(__uint_as_float(r1[2 * j + e])), x2 = rb(__uint_as_float(r2[2 * j + e]));
-                  a[e] = rb(rb(x1 * co) + rb(-x2 * si));
-                  b[e] = rb(rb(x2 * co) + rb(x1 * si));
+                for (int h = 0; h < 2; ++h) {
+                  float a[2], b[2];
+#pragma unroll
+                  for (int e = 0; e < 2; ++e) {
+                    const uint32_t w = ws[2 * h + e];
+                    const float co = lo16(w), si = hi16(w);
+                    const float x1 = rb(__uint_as_float(r1[4 * j4 + 2 * h + e])), x2 = rb(__uint_as_float(r2[4 * j4 + 2 * h + e]));
+                    a[e] = rb(rb(x1 * co) + rb(-x2 * si));
+                    b[e] = rb(rb(x2 * co) + rb(x1 * si));
+                  }
+                  o1[2 * j4 + h] = pack2(a[0], a[1]);
+                  o2[2 * j4 + h] = pack2(b[0], b[1]);
                 }
-                o1[j] = pack2(a[0], a[1]);
-                o2[j] = pack2(b[0], b[1]);
               }
             }
             __nv_bfloat16* base = nt < 8 ? p.q + (size_t)token * 2048 + nt * 256
@@ -434,12 +567,6 @@ __device__ __forceinline__ void umma_k64(uint32_t d_tmem, uint64_t adesc, uint64
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-#ifdef PI05_PFA_TRACE
-#define PFA_STAMP(i) do { if (blockIdx.x == 0) reinterpret_cast<unsigned long long*>(p.status + 16)[i] = clock64(); } while (0)
-#else
-#define PFA_STAMP(i) do { } while (0)
-#endif
-
 __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -476,7 +603,6 @@ __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_co
   const uint32_t sbase = ptx::smem_u32(smem);
   ptx::grid_dep_launch();
   ptx::grid_dep_wait();
-  if (tid == 0) PFA_STAMP(0);
 
   if (warp == 0) {
     // ---- producer: Q once, the key chunks twice (pass 1, pass 2), the V^T chunks in pass 2
@@ -484,7 +610,6 @@ __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_co
       ptx::mbar_expect_tx(q_full, Q_BYTES);
       for (int kb = 0; kb < 4; ++kb)
         ptx::tma_load_2d(sbase + OFF_Q + kb * (ROWS * 128), &p.qmap, q_full, kb * 64, blockIdx.x * ROWS);
-      PFA_STAMP(1);
     }
     for (int i = 0; i < 2 * npc; ++i) {
       const int c = i < npc ? i : i - npc, slot = i & 1;
@@ -508,7 +633,6 @@ __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_co
     const uint64_t qdesc = ptx::umma_smem_desc(sbase + OFF_Q), kdesc = ptx::umma_smem_desc(sbase + OFF_K);
     const uint64_t vdesc = ptx::umma_smem_desc(sbase + OFF_V), pdesc = ptx::umma_smem_desc(sbase + OFF_P);
     bool ok = wait_bar(p.status, p.wait_limit, q_full, 0, 3);
-    if (leader) PFA_STAMP(2);
     // S tile i (i counts through both passes) into S buffer i & 1 from key stage i & 1
     auto issue_s = [&](int i) -> bool {
       const int slot = i & 1;
@@ -540,20 +664,12 @@ __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_co
       }
       return true;
     };
-    for (int i = 0; ok && i < npc; ++i) {
-      ok = issue_s(i);
-      if (leader && i < 4) PFA_STAMP(3 + i);
-    }
-    if (leader) PFA_STAMP(7);
+    for (int i = 0; ok && i < npc; ++i) ok = issue_s(i);
     for (int c = 0; ok && c < npc; ++c) {
       ok = issue_s(npc + c);
-      if (ok && c >= 1) {
-        ok = issue_pv(c - 1);
-        if (leader && c <= 3) PFA_STAMP(7 + c);
-      }
+      if (ok && c >= 1) ok = issue_pv(c - 1);
     }
     if (ok) ok = issue_pv(npc - 1);
-    if (leader) PFA_STAMP(11);
     if (ok && leader) ptx::umma_commit(o_full);
   } else {
     // ---- softmax threads: thread = query row (TMEM lane); warp w may touch lanes 32 (w % 4) .. only
@@ -599,7 +715,6 @@ __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_co
       mraw = fmaxf(mraw, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
     }
     const float m = fmaxf(rb(mraw) * 0.0625f, -1e30f);
-    if (st == 0) PFA_STAMP(15);
     // pass 2: probabilities
     float l = 0.f;
     constexpr float SCALE_LOG2E = 0.0625f * 1.4426950408889634f;
@@ -608,7 +723,6 @@ __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_co
     for (int c = 0; ok && c < npc; ++c) {
       const int i = npc + c, slot = i & 1, pslot = c & 1;
       if (!wait_bar(p.status, p.wait_limit, s_full + 8 * slot, (i >> 1) & 1, 9)) { ok = false; break; }
-      if (st == 0 && c < 2) PFA_STAMP(16 + 2 * c);
       ptx::tc_fence_after();
       uint32_t r0[32], r1[32];
       ptx::tmem_ld_32x32(trow + TM_S + slot * KCH, r0);
@@ -616,7 +730,6 @@ __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_co
       ptx::tmem_wait_ld();
       ptx::tc_fence_before();
       ptx::mbar_arrive(s_empty + 8 * slot);
-      if (st == 0 && c == 1) PFA_STAMP(12);
       const uint32_t m0 = s_mask[2 * c], m1 = s_mask[2 * c + 1];
       // p = exp(bf16(s) / 16 - m) as one FMA and one ex2 per score; every score is computed, masked ones are replaced
       // afterwards, so that the 64 chains stay independent of each other
@@ -638,23 +751,17 @@ __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_co
         pk[16 + (j >> 1)] = pack2(e, f);
       }
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      if (st == 0 && c == 1) PFA_STAMP(13);
       // the P buffer is free once the P V of chunk c - 2 has read it
       if (!wait_bar(p.status, p.wait_limit, p_empty + 8 * pslot, ((c >> 1) & 1) ^ 1, 10)) { ok = false; break; }
-      if (st == 0 && c == 1) PFA_STAMP(14);
       const uint32_t dst = prow + pslot * P_BYTES;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch)   // 16-byte piece ch of the row sits at piece ch ^ (row & 7) of its 128-byte line
         ptx::st_shared_v4(dst + (((uint32_t)ch ^ psw) << 4), pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-      if (st == 0 && c == 1) PFA_STAMP(20);
       ptx::fence_proxy_async_shared();
-      if (st == 0 && c == 1) PFA_STAMP(23);
       ptx::mbar_arrive(p_full + 8 * pslot);
-      if (st == 0 && c < 2) PFA_STAMP(17 + 2 * c);
     }
     // ---- O / l -> BF16: row = token_local * 8 + head, so a row's 256 dims are contiguous in [tokens, 2048]
     if (ok && wait_bar(p.status, p.wait_limit, o_full, 0, 11)) {
-      if (st == 0) PFA_STAMP(21);
       ptx::tc_fence_after();
       const float il = 1.0f / l;
       const int token = blockIdx.x * TOK + (row >> 3);
@@ -675,7 +782,6 @@ __global__ void __launch_bounds__(THREADS_A, 1) attention_kernel(const __grid_co
         }
       }
       ptx::tc_fence_before();
-      if (st == 0) PFA_STAMP(22);
     }
   }
   __syncthreads();
@@ -699,8 +805,9 @@ struct pi05_prefill {
   long long wait_limit = 4000000000ll;
   std::string last_error;
   // workspace offsets
-  size_t off_status, off_x, off_n, off_q, off_mixed, off_act, off_rope, off_pos, off_vt;
+  size_t off_status, off_x, off_n, off_q, off_mixed, off_act, off_rope, off_pos, off_vt, off_partial;
   int vt_stride = 0;
+  unsigned int sk_epoch = 0;        // stream-K launches of the current prefill so far
 };
 
 namespace {
@@ -769,6 +876,7 @@ struct Guard {
 };
 
 size_t up(size_t v) { return (v + 255) / 256 * 256; }
+constexpr size_t CONTROL_BYTES = 256 + 1024 * 4;
 
 // Launch with programmatic stream serialisation: the kernel may begin (set up its barriers and tensor memory) while the
 // kernel before it in the stream drains; it reads nothing that kernel wrote before its grid_dep_wait.
@@ -785,18 +893,20 @@ cudaError_t launch_after(void (*kernel)(Params...), dim3 grid, dim3 block, size_
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-template <int EPI, int BN>
+template <int EPI, int BN, bool SK>
 cudaError_t launch_gemm(pi05_prefill* h, pf::GemmParams& gp, cudaStream_t stream) {
   static bool attr_set[64] = {};
   if (!attr_set[h->device]) {
-    cudaError_t e = cudaFuncSetAttribute(pf::gemm_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(pf::gemm_kernel<EPI, BN, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          pf::RING_BYTES + 1024);
     if (e != cudaSuccess) return e;
     attr_set[h->device] = true;
   }
-  const int tiles = gp.n_tiles * gp.m_tiles;
-  const int grid = tiles < h->sms ? tiles : h->sms;
-  return launch_after(pf::gemm_kernel<EPI, BN>, dim3(grid), dim3(pf::GEMM_THREADS), pf::RING_BYTES + 1024, stream, h->overlap, gp);
+  const long long tiles = (long long)gp.n_tiles * gp.m_tiles, work = SK ? tiles * gp.kblocks : tiles;
+  const int grid = work < h->sms ? (int)work : h->sms;
+  if (SK) gp.sk_epoch = ++h->sk_epoch;
+  return launch_after(pf::gemm_kernel<EPI, BN, SK>, dim3(grid), dim3(pf::GEMM_THREADS), pf::RING_BYTES + 1024, stream,
+                      h->overlap, gp);
 }
 
 }  // namespace
@@ -821,7 +931,7 @@ int pi05_prefill_create(int device, int max_tokens, pi05_prefill_t* out) {
   const size_t P = (size_t)(max_tokens + 1) / 2 * 2;      // the attention writes token pairs
   size_t off = 0;
   auto add = [&](size_t bytes) { const size_t at = off; off = up(off + bytes); return at; };
-  h->off_status = add(256);
+  h->off_status = add(CONTROL_BYTES);   // status words, then one stream-K flag per CTA
   h->off_x = add(P * pf::H * 2);
   h->off_n = add(P * pf::H * 2);
   h->off_q = add(P * QD * 2);
@@ -831,6 +941,7 @@ int pi05_prefill_create(int device, int max_tokens, pi05_prefill_t* out) {
   h->off_pos = add(P * 4);
   h->vt_stride = (max_tokens + 63) / 64 * 64;
   h->off_vt = add((size_t)HD * h->vt_stride * 2);
+  h->off_partial = add((size_t)h->sms * pf::BM * 256 * 4);
   h->ws_bytes = off;
   *out = h;
   return PI05_OK;
@@ -892,7 +1003,8 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
   __nv_bfloat16* K = static_cast<__nv_bfloat16*>(keys);
   __nv_bfloat16* V = static_cast<__nv_bfloat16*>(values);
 
-  cudaError_t e = cudaMemsetAsync(status, 0, 256, stream);
+  h->sk_epoch = 0;
+  cudaError_t e = cudaMemsetAsync(status, 0, CONTROL_BYTES, stream);
   if (e != cudaSuccess) { h->last_error = cudaGetErrorString(e); return PI05_ERR_CUDA; }
   pf::cast_copy_kernel<<<h->sms, 256, 0, stream>>>(static_cast<const uint4*>(embeddings), reinterpret_cast<uint4*>(x),
                                                    (size_t)P * pf::H * 2 / 16);
@@ -905,13 +1017,16 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
   base.tokens = P; base.m_tiles = (P + pf::BM - 1) / pf::BM;
   base.x = x; base.act = act; base.q = q; base.rope = rope; base.status = status; base.wait_limit = h->wait_limit;
   base.vt = vt; base.vt_stride = h->vt_stride;
-  CUtensorMap a_n, a_mixed, a_act, wq, wk, wv, wo, wg, wu, wd, kmap, qmap, vtmap;
+  base.sk_partial = reinterpret_cast<float*>(ptr(h->off_partial));
+  base.sk_flags = status + 64;
+  CUtensorMap a_n, a_mixed, a_act, wq, wk, wv, wo, wg, wu, wd, wd64, kmap, qmap, vtmap;
   bool ok = map_2d(&a_n, nrm, pf::H, P, pf::BM) && map_2d(&a_mixed, mixed, QD, P, pf::BM) &&
             map_2d(&a_act, act, pf::FFN, P, pf::BM) &&
             map_2d(&wq, w[LQ], pf::H, (uint64_t)pf::LAYERS * QD, 128) && map_2d(&wk, w[LK], pf::H, (uint64_t)pf::LAYERS * HD, 128) &&
             map_2d(&wv, w[LV], pf::H, (uint64_t)pf::LAYERS * HD, 128) && map_2d(&wo, w[LO], QD, (uint64_t)pf::LAYERS * pf::H, 64) &&
             map_2d(&wg, w[LG], pf::H, (uint64_t)pf::LAYERS * pf::FFN, 128) && map_2d(&wu, w[LU], pf::H, (uint64_t)pf::LAYERS * pf::FFN, 128) &&
-            map_2d(&wd, w[LD], pf::FFN, (uint64_t)pf::LAYERS * pf::H, 64) && map_kv(&kmap, K, P) && map_2d(&qmap, q, HD, (uint64_t)P * 8, 128) &&
+            map_2d(&wd, w[LD], pf::FFN, (uint64_t)pf::LAYERS * pf::H, 128) &&
+            map_2d(&wd64, w[LD], pf::FFN, (uint64_t)pf::LAYERS * pf::H, 64) && map_kv(&kmap, K, P) && map_2d(&qmap, q, HD, (uint64_t)P * 8, 128) &&
             map_vt(&vtmap, vt, P, h->vt_stride);
   if (!ok) { h->last_error = "cuTensorMapEncodeTiled failed"; return PI05_ERR_CUDA; }
 
@@ -928,6 +1043,10 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
   ap.tokens = P; ap.status = status; ap.wait_limit = h->wait_limit;
 
   const int norm_blocks = (P + 7) / 8;
+  // The down projection (K = 16384) as whole 128 x 128 tiles when those fill more than half of the SMs (measured at 968
+  // tokens: 4.13 against 4.43 ms per prefill), as a stream-K launch of 128 x 256 tiles for shorter prompts (256 tokens: 2.43
+  // against 2.71 ms), where whole tiles would leave most SMs without work for the longest GEMM of the layer.
+  const bool sk_down = base.m_tiles * (pf::H / 128) * 2 <= h->sms;
   for (int l = 0; l < n_layers; ++l) {
     if ((e = launch_after(pf::rmsnorm_kernel, dim3(norm_blocks), dim3(256), 0, stream, h->overlap && l > 0,
                           (const __nv_bfloat16*)x, w[LN1] + (size_t)l * pf::H, nrm, P)) != cudaSuccess) break;
@@ -936,7 +1055,7 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
       gp.a = a_n; gp.b0 = gp.b1 = wq; gp.b2 = wk; gp.b3 = wv;
       gp.kblocks = pf::H / pf::BK; gp.n_tiles = 10; gp.layer = l;
       gp.k = K + (size_t)l * P * HD; gp.v = V + (size_t)l * P * HD;
-      if ((e = launch_gemm<pf::EPI_QKV, 256>(h, gp, stream)) != cudaSuccess) break;
+      if ((e = launch_gemm<pf::EPI_QKV, 256, false>(h, gp, stream)) != cudaSuccess) break;
     }
     ap.layer = l;
     if ((e = launch_after(pf::pfa::attention_kernel, dim3((P + pf::pfa::TOK - 1) / pf::pfa::TOK), dim3(pf::pfa::THREADS_A),
@@ -945,7 +1064,7 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
       pf::GemmParams gp = base;
       gp.a = a_mixed; gp.b0 = gp.b1 = wo;
       gp.kblocks = QD / pf::BK; gp.n_tiles = pf::H / 128; gp.layer = l;
-      if ((e = launch_gemm<pf::EPI_RESID, 128>(h, gp, stream)) != cudaSuccess) break;
+      if ((e = launch_gemm<pf::EPI_RESID, 128, false>(h, gp, stream)) != cudaSuccess) break;
     }
     if (l + 1 == n_layers) break;          // the last MLP does not affect any cached key or value
     if ((e = launch_after(pf::rmsnorm_kernel, dim3(norm_blocks), dim3(256), 0, stream, h->overlap,
@@ -954,13 +1073,14 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
       pf::GemmParams gp = base;
       gp.a = a_n; gp.b0 = wg; gp.b1 = wu;
       gp.kblocks = pf::H / pf::BK; gp.n_tiles = pf::FFN / 128; gp.layer = l;
-      if ((e = launch_gemm<pf::EPI_GEGLU, 256>(h, gp, stream)) != cudaSuccess) break;
+      if ((e = launch_gemm<pf::EPI_GEGLU, 256, false>(h, gp, stream)) != cudaSuccess) break;
     }
     {
       pf::GemmParams gp = base;
-      gp.a = a_act; gp.b0 = gp.b1 = wd;
-      gp.kblocks = pf::FFN / pf::BK; gp.n_tiles = pf::H / 128; gp.layer = l;
-      if ((e = launch_gemm<pf::EPI_RESID, 128>(h, gp, stream)) != cudaSuccess) break;
+      gp.a = a_act; gp.b0 = gp.b1 = sk_down ? wd : wd64;
+      gp.kblocks = pf::FFN / pf::BK; gp.n_tiles = pf::H / (sk_down ? 256 : 128); gp.layer = l;
+      e = sk_down ? launch_gemm<pf::EPI_RESID, 256, true>(h, gp, stream) : launch_gemm<pf::EPI_RESID, 128, false>(h, gp, stream);
+      if (e != cudaSuccess) break;
     }
   }
   if (e == cudaSuccess) e = cudaGetLastError();
