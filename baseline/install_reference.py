@@ -128,9 +128,12 @@ def prebuild(pairs: list[str]) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("PI05_REFERENCE_DIR", ""),
+                    help="root of the reference's source tree (or set PI05_REFERENCE_DIR)")
     ap.add_argument("--prebuild", nargs="*", default=[])
     args = ap.parse_args()
+    if not args.reference or not os.path.isdir(args.reference):
+        raise SystemExit("give the reference's source tree with --reference DIR")
     install(args.reference)
     print("installed", PKG)
     if args.prebuild:
