@@ -35,11 +35,12 @@ def _run(geo, inputs, layers=None):
     return k.cpu(), v.cpu()
 
 
-@pytest.mark.parametrize("tokens,mask,layers", [(64, "full", 1), (200, "pad", 2), (131, "pad", 3), (650, "pad", 3)])
+@pytest.mark.parametrize("tokens,mask,layers", [(64, "full", 1), (200, "pad", 2), (131, "pad", 3), (300, "pad", 2), (650, "pad", 3)])
 def test_first_layers_against_the_oracle(tokens, mask, layers):
     """Short runs: one to three layers, token counts that do not fill the 128-token tiles or the 64-key chunks.  Up to 512
     tokens the down projection runs as a stream-K launch (partial tiles summed through the workspace), beyond as whole
-    tiles: the 650-token case covers that path and an attention of eleven key chunks."""
+    tiles: the 650-token case covers that path and an attention of eleven key chunks.  From two 128-token tiles on the big
+    GEMMs run on CTA pairs over 256 tokens: 300 tokens leave the second CTA of the last pair without any token."""
     geo = FX.PrefillGeometry(tokens=tokens)
     inputs = FX.make_prefill_inputs(geo, 31, mask)
     args = (inputs, inputs["embeddings"], inputs["valid"], geo.q_heads, geo.kv_heads, geo.head_dim)
