@@ -53,6 +53,35 @@ def test_argument_errors_never_touch_a_gpu(lib):
         assert not h.value
 
 
+def test_prefill_argument_errors_never_touch_a_gpu(lib):
+    """The prefill entry points check their arguments before they look for a device, and the Python wrapper has no CPU path."""
+    h = ctypes.c_void_p()
+    assert lib.pi05_prefill_create(0, 968, None) == _lib.ERR_ARGUMENT
+    assert lib.pi05_prefill_create(-1, 968, ctypes.byref(h)) == _lib.ERR_ARGUMENT
+    assert lib.pi05_prefill_create(0, 0, ctypes.byref(h)) == _lib.ERR_ARGUMENT
+    assert lib.pi05_prefill_create(0, 4097, ctypes.byref(h)) == _lib.ERR_ARGUMENT
+    n = ctypes.c_size_t()
+    assert lib.pi05_prefill_workspace_bytes(None, ctypes.byref(n)) == _lib.ERR_ARGUMENT
+    assert lib.pi05_prefill_run(None, None, None, 1, None, None, 18, None) == _lib.ERR_ARGUMENT
+    assert lib.pi05_prefill_destroy(None) == _lib.ERR_ARGUMENT
+    if not torch.cuda.is_available():
+        assert lib.pi05_prefill_create(0, 968, ctypes.byref(h)) == _lib.ERR_NO_DEVICE
+        assert not h.value
+        from pi05_megakernel_b200.prefill import Pi05Prefill
+        with pytest.raises(RuntimeError):
+            Pi05Prefill(FX.PrefillGeometry(tokens=64), "cuda")
+
+
+def test_prefill_fixture_is_deterministic():
+    geo = FX.PrefillGeometry(tokens=96, layers=1)
+    shapes = FX.prefill_shapes(geo)
+    assert set(FX.PREFILL_WEIGHTS) <= set(shapes) and shapes["ld"][0] == (1, 2048, 16384)
+    a, b = FX.make_prefill_inputs(geo, 5, "pad"), FX.make_prefill_inputs(geo, 5, "pad")
+    assert all(torch.equal(a[k], b[k]) for k in a)
+    assert a["valid"].dtype == torch.bool and 48 <= int(a["valid"].sum()) <= 96
+    assert bool(a["valid"][: int(a["valid"].sum())].all())          # right-padded: the valid tokens come first
+
+
 def test_no_cpu_fallback():
     if torch.cuda.is_available():
         pytest.skip("GPU present")
