@@ -262,6 +262,15 @@ int pi05_prefill_bind(pi05_prefill_t h, const void* const weights[PI05_PREFILL_N
  * layers ([18, tokens, 1, 256]); n_layers < 18 runs only the first layers (debug). */
 int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid, int tokens, void* keys, void* values,
                      int n_layers, void* stream);
+/* How pi05_prefill_run launches a prefill of `tokens` tokens on a GPU of `sms` SMs, computed on the host (no counterpart
+ * in the reference, whose prefill is eager PyTorch; it exists so that these decisions can be tested without a GPU).
+ * info = {128-token tiles, 1 when the gate/up, down and O projections run on CTA pairs over 256-token tiles, 1 when the
+ * down projection is a stream-K launch, and for that launch its 128 x 256 tiles, k blocks per tile and CTAs (else 0)}.
+ * With a stream-K down projection the call also lists the segments {tile, first k block, one past the last} CTA `cta`
+ * works through, in order (up to `capacity` triples; *count receives their number): a segment that starts at k block 0
+ * makes the CTA the tile's owner, any other one a contributor of partial sums. */
+#define PI05_PREFILL_PLAN_INFO 6
+int pi05_prefill_plan(int sms, int tokens, int cta, int info[PI05_PREFILL_PLAN_INFO], int* segments, int capacity, int* count);
 /* Synchronises `stream` and reports a bounded device-side wait that gave up (PI05_ERR_DEVICE_TIMEOUT), like pi05_status. */
 int pi05_prefill_status(pi05_prefill_t h, void* stream, int* code, int* where);
 const char* pi05_prefill_last_error(pi05_prefill_t h);

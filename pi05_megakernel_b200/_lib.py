@@ -95,6 +95,8 @@ SIGNATURES = {
     "pi05_prefill_run": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int,
                                     _c.c_void_p]),
     "pi05_prefill_status": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
+    "pi05_prefill_plan": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_int), _c.POINTER(_c.c_int), _c.c_int,
+                                     _c.POINTER(_c.c_int)]),
     "pi05_prefill_last_error": (_c.c_char_p, [_c.c_void_p]),
     "pi05_prefill_destroy": (_c.c_int, [_c.c_void_p]),
     "pi05_tuning_defaults": (_c.c_int, [_c.POINTER(Tuning)]),

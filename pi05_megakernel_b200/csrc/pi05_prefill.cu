@@ -240,16 +240,15 @@ template <bool SK>
 struct Segments {
   int kblocks, ntiles, tile, stride;
   long long u, uend;
-  __device__ Segments(int kblocks_, int ntiles_) : kblocks(kblocks_), ntiles(ntiles_) {
+  __host__ __device__ Segments(int kblocks_, int ntiles_, int cta, int ctas) : kblocks(kblocks_), ntiles(ntiles_) {
+    tile = cta; stride = ctas; u = uend = 0;
     if (SK) {
       const long long total = (long long)ntiles * kblocks;
-      u = total * blockIdx.x / gridDim.x;
-      uend = total * (blockIdx.x + 1) / gridDim.x;
-    } else {
-      tile = blockIdx.x; stride = gridDim.x;
+      u = total * cta / ctas;
+      uend = total * (cta + 1) / ctas;
     }
   }
-  __device__ bool next(int& t, int& kb0, int& kb1) {
+  __host__ __device__ bool next(int& t, int& kb0, int& kb1) {
     if (SK) {
       if (u >= uend) return false;
       t = (int)(u / kblocks);
@@ -301,7 +300,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
   // everything up to here overlapped the tail of the kernel before; its outputs are read from here on
   ptx::grid_dep_launch();
   ptx::grid_dep_wait();
-  Segments<SK> segs(p.kblocks, ntiles);
+  Segments<SK> segs(p.kblocks, ntiles, (int)blockIdx.x, (int)gridDim.x);
   int tile, kb0, kb1;
 
   if (warp == 0) {
@@ -1038,6 +1037,32 @@ cudaError_t launch_after(void (*kernel)(Params...), dim3 grid, dim3 block, size_
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// How a prefill of `tokens` tokens is launched on a GPU of `sms` SMs: the decisions pi05_prefill_run takes and
+// pi05_prefill_plan reports.
+struct PrefillPlan {
+  int m_tiles;        // 128-token tiles
+  bool pairs;         // gate/up, down and O projections on CTA pairs (256-token tiles)
+  bool sk_down;       // down projection as a stream-K launch of 128 x 256 tiles
+  int down_tiles, down_kblocks, down_ctas;
+};
+
+PrefillPlan plan_prefill(int sms, int tokens) {
+  PrefillPlan pl;
+  pl.m_tiles = (tokens + pf::BM - 1) / pf::BM;
+  // The down projection (K = 16384) as whole 128 x 128 tiles when those fill more than half of the SMs (measured at 968
+  // tokens: 4.13 against 4.43 ms per prefill), as a stream-K launch of 128 x 256 tiles for shorter prompts (256 tokens: 2.43
+  // against 2.71 ms), where whole tiles would leave most SMs without work for the longest GEMM of the layer.
+  pl.sk_down = pl.m_tiles * (pf::H / 128) * 2 <= sms;
+  // CTA pairs work on 256 tokens at a time: with a single tile of tokens the second CTA of every pair would idle.  Measured
+  // at 968 tokens, ms per prefill: no pairs 4.15, gate/up on pairs 3.95, + down projection 3.73, + O projection 3.73-3.77.
+  pl.pairs = pl.m_tiles >= 2;
+  pl.down_kblocks = pf::FFN / pf::BK;
+  pl.down_tiles = pl.m_tiles * (pf::H / 256);
+  const long long units = (long long)pl.down_tiles * pl.down_kblocks;
+  pl.down_ctas = units < sms ? (int)units : sms;
+  return pl;
+}
+
 template <int EPI, int BN, bool SK>
 cudaError_t launch_gemm(pi05_prefill* h, pf::GemmParams& gp, cudaStream_t stream) {
   static bool attr_set[64] = {};
@@ -1204,13 +1229,8 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
   ap.tokens = P; ap.status = status; ap.wait_limit = h->wait_limit;
 
   const int norm_blocks = (P + 7) / 8;
-  // The down projection (K = 16384) as whole 128 x 128 tiles when those fill more than half of the SMs (measured at 968
-  // tokens: 4.13 against 4.43 ms per prefill), as a stream-K launch of 128 x 256 tiles for shorter prompts (256 tokens: 2.43
-  // against 2.71 ms), where whole tiles would leave most SMs without work for the longest GEMM of the layer.
-  const bool sk_down = base.m_tiles * (pf::H / 128) * 2 <= h->sms;
-  // CTA pairs work on 256 tokens at a time: with a single tile of tokens the second CTA of every pair would idle.  Measured
-  // at 968 tokens, ms per prefill: no pairs 4.15, gate/up on pairs 3.95, + down projection 3.73, + O projection 3.73-3.77.
-  const bool pairs_pay = base.m_tiles >= 2;
+  const PrefillPlan plan = plan_prefill(h->sms, P);
+  const bool sk_down = plan.sk_down, pairs_pay = plan.pairs;
   for (int l = 0; l < n_layers; ++l) {
     if ((e = launch_after(pf::rmsnorm_kernel, dim3(norm_blocks), dim3(256), 0, stream, h->overlap && l > 0, false,
                           (const __nv_bfloat16*)x, w[LN1] + (size_t)l * pf::H, nrm, P)) != cudaSuccess) break;
@@ -1255,6 +1275,24 @@ int pi05_prefill_run(pi05_prefill_t h, const void* embeddings, const void* valid
   }
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) { h->last_error = std::string("kernel launch: ") + cudaGetErrorString(e); return PI05_ERR_CUDA; }
+  return PI05_OK;
+}
+
+int pi05_prefill_plan(int sms, int tokens, int cta, int info[PI05_PREFILL_PLAN_INFO], int* segments, int capacity, int* count) {
+  if (sms < 2 || sms > 1024 || tokens < 1 || tokens > 4096 || !info || !count || capacity < 0 || (capacity && !segments))
+    return PI05_ERR_ARGUMENT;
+  const PrefillPlan pl = plan_prefill(sms, tokens);
+  info[0] = pl.m_tiles; info[1] = pl.pairs; info[2] = pl.sk_down;
+  info[3] = pl.sk_down ? pl.down_tiles : 0; info[4] = pl.sk_down ? pl.down_kblocks : 0; info[5] = pl.sk_down ? pl.down_ctas : 0;
+  *count = 0;
+  if (!pl.sk_down) return PI05_OK;
+  if (cta < 0 || cta >= pl.down_ctas) return PI05_ERR_ARGUMENT;
+  pf::Segments<true> segs(pl.down_kblocks, pl.down_tiles, cta, pl.down_ctas);
+  int tile, kb0, kb1;
+  while (segs.next(tile, kb0, kb1)) {
+    if (*count < capacity) { segments[3 * *count] = tile; segments[3 * *count + 1] = kb0; segments[3 * *count + 2] = kb1; }
+    ++*count;
+  }
   return PI05_OK;
 }
 

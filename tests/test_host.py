@@ -72,6 +72,44 @@ def test_prefill_argument_errors_never_touch_a_gpu(lib):
             Pi05Prefill(FX.PrefillGeometry(tokens=64), "cuda")
 
 
+@pytest.mark.parametrize("sms", [148, 132])
+@pytest.mark.parametrize("tokens", [1, 64, 129, 200, 256, 300, 512, 513, 968, 4096])
+def test_prefill_plan(lib, sms, tokens):
+    """The launch decisions of the prefill, and for a stream-K down projection the partition of (tile, k block) units over
+    the CTAs: every unit exactly once, contiguous ranges of equal size (+-1), and for every tile cut over several CTAs one
+    owner (the CTA that has its k block 0) followed by contributors that are the next CTAs' FIRST segments - the order
+    that lets an owner wait for CTAs of higher index only while contributors wait for nobody."""
+    info, count = (ctypes.c_int * 6)(), ctypes.c_int()
+    assert lib.pi05_prefill_plan(sms, tokens, 0, info, None, 0, ctypes.byref(count)) == _lib.OK
+    m_tiles, pairs, sk, tiles, kblocks, ctas = list(info)
+    assert m_tiles == (tokens + 127) // 128 and pairs == (m_tiles >= 2) and sk == (m_tiles * 16 * 2 <= sms)
+    if not sk:
+        assert (tiles, kblocks, ctas, count.value) == (0, 0, 0, 0)
+        return
+    assert (tiles, kblocks, ctas) == (m_tiles * 8, 256, min(sms, m_tiles * 8 * 256))
+    assert lib.pi05_prefill_plan(sms, tokens, ctas, info, None, 0, ctypes.byref(count)) == _lib.ERR_ARGUMENT
+    per_cta = []
+    for cta in range(ctas):
+        buf = (ctypes.c_int * (3 * 8))()
+        assert lib.pi05_prefill_plan(sms, tokens, cta, info, buf, 8, ctypes.byref(count)) == _lib.OK
+        assert 1 <= count.value <= 8
+        per_cta.append([tuple(buf[3 * i: 3 * i + 3]) for i in range(count.value)])
+    units = [(t, kb) for segs in per_cta for (t, a, b) in segs for kb in range(a, b)]
+    assert units == [(t, kb) for t in range(tiles) for kb in range(kblocks)]          # every unit once, in order
+    sizes = [sum(b - a for (_t, a, b) in segs) for segs in per_cta]
+    assert max(sizes) - min(sizes) <= 1
+    for cta, segs in enumerate(per_cta):
+        for i, (t, a, b) in enumerate(segs):
+            assert i == 0 or a == 0                      # only a CTA's first segment can start inside a tile
+            if a == 0 and b < kblocks:                   # owner of a tile that goes on in the following CTAs
+                assert i == len(segs) - 1
+                end, peer = b, cta + 1
+                while end < kblocks:
+                    pt, pa, pb = per_cta[peer][0]
+                    assert (pt, pa) == (t, end) and pa > 0
+                    end, peer = pb, peer + 1
+
+
 def test_prefill_fixture_is_deterministic():
     geo = FX.PrefillGeometry(tokens=96, layers=1)
     shapes = FX.prefill_shapes(geo)
