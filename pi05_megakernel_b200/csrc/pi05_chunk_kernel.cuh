@@ -36,7 +36,7 @@ constexpr int V_A_ATOM = GN * A_ATOM_BYTES;            // 64 * GN token rows x 6
 constexpr int V_STAGE_ALL = W_STAGE_BYTES + 2 * V_A_ATOM;
 constexpr int V_NSTG = GN == 1 ? 4 : 3;
 constexpr int V_TMEM_COLS = 2 * 64 * GN;               // two accumulators of 64 * GN columns
-static_assert(V_NSTG * V_STAGE_ALL <= OFF_STAGE && V_NSTG <= NSTG && V_TMEM_COLS <= 512, "ring / TMEM budget");
+static_assert(V_NSTG * V_STAGE_ALL <= OFF_STAGE && V_NSTG <= NSTG && V_TMEM_COLS <= 512, "ring / TMEM capacity");
 #define PI05_NGRP(p) ((PI05_NB(p) + GN - 1) / GN)      // groups of observations that share MMAs
 
 __device__ __constant__ int kGemmStage[4] = {ST_QKV, ST_O, ST_GU, ST_DOWN};

@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
   constexpr int NST = RING_BYTES / STAGE;
   constexpr int TCOLS = 2 * BN;
-  static_assert(NST >= 4 && TCOLS <= 512, "ring / TMEM budget");
+  static_assert(NST >= 4 && TCOLS <= 512, "ring / TMEM capacity");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bars[2 * NST + 6];
@@ -458,7 +458,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_pair_kernel(const __grid
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, STAGE = A_BYTES + B_BYTES;
   constexpr int NST = RING_BYTES / STAGE;
   constexpr int TCOLS = 2 * BN;
-  static_assert(NST >= 4 && TCOLS <= 512 && TCOLS >= 32 && (TCOLS & (TCOLS - 1)) == 0, "ring / TMEM budget");
+  static_assert(NST >= 4 && TCOLS <= 512 && TCOLS >= 32 && (TCOLS & (TCOLS - 1)) == 0, "ring / TMEM capacity");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bars[2 * NST + 4];
