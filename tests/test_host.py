@@ -289,3 +289,23 @@ def test_tensor_parallel_plans_partition_the_work(lib, size):
     assert lib.pi05_schedule_plan_tp(148, 1, 128, 2, 2, None, None, 0, ctypes.byref(count), info) == _lib.ERR_ARGUMENT
     assert lib.pi05_schedule_plan_tp(148, 2, 128, 0, 2, None, None, 0, ctypes.byref(count), info) == _lib.ERR_UNSUPPORTED
     assert lib.pi05_schedule_plan_tp(148, 1, 128, 0, 3, None, None, 0, ctypes.byref(count), info) == _lib.ERR_UNSUPPORTED
+
+
+def test_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` runs on the host cores alone: the reference's own eager path where it is installed
+    beside the benchmark, else the oracle port; its one JSON line carries the keys the driver of the benchmark reads."""
+    import json
+    import subprocess
+    import sys
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "3"],
+                          capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [l for l in proc.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["unit"] == "chunks/s" and d["higher_is_better"] is True and d["n_gpus"] == 1
+    assert d["steps"] == 1 and d["warmup"] >= 3 and d["value"] > 0 and abs(d["value"] * d["ms_per_step"] - 1e3) < 1e-6 * 1e3
+    assert d["cpu_baseline"]["kind"] in ("reference", "port") and d["cpu_baseline"]["cores"] >= 1
+    assert d["cpu_baseline"]["value"] == d["value"]
+    assert d["e2e"] == {"value": d["value"], "unit": "chunks/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in d["config"]
